@@ -1,0 +1,291 @@
+"""CPU oracle for the paged KV cache path — TEST INFRASTRUCTURE ONLY.
+
+ctypes wrapper over ``kv_oracle.c`` (the C restatement of the reference's
+``engine/core/combs-models/src/kv.rs``).  Only the tests, the smoke check and
+the CPU-baseline leg of the benchmark may import this package; the product
+package ``combsengine_b200`` never does.
+
+Floating-point parity is unpinned in the golden-vector sense (the reference
+stores no attention outputs); integer/state behaviour is pinned by the
+reference's own known-answer tests.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIBS: dict[str, C.CDLL] = {}
+
+I64 = C.c_int64
+P = C.c_void_p
+
+
+def build(force: bool = False) -> None:
+    """Compile the oracle (gcc, a few seconds)."""
+    out = os.path.join(_HERE, "_build")
+    if not force and all(os.path.exists(os.path.join(out, f"liborc_{k}.so")) for k in ("f32", "f16")):
+        src = os.path.getmtime(os.path.join(_HERE, "kv_oracle.c"))
+        if all(os.path.getmtime(os.path.join(out, f"liborc_{k}.so")) >= src for k in ("f32", "f16")):
+            return
+    subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+
+
+def _lib(kind: str) -> C.CDLL:
+    if kind in _LIBS:
+        return _LIBS[kind]
+    path = os.path.join(_HERE, "_build", f"liborc_{kind}.so")
+    if not os.path.exists(path):
+        build()
+    lib = C.CDLL(path)
+    lib.orc_last_error.restype = C.c_char_p
+    lib.orc_arena_new.restype = P
+    lib.orc_arena_new.argtypes = [C.c_int, C.c_int, C.c_int, I64, C.c_int, I64, P, C.c_int]
+    lib.orc_arena_free.argtypes = [P]
+    lib.orc_set_free_list.argtypes = [P, P, I64]
+    lib.orc_seq_new.restype = P
+    lib.orc_seq_new.argtypes = [P]
+    lib.orc_seq_free.argtypes = [P]
+    lib.orc_seq_fork_prefix.restype = P
+    lib.orc_seq_fork_prefix.argtypes = [P, I64]
+    lib.orc_grow.argtypes = [P, I64]
+    lib.orc_begin.argtypes = [P, I64, I64]
+    for name in ("orc_layer", "orc_attention", "orc_contig_attention"):
+        getattr(lib, name).argtypes = [P, C.c_int, P, P, P, P, C.c_int, I64, I64, C.c_double, I64]
+    lib.orc_popn.restype = I64
+    lib.orc_popn.argtypes = [P, I64]
+    lib.orc_reset.argtypes = [P]
+    for name in ("orc_seq_len", "orc_pages_used", "orc_num_free_pages", "orc_contig_seq_len"):
+        getattr(lib, name).restype = I64
+        getattr(lib, name).argtypes = [P]
+    lib.orc_page_stats.argtypes = [P, P]
+    lib.orc_export_block_table.restype = I64
+    lib.orc_export_block_table.argtypes = [P, P, I64]
+    lib.orc_export_free_list.restype = I64
+    lib.orc_export_free_list.argtypes = [P, P, I64]
+    lib.orc_export_page.argtypes = [P, C.c_int, I64, P, P]
+    lib.orc_page_refcount.restype = C.c_int32
+    lib.orc_page_refcount.argtypes = [P, I64]
+    lib.orc_contig_new.restype = P
+    lib.orc_contig_new.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.orc_contig_reset.argtypes = [P]
+    lib.orc_contig_free.argtypes = [P]
+    lib.orc_batch_begin.argtypes = [P, P, C.c_int]
+    lib.orc_batch_layer.argtypes = [P, P, C.c_int, C.c_int, P, P, P, P, C.c_int, C.c_double, I64]
+    _LIBS[kind] = lib
+    return lib
+
+
+class OracleError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+PAGE_STATS_FIELDS = ("pages_used", "pages_free", "num_pages", "page_size", "seq_len",
+                     "layers_materialized", "layers_total", "layers_sliding")
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(P)
+
+
+class OracleArena:
+    """Arena + allocator shared by the sequences created from it."""
+
+    def __init__(self, layers: int, n_kv: int, head_dim: int, max_seq_len: int, page_size: int = 16,
+                 num_pages: int = 0, windows=None, rolling: bool = True, dtype: str = "f16"):
+        self.kind = dtype
+        self.np_dtype = np.float16 if dtype == "f16" else np.float32
+        self.lib = _lib(dtype)
+        self.layers, self.n_kv, self.d, self.page_size = layers, n_kv, head_dim, page_size
+        w = None
+        if windows is not None:
+            assert len(windows) == layers, "one window entry per layer"
+            w = np.asarray([0 if x is None else int(x) for x in windows], dtype=np.int64)
+        self.h = self.lib.orc_arena_new(layers, n_kv, head_dim, max_seq_len, page_size, num_pages,
+                                        _ptr(w) if w is not None else None, 1 if rolling else 0)
+        if not self.h:
+            raise OracleError(-4, self.lib.orc_last_error().decode())
+        self.num_pages = num_pages if num_pages > 0 else -(-max_seq_len // page_size)
+        self._seqs = []
+
+    def __del__(self):
+        try:
+            for s in list(self._seqs):
+                s.close()
+            if self.h:
+                self.lib.orc_arena_free(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def set_free_list(self, ids) -> None:
+        a = np.ascontiguousarray(ids, dtype=np.int64)
+        rc = self.lib.orc_set_free_list(self.h, _ptr(a), len(a))
+        if rc:
+            raise OracleError(rc, self.lib.orc_last_error().decode())
+
+    def new_seq(self) -> "OracleSeq":
+        return OracleSeq(self, self.lib.orc_seq_new(self.h))
+
+    def num_free_pages(self) -> int:
+        return self.lib.orc_num_free_pages(self.h)
+
+    def free_list(self) -> np.ndarray:
+        out = np.zeros(self.num_pages, dtype=np.int64)
+        n = self.lib.orc_export_free_list(self.h, _ptr(out), len(out))
+        return out[:n]
+
+    def page(self, layer: int, page: int):
+        k = np.zeros((self.n_kv, self.page_size, self.d), dtype=self.np_dtype)
+        v = np.zeros_like(k)
+        self.lib.orc_export_page(self.h, layer, page, _ptr(k), _ptr(v))
+        return k, v
+
+    def refcount(self, page: int) -> int:
+        return self.lib.orc_page_refcount(self.h, page)
+
+    # batch driver (timed CPU baseline): packed per-sequence [H, s_b, d] blocks
+    def batch_begin(self, seqs, new_tokens) -> None:
+        hs = (P * len(seqs))(*[s.h for s in seqs])
+        nt = np.ascontiguousarray(new_tokens, dtype=np.int64)
+        rc = self.lib.orc_batch_begin(hs, _ptr(nt), len(seqs))
+        if rc:
+            raise OracleError(rc, self.lib.orc_last_error().decode())
+
+    def batch_layer(self, seqs, new_tokens, layer, q, k, v, n_q, scale, window=None) -> np.ndarray:
+        hs = (P * len(seqs))(*[s.h for s in seqs])
+        nt = np.ascontiguousarray(new_tokens, dtype=np.int64)
+        q = np.ascontiguousarray(q, dtype=self.np_dtype)
+        k = np.ascontiguousarray(k, dtype=self.np_dtype)
+        v = np.ascontiguousarray(v, dtype=self.np_dtype)
+        out = np.empty_like(q)
+        rc = self.lib.orc_batch_layer(hs, _ptr(nt), len(seqs), layer, _ptr(q), _ptr(k), _ptr(v), _ptr(out),
+                                      n_q, float(scale), 0 if window is None else int(window))
+        if rc:
+            raise OracleError(rc, self.lib.orc_last_error().decode())
+        return out
+
+
+class OracleSeq:
+    """One sequence; alone in a fresh arena it is the reference's PagedKVCache."""
+
+    def __init__(self, arena: OracleArena, handle):
+        self.arena, self.lib, self.h = arena, arena.lib, handle
+        arena._seqs.append(self)
+
+    def close(self):
+        if self.h:
+            self.lib.orc_seq_free(self.h)
+            self.h = None
+            self.arena._seqs.remove(self)
+
+    def _check(self, rc):
+        if rc:
+            raise OracleError(rc, self.lib.orc_last_error().decode())
+
+    def _call(self, fn, layer, q, k, v, pos, scale, window):
+        dt = self.arena.np_dtype
+        q = np.ascontiguousarray(q, dtype=dt)
+        k = np.ascontiguousarray(k, dtype=dt)
+        v = np.ascontiguousarray(v, dtype=dt)
+        lead = q.shape[:-3]
+        n_q, seq, d = q.shape[-3:]
+        assert k.shape[-3:] == (self.arena.n_kv, seq, d) and v.shape == k.shape
+        out = np.empty_like(q)
+        self._check(fn(self.h, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(out), n_q, seq, pos, float(scale),
+                       0 if window is None else int(window)))
+        return out.reshape(lead + (n_q, seq, d))
+
+    def attention_opts(self, layer, q, k, v, pos, scale, window=None):
+        """q [1,n_q,seq,d] (or [n_q,seq,d]); k, v [1,n_kv,seq,d]; returns q's shape."""
+        return self._call(self.lib.orc_attention, layer, q, k, v, pos, scale, window)
+
+    def attention(self, layer, q, k, v, pos, scale):
+        return self.attention_opts(layer, q, k, v, pos, scale, None)
+
+    def begin(self, pos, seq):
+        self._check(self.lib.orc_begin(self.h, pos, seq))
+
+    def layer(self, layer, q, k, v, pos, scale, window=None):
+        return self._call(self.lib.orc_layer, layer, q, k, v, pos, scale, window)
+
+    def grow(self, total):
+        self._check(self.lib.orc_grow(self.h, total))
+
+    def fork_prefix(self, n_tokens) -> "OracleSeq":
+        h = self.lib.orc_seq_fork_prefix(self.h, n_tokens)
+        if not h:
+            raise OracleError(-4, self.lib.orc_last_error().decode())
+        return OracleSeq(self.arena, h)
+
+    def popn(self, n) -> int:
+        return self.lib.orc_popn(self.h, n)
+
+    def reset(self):
+        self.lib.orc_reset(self.h)
+
+    def seq_len(self) -> int:
+        return self.lib.orc_seq_len(self.h)
+
+    def pages_used(self) -> int:
+        return self.lib.orc_pages_used(self.h)
+
+    def num_free_pages(self) -> int:
+        return self.arena.num_free_pages()
+
+    def page_stats(self) -> dict:
+        out = np.zeros(8, dtype=np.int64)
+        self.lib.orc_page_stats(self.h, _ptr(out))
+        return dict(zip(PAGE_STATS_FIELDS, (int(x) for x in out)))
+
+    def block_table(self) -> np.ndarray:
+        out = np.zeros(max(1, self.pages_used()), dtype=np.int64)
+        n = self.lib.orc_export_block_table(self.h, _ptr(out), len(out))
+        return out[:n]
+
+
+class OracleContiguous:
+    """ContiguousKVCache (kv.rs:360-415), the reference's cross-validation baseline."""
+
+    def __init__(self, layers, n_kv, head_dim, dtype="f32"):
+        self.lib = _lib(dtype)
+        self.np_dtype = np.float16 if dtype == "f16" else np.float32
+        self.n_kv = n_kv
+        self.h = self.lib.orc_contig_new(layers, n_kv, head_dim)
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.lib.orc_contig_free(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def attention_opts(self, layer, q, k, v, pos, scale, window=None):
+        dt = self.np_dtype
+        q = np.ascontiguousarray(q, dtype=dt)
+        k = np.ascontiguousarray(k, dtype=dt)
+        v = np.ascontiguousarray(v, dtype=dt)
+        n_q, seq, d = q.shape[-3:]
+        out = np.empty_like(q)
+        rc = self.lib.orc_contig_attention(self.h, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(out), n_q, seq, pos,
+                                           float(scale), 0 if window is None else int(window))
+        assert rc == 0
+        return out
+
+    def attention(self, layer, q, k, v, pos, scale):
+        return self.attention_opts(layer, q, k, v, pos, scale, None)
+
+    def seq_len(self):
+        return self.lib.orc_contig_seq_len(self.h)
+
+    def reset(self):
+        self.lib.orc_contig_reset(self.h)
+
+    def popn(self, n):  # KVCache default, kv.rs:133-136
+        return 0
