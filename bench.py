@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the paged KV decode path (append + GQA decode attention over pages).
+
+Workload (N=1): batched decode at Qwen2.5-7B geometry — 28 layers, 28 q heads,
+4 kv heads, head_dim 128, f16 K/V; 32 sequences per GPU with context lengths
+uniform in [1024, 4096] from a seed; pages scattered over an arena of 8192 pages
+(131072 tokens) by a seeded shuffle of the free-list.  One step = one token
+appended per sequence + decode attention over every layer (28 fused launches).
+With N GPUs every rank runs its own 32 sequences (sharded by sequence, no
+collective in the path): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM;
+`e2e` is the same step driven through the host-buffer entry point with the
+host<->device copies inside the timed region; `roofline` is the decode kernel's
+algorithmic bytes per launch over its CUDA-event duration against the measured
+HBM copy bandwidth; `cpu_baseline` is the CPU oracle (a port of the reference
+algorithm) timed on this box's host cores on a bounded sample.
+
+`--impl reference` times that CPU port alone, with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS, N_Q, N_KV, D, PAGE = 28, 28, 4, 128, 16
+BATCH, CTX_LO, CTX_HI, ARENA_PAGES = 32, 1024, 4096, 8192
+SEED = 0xC0B50002
+SCALE = D ** -0.5
+METRIC = "paged_decode_attention_tokens_per_s"
+
+
+def context_lengths(rank: int) -> np.ndarray:
+    rng = np.random.default_rng(SEED + 1000 * rank)
+    return rng.integers(CTX_LO, CTX_HI + 1, BATCH)
+
+
+def algorithmic_bytes_per_layer(lens_after: np.ndarray) -> float:
+    """Per sequence: read K and V of L tokens, read Q / write O, read the new k,v and
+    write them into the page, read the block-table ids."""
+    L = lens_after.astype(np.float64)
+    per = 4 * N_KV * D * L + 4 * N_Q * D + 8 * N_KV * D + 4 * np.ceil(L / PAGE)
+    return float(per.sum())
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "power_w_max": max(float(r[3]) for r in rows), "samples": len(rows)}
+
+
+# ------------------------------------------------------------------ CPU port (oracle) timing
+def time_cpu_port(n_seqs: int, n_layers: int, budget_s: float, lens: np.ndarray) -> dict:
+    """The oracle's batch driver (a port of the reference algorithm: per-page scatter,
+    materialised gather, repeat_kv, f32 upcast, scores, softmax, P.V) on host cores."""
+    import oracle
+    oracle.build()
+    from oracle import OracleArena
+    rng = np.random.default_rng(SEED)
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    lens = lens[:n_seqs]
+    pages = int(sum(-(-(int(n) + 64) // PAGE) for n in lens)) + 8
+    arena = OracleArena(n_layers, N_KV, D, CTX_HI + 256, PAGE, pages, rolling=False, dtype="f16")
+    seqs = [arena.new_seq() for _ in range(n_seqs)]
+    arena.batch_begin(seqs, [int(n) for n in lens])
+    for s, n in zip(seqs, lens):
+        k = rng.standard_normal((N_KV, int(n), D)).astype(np.float16)
+        v = rng.standard_normal((N_KV, int(n), D)).astype(np.float16)
+        for layer in range(n_layers):
+            s.append_only(layer, k, v, 0)
+    ones = [1] * n_seqs
+    q = rng.standard_normal(n_seqs * N_Q * D).astype(np.float16)
+    k = rng.standard_normal(n_seqs * N_KV * D).astype(np.float16)
+    v = rng.standard_normal(n_seqs * N_KV * D).astype(np.float16)
+    steps, t0 = 0, time.perf_counter()
+    while True:
+        arena.batch_begin(seqs, ones)
+        for layer in range(n_layers):
+            arena.batch_layer(seqs, ones, layer, q, k, v, N_Q, SCALE)
+        steps += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s or steps >= 64:
+            break
+    # a token = one sequence advanced through all 28 layers
+    value = n_seqs * steps * (n_layers / LAYERS) / el
+    return {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{n_seqs} sequences x {n_layers} of {LAYERS} layers x {steps} decode steps in {el:.1f} s, scaled by layers"}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    lens = context_lengths(0)
+    # every "step" is a bounded sample: all 32 sequences, 2 of the 28 layers
+    total_budget = 8.0 * max(1, args.steps + args.warmup)
+    res = time_cpu_port(BATCH, 2, min(90.0, total_budget), lens)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": BATCH / res["value"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "cfg2 qwen2.5-7b geometry batched decode, batch 32, ctx U[1024,4096], 28 layers",
+                   "note": "the reference (Rust on Burn/wgpu) cannot be built here; this is the CPU port of its algorithm"},
+        "cpu_baseline": res,
+        "e2e": {"value": res["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+    import torch.distributed as dist
+    from combsengine_b200 import KVArena, _lib, kv
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    lens = context_lengths(rank)
+    total_steps = 3 * (args.steps + args.warmup) + 16
+    arena = KVArena(LAYERS, N_Q, N_KV, D, CTX_HI + total_steps + 64, PAGE, ARENA_PAGES, device=local_rank)
+    arena.set_free_list(np.random.default_rng(SEED + 7 + rank).permutation(ARENA_PAGES))
+    if args.ctas_per_sm:
+        arena.set_decode_ctas_per_sm(args.ctas_per_sm)
+    seqs = [arena.new_seq() for _ in range(BATCH)]
+    gen = torch.Generator(device=dev).manual_seed(SEED + rank)
+
+    # fill the contexts through the product path: one chunk step, append only
+    ntok = int(lens.sum())
+    kfill = torch.randn(ntok * N_KV * D, device=dev, generator=gen).half()
+    vfill = torch.randn(ntok * N_KV * D, device=dev, generator=gen).half()
+    arena.begin_step(seqs, [int(n) for n in lens])
+    for layer in range(LAYERS):
+        arena.append(layer, kfill, vfill)
+    torch.cuda.synchronize()
+    del kfill, vfill
+
+    q = [torch.randn(BATCH * N_Q * D, device=dev, generator=gen).half() for _ in range(LAYERS)]
+    k = [torch.randn(BATCH * N_KV * D, device=dev, generator=gen).half() for _ in range(LAYERS)]
+    v = [torch.randn(BATCH * N_KV * D, device=dev, generator=gen).half() for _ in range(LAYERS)]
+    out = [torch.empty_like(x) for x in q]
+    qh = [x.cpu().pin_memory() for x in q]
+    kh = [x.cpu().pin_memory() for x in k]
+    vh = [x.cpu().pin_memory() for x in v]
+    oh = [torch.empty_like(x).pin_memory() for x in qh]
+
+    lib = _lib.load()
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    hs = (C.c_void_p * BATCH)(*[s._h for s in seqs])
+    ones = (C.c_int64 * BATCH)(*([1] * BATCH))
+    ah = C.c_void_p(arena._h)
+    dargs = [(C.c_void_p(q[l].data_ptr()), C.c_void_p(k[l].data_ptr()), C.c_void_p(v[l].data_ptr()),
+              C.c_void_p(out[l].data_ptr())) for l in range(LAYERS)]
+    hargs = [(C.c_void_p(qh[l].data_ptr()), C.c_void_p(kh[l].data_ptr()), C.c_void_p(vh[l].data_ptr()),
+              C.c_void_p(oh[l].data_ptr())) for l in range(LAYERS)]
+    scale = C.c_double(SCALE)
+
+    def step_device():
+        _lib.check(lib.cbkv_begin_step(ah, hs, ones, None, BATCH, sp))
+        for l in range(LAYERS):
+            a = dargs[l]
+            rc = lib.cbkv_attention(ah, l, a[0], a[1], a[2], a[3], scale, 0, sp)
+            if rc:
+                _lib.check(rc)
+
+    def step_host():
+        _lib.check(lib.cbkv_begin_step(ah, hs, ones, None, BATCH, sp))
+        for l in range(LAYERS):
+            a = hargs[l]
+            rc = lib.cbkv_attention_host(ah, l, a[0], a[1], a[2], a[3], scale, 0, sp)
+            if rc:
+                _lib.check(rc)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        t1 = time.time()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, t0, t1
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = kv.launch_count()
+    ms, t0, t1 = timed(step_device, args.steps, args.warmup)
+    launches = kv.launch_count() - launches0
+    launches_timed = launches * args.steps // (args.steps + args.warmup)
+    clocks = sampler.summary(t0, t1) if rank == 0 else None
+    assert arena.device_status() == 0, "kernel status word set"
+    value = BATCH * world * args.steps / (ms * 1e-3)
+    lens_mid = lens + 1 + args.warmup + args.steps // 2
+    bytes_step = algorithmic_bytes_per_layer(lens_mid) * LAYERS
+
+    # roofline of the decode kernel: CUDA events around every launch, same steps again
+    arena.profile_enable(True)
+    for _ in range(args.steps):
+        step_device()
+    kms, kn = arena.profile_read()
+    arena.profile_enable(False)
+    lens_prof = lens + 1 + args.warmup + args.steps + args.steps // 2
+    bytes_launch = algorithmic_bytes_per_layer(lens_prof)
+    achieved = bytes_launch / (kms / kn * 1e-3) / 1e9
+
+    # end to end: host buffers in, host buffers out, every layer
+    ems, _, _ = timed(step_host, args.steps, args.warmup)
+    e2e_value = BATCH * world * args.steps / (ems * 1e-3)
+    h2d = LAYERS * (qh[0].numel() + kh[0].numel() + vh[0].numel()) * 2
+    d2h = LAYERS * oh[0].numel() * 2
+    assert arena.device_status() == 0
+    if rank == 0:
+        sampler.stop()
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured copy bandwidth (MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = time_cpu_port(8, 2, 12.0, context_lengths(0))
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "cfg2 qwen2.5-7b geometry batched decode: 28 layers, 28/4/128, batch 32 per GPU, "
+                               "ctx U[1024,4096], 8192-page arena, append + decode attention per layer",
+                   "l2": "inputs larger than L2 (about 4.7 GB of KV read per step)",
+                   "sharding": "by sequence, no collective"},
+        "hbm_gbs": bytes_step * world / (ms / args.steps * 1e-3) / 1e9,
+        "hbm_frac_of_8tbs": bytes_step / (ms / args.steps * 1e-3) / 8e12,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "decode_kernel<128,4,3,f16>", "us_per_launch": kms / kn * 1e3,
+                     "algorithmic_bytes_per_launch": bytes_launch, "peak_source": peak_src},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ems / args.steps},
+        "gpu_launches": launches_timed,
+        "clocks": clocks,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctas-per-sm", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

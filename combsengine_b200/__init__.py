@@ -1,0 +1,9 @@
+"""B200-native paged KV cache + attention: the KVCache path of CombsEngine.
+
+The compute lives in ``libcombskv.so`` (hand-written CUDA for sm_100a behind the C
+ABI of ``include/combs_kv.h``); this package is the host-side mirror of the
+reference's operator surface (``combs-models/src/kv.rs``).
+"""
+from .kv import (CacheConfig, CacheKind, KVArena, PagedKVCache, PagedSeq, PageStats, CbkvError)
+
+__all__ = ["CacheConfig", "CacheKind", "KVArena", "PagedKVCache", "PagedSeq", "PageStats", "CbkvError"]

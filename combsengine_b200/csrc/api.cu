@@ -1,0 +1,663 @@
+// extern "C" boundary (include/combs_kv.h) and the device-side state behind it:
+// lazily materialised per-layer arenas, TMA descriptors, per-step metadata upload,
+// kernel selection and launch.  The host bookkeeping itself is manager.cpp.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "kernels.hpp"
+#include "manager.hpp"
+
+using namespace cbkv;
+
+namespace {
+
+std::atomic<int64_t> g_launches{0};
+
+#define CU_TRY(expr)                                                                     \
+    do {                                                                                 \
+        cudaError_t e__ = (expr);                                                        \
+        if (e__ != cudaSuccess) {                                                        \
+            set_error(std::string(#expr) + ": " + cudaGetErrorString(e__));              \
+            return CBKV_ERR_CUDA;                                                        \
+        }                                                                                \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+constexpr int kSlots = 4;
+
+struct StepSlot {
+    uint8_t* host = nullptr;  // pinned
+    uint8_t* dev = nullptr;
+    size_t cap = 0, used = 0;
+    cudaEvent_t ev = nullptr;
+    bool pending = false;
+};
+
+struct DecodePlanDev {
+    DecodePlan host;
+    const int32_t *seg_unit_begin, *seg_page_lo, *seg_first_cta, *seg_nparts, *seg_part_base, *cta_unit_begin, *cta_first_seg;
+};
+
+struct DeviceState {
+    int device = 0;
+    int sm_count = 148;
+    bool fast = false;  // page 16, head_dim in {64,128,256}, n_rep <= 8: the TMA + mma kernels apply
+    size_t layer_bytes = 0;
+    std::vector<LayerArena> layers;
+    StepSlot slots[kSlots];
+    int cur = 0;
+    uint64_t uploaded_step = 0;
+    StepDev step{};
+    std::map<int64_t, DecodePlanDev> decode_plans;
+    bool chunk_plan_ok = false;
+    ChunkPlan chunk_host;
+    const int32_t* chunk_item_begin = nullptr;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    size_t part_cap = 0;
+    int32_t* seg_counter = nullptr;
+    size_t counter_cap = 0;
+    int32_t* status = nullptr;
+    int decode_ctas_per_sm = 0;
+    // host-buffer entry point staging
+    uint8_t* io = nullptr;
+    size_t io_cap = 0;
+    // profiling
+    bool profile = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof;
+    size_t prof_used = 0;
+};
+
+DeviceState* dev_of(Arena* a) { return static_cast<DeviceState*>(a->dev); }
+
+int32_t ensure_device(Arena* a) {
+    if (a->dev) {
+        CU_TRY(cudaSetDevice(dev_of(a)->device));
+        return CBKV_OK;
+    }
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        set_error(std::string("no CUDA device: this library has no CPU path (") + cudaGetErrorString(e) + ")");
+        return CBKV_ERR_CUDA;
+    }
+    CU_TRY(cudaSetDevice(a->cfg.device));
+    cudaDeviceProp prop;
+    CU_TRY(cudaGetDeviceProperties(&prop, a->cfg.device));
+    if (prop.major < 10) {
+        set_error("this library is built for sm_100a (B200) only; found sm_" + std::to_string(prop.major * 10 + prop.minor));
+        return CBKV_ERR_CUDA;
+    }
+    auto* d = new DeviceState();
+    d->device = a->cfg.device;
+    d->sm_count = prop.multiProcessorCount;
+    const int D = a->cfg.head_dim;
+    d->fast = a->cfg.page_size == 16 && (D == 64 || D == 128 || D == 256) && a->n_rep() <= 8;
+    if (!d->fast && D > 512) { delete d; set_error("head_dim > 512 is not supported"); return CBKV_ERR_ARG; }
+    d->layer_bytes = (size_t)a->num_pages * a->cfg.n_kv_heads * 2 * a->cfg.page_size * D * 2;
+    d->layers.resize((size_t)a->cfg.num_layers);
+    if (d->fast) {
+        cudaError_t ke = kernels_init();
+        if (ke != cudaSuccess) { delete d; set_error(std::string("kernels_init: ") + cudaGetErrorString(ke)); return CBKV_ERR_CUDA; }
+        if (!encode_fn()) { delete d; set_error("cuTensorMapEncodeTiled not available from the driver"); return CBKV_ERR_CUDA; }
+    }
+    cudaError_t se = cudaMalloc(&d->status, sizeof(int32_t));
+    if (se != cudaSuccess) { delete d; set_error(std::string("cudaMalloc: ") + cudaGetErrorString(se)); return CBKV_ERR_CUDA; }
+    cudaMemset(d->status, 0, sizeof(int32_t));
+    for (auto& s : d->slots) cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming);
+    a->dev = d;
+    return CBKV_OK;
+}
+
+int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
+    return CBKV_OK;
+}
+
+// Arenas appear on a layer's first write, zero-filled (kv.rs:695-713).
+int32_t materialize(Arena* a, int layer, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    LayerArena& L = d->layers[(size_t)layer];
+    if (L.base) return CBKV_OK;
+    CU_TRY(cudaMalloc(&L.base, d->layer_bytes));
+    CU_TRY(cudaMemsetAsync(L.base, 0, d->layer_bytes, st));
+    if (d->fast) {
+        uint64_t rows = (uint64_t)a->num_pages * a->cfg.n_kv_heads * 32;
+        if (rows >= (1ull << 32)) { set_error("arena too large for one tensor map"); return CBKV_ERR_ARG; }
+        bool bf16 = a->cfg.dtype == CBKV_BF16;
+        int32_t rc = encode_map(&L.map_kv, bf16, L.base, rows, a->cfg.head_dim, 32);
+        if (rc) return rc;
+        rc = encode_map(&L.map_k16, bf16, L.base, rows, a->cfg.head_dim, 16);
+        if (rc) return rc;
+    }
+    return CBKV_OK;
+}
+
+// Bump-allocate `bytes` in the current step slot, copy `src` there and enqueue the
+// upload; returns the device address.
+int32_t slot_upload(DeviceState* d, const void* src, size_t bytes, cudaStream_t st, const void** dev_out) {
+    StepSlot& s = d->slots[d->cur];
+    size_t off = (s.used + 255) & ~(size_t)255;
+    if (off + bytes > s.cap) {
+        // grow: nothing of this slot may still be in flight
+        CU_TRY(cudaStreamSynchronize(st));
+        size_t ncap = std::max<size_t>((off + bytes) * 2, 1 << 20);
+        uint8_t *nh = nullptr, *nd = nullptr;
+        CU_TRY(cudaMallocHost(&nh, ncap));
+        CU_TRY(cudaMalloc(&nd, ncap));
+        if (s.used) {
+            memcpy(nh, s.host, s.used);
+            CU_TRY(cudaMemcpy(nd, s.dev, s.used, cudaMemcpyDeviceToDevice));
+        }
+        // earlier uploads of this step keep their offsets; re-point what was handed out
+        ptrdiff_t delta = nd - s.dev;
+        if (s.dev) {
+            auto fix = [&](const void*& p) { if (p) p = (const uint8_t*)p + delta; };
+            const void* p;
+            p = d->step.seq_meta; fix(p); d->step.seq_meta = (const SeqMeta*)p;
+            p = d->step.tables; fix(p); d->step.tables = (const int32_t*)p;
+            for (auto& kv : d->decode_plans) {
+                DecodePlanDev& pd = kv.second;
+                const int32_t** arr[] = {&pd.seg_unit_begin, &pd.seg_page_lo, &pd.seg_first_cta, &pd.seg_nparts,
+                                         &pd.seg_part_base, &pd.cta_unit_begin, &pd.cta_first_seg};
+                for (auto pp : arr) { p = *pp; fix(p); *pp = (const int32_t*)p; }
+            }
+            p = d->chunk_item_begin; fix(p); d->chunk_item_begin = (const int32_t*)p;
+            cudaFreeHost(s.host);
+            cudaFree(s.dev);
+        }
+        s.host = nh; s.dev = nd; s.cap = ncap;
+    }
+    memcpy(s.host + off, src, bytes);
+    CU_TRY(cudaMemcpyAsync(s.dev + off, s.host + off, bytes, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaEventRecord(s.ev, st));
+    s.pending = true;
+    s.used = off + bytes;
+    *dev_out = s.dev + off;
+    return CBKV_OK;
+}
+
+int32_t upload_step(Arena* a, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    d->cur = (d->cur + 1) % kSlots;
+    StepSlot& s = d->slots[d->cur];
+    if (s.pending) { CU_TRY(cudaEventSynchronize(s.ev)); s.pending = false; }
+    s.used = 0;
+    d->decode_plans.clear();
+    d->chunk_plan_ok = false;
+    d->chunk_item_begin = nullptr;
+    d->step = StepDev{};
+    const void* p = nullptr;
+    int32_t rc = slot_upload(d, a->step_meta.data(), a->step_meta.size() * sizeof(SeqMeta), st, &p);
+    if (rc) return rc;
+    d->step.seq_meta = (const SeqMeta*)p;
+    rc = slot_upload(d, a->step_tables.data(), std::max<size_t>(1, a->step_tables.size()) * sizeof(int32_t), st, &p);
+    if (rc) return rc;
+    d->step.tables = (const int32_t*)p;
+    d->step.n_seqs = (int32_t)a->step_meta.size();
+    d->step.n_tokens = (int32_t)a->step_tokens;
+    d->uploaded_step = a->step_id;
+    return CBKV_OK;
+}
+
+GeomDev geom(const Arena* a) {
+    return GeomDev{a->cfg.n_q_heads, a->cfg.n_kv_heads, a->cfg.n_q_heads / a->cfg.n_kv_heads, a->cfg.head_dim,
+                   a->cfg.page_size, (int32_t)a->num_pages};
+}
+
+int32_t get_decode_plan(Arena* a, int64_t window, cudaStream_t st, DecodePlanDev** out) {
+    DeviceState* d = dev_of(a);
+    auto it = d->decode_plans.find(window);
+    if (it != d->decode_plans.end()) { *out = &it->second; return CBKV_OK; }
+    DecodeConfig dc = decode_config(a->cfg.head_dim);
+    int per_sm = d->decode_ctas_per_sm > 0 ? d->decode_ctas_per_sm : dc.ctas_per_sm;
+    DecodePlanDev pd{};
+    // at least one page per warp, at most one resident wave of CTAs
+    build_decode_plan(*a, window, d->sm_count * per_sm, &pd.host);
+    {
+        int want = std::max(1, (pd.host.n_units + dc.warps - 1) / dc.warps);
+        if (want < pd.host.n_ctas) build_decode_plan(*a, window, want, &pd.host);
+    }
+    std::vector<int32_t> flat;
+    auto push = [&](const std::vector<int32_t>& v) { size_t o = flat.size(); flat.insert(flat.end(), v.begin(), v.end()); return o; };
+    size_t o0 = push(pd.host.seg_unit_begin), o1 = push(pd.host.seg_page_lo), o2 = push(pd.host.seg_first_cta),
+           o3 = push(pd.host.seg_nparts), o4 = push(pd.host.seg_part_base), o5 = push(pd.host.cta_unit_begin),
+           o6 = push(pd.host.cta_first_seg);
+    const void* p = nullptr;
+    int32_t rc = slot_upload(d, flat.data(), flat.size() * sizeof(int32_t), st, &p);
+    if (rc) return rc;
+    const int32_t* base = (const int32_t*)p;
+    pd.seg_unit_begin = base + o0; pd.seg_page_lo = base + o1; pd.seg_first_cta = base + o2; pd.seg_nparts = base + o3;
+    pd.seg_part_base = base + o4; pd.cta_unit_begin = base + o5; pd.cta_first_seg = base + o6;
+    // scratch for partial results and the per-segment tickets
+    if ((size_t)pd.host.n_parts > d->part_cap) {
+        CU_TRY(cudaStreamSynchronize(st));
+        if (d->part_o) { cudaFree(d->part_o); cudaFree(d->part_ml); }
+        d->part_cap = std::max<size_t>((size_t)pd.host.n_parts * 2, 1024);
+        CU_TRY(cudaMalloc(&d->part_o, d->part_cap * 8 * a->cfg.head_dim * sizeof(float)));
+        CU_TRY(cudaMalloc(&d->part_ml, d->part_cap * 16 * sizeof(float)));
+    }
+    if ((size_t)pd.host.n_segs > d->counter_cap) {
+        CU_TRY(cudaStreamSynchronize(st));
+        if (d->seg_counter) cudaFree(d->seg_counter);
+        d->counter_cap = std::max<size_t>((size_t)pd.host.n_segs * 2, 1024);
+        CU_TRY(cudaMalloc(&d->seg_counter, d->counter_cap * sizeof(int32_t)));
+        CU_TRY(cudaMemsetAsync(d->seg_counter, 0, d->counter_cap * sizeof(int32_t), st));
+    }
+    auto ins = d->decode_plans.emplace(window, std::move(pd));
+    *out = &ins.first->second;
+    return CBKV_OK;
+}
+
+int32_t get_chunk_plan(Arena* a, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    if (d->chunk_plan_ok) return CBKV_OK;
+    build_chunk_plan(*a, chunk_config(a->cfg.head_dim).cols_per_item, &d->chunk_host);
+    const void* p = nullptr;
+    int32_t rc = slot_upload(d, d->chunk_host.item_begin.data(), d->chunk_host.item_begin.size() * sizeof(int32_t), st, &p);
+    if (rc) return rc;
+    d->chunk_item_begin = (const int32_t*)p;
+    d->chunk_plan_ok = true;
+    return CBKV_OK;
+}
+
+struct ProfScope {
+    DeviceState* d;
+    cudaStream_t st;
+    size_t idx = 0;
+    bool on;
+    ProfScope(DeviceState* d_, cudaStream_t s) : d(d_), st(s), on(d_->profile) {
+        if (!on) return;
+        if (d->prof_used == d->prof.size()) {
+            cudaEvent_t a, b;
+            cudaEventCreate(&a); cudaEventCreate(&b);
+            d->prof.emplace_back(a, b);
+        }
+        idx = d->prof_used++;
+        cudaEventRecord(d->prof[idx].first, st);
+    }
+    ~ProfScope() { if (on) cudaEventRecord(d->prof[idx].second, st); }
+};
+
+int32_t check_step(Arena* a, int32_t layer) {
+    if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
+    if (layer < 0 || layer >= a->cfg.num_layers) { set_error("layer out of range"); return CBKV_ERR_ARG; }
+    if (!a->step_open || !a->dev || dev_of(a)->uploaded_step != a->step_id) {
+        set_error("no step begun (call cbkv_begin_step first)"); return CBKV_ERR_STATE;
+    }
+    return CBKV_OK;
+}
+
+int32_t run_append(Arena* a, int layer, const void* k, const void* v, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    AppendArgs args{d->step, geom(a), k, v, d->layers[(size_t)layer].base, d->status};
+    CU_TRY(launch_append(args, a->cfg.dtype == CBKV_BF16, st));
+    g_launches++;
+    return CBKV_OK;
+}
+
+// k, v non-null on a decode step => the append rides inside the decode kernel.
+int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, const void* v_fused, void* out,
+                      double scale, int64_t window, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    const bool bf16 = a->cfg.dtype == CBKV_BF16;
+    const int64_t w = a->layer_window(layer, window);
+    if (w != 0 && w < 2) { set_error("sliding window must be >= 2, got " + std::to_string(w)); return CBKV_ERR_ARG; }
+    LayerArena& L = d->layers[(size_t)layer];
+    const float scale_log2 = (float)(scale * 1.4426950408889634);
+    if (d->fast && a->step_is_decode) {
+        DecodePlanDev* pd = nullptr;
+        int32_t rc = get_decode_plan(a, w, st, &pd);
+        if (rc) return rc;
+        DecodeArgs args{};
+        args.step = d->step; args.geo = geom(a);
+        args.seg_unit_begin = pd->seg_unit_begin; args.seg_page_lo = pd->seg_page_lo; args.seg_first_cta = pd->seg_first_cta;
+        args.seg_nparts = pd->seg_nparts; args.seg_part_base = pd->seg_part_base; args.cta_unit_begin = pd->cta_unit_begin;
+        args.cta_first_seg = pd->cta_first_seg; args.n_segs = pd->host.n_segs;
+        args.q = q; args.out = out; args.k_new = k_fused; args.v_new = v_fused; args.arena = L.base;
+        args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
+        args.window = (int32_t)w; args.scale_log2 = scale_log2;
+        ProfScope ps(d, st);
+        CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, bf16, st));
+        g_launches++;
+        return CBKV_OK;
+    }
+    if (d->fast) {
+        int32_t rc = get_chunk_plan(a, st);
+        if (rc) return rc;
+        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2};
+        ProfScope ps(d, st);
+        CU_TRY(launch_chunk(L.map_kv, args, bf16, st));
+        g_launches++;
+        return CBKV_OK;
+    }
+    GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
+    ProfScope ps(d, st);
+    CU_TRY(launch_generic(args, bf16, st));
+    g_launches++;
+    return CBKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* cbkv_last_error(void) { return last_error(); }
+
+int32_t cbkv_arena_create(const cbkv_config* cfg, cbkv_arena** out) {
+    Arena* a = nullptr;
+    int32_t rc = arena_create(cfg, &a);
+    if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_arena*>(a);
+    return rc;
+}
+
+int32_t cbkv_arena_destroy(cbkv_arena* arena) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a) return CBKV_OK;
+    if (a->dev) {
+        DeviceState* d = dev_of(a);
+        cudaSetDevice(d->device);
+        cudaDeviceSynchronize();
+        for (auto& L : d->layers) if (L.base) cudaFree(L.base);
+        for (auto& s : d->slots) { if (s.host) cudaFreeHost(s.host); if (s.dev) cudaFree(s.dev); if (s.ev) cudaEventDestroy(s.ev); }
+        if (d->part_o) { cudaFree(d->part_o); cudaFree(d->part_ml); }
+        if (d->seg_counter) cudaFree(d->seg_counter);
+        if (d->status) cudaFree(d->status);
+        if (d->io) cudaFree(d->io);
+        for (auto& p : d->prof) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
+        delete d;
+    }
+    while (!a->seqs.empty()) seq_destroy(a->seqs.back());
+    delete a;
+    return CBKV_OK;
+}
+
+int32_t cbkv_set_free_list(cbkv_arena* arena, const int64_t* ids, int64_t n) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !ids) { set_error("null argument"); return CBKV_ERR_ARG; }
+    if (!a->alloc.set_initial(ids, n)) {
+        set_error("set_free_list needs a full permutation of the page ids on an unused arena");
+        return CBKV_ERR_ARG;
+    }
+    return CBKV_OK;
+}
+
+int32_t cbkv_seq_create(cbkv_arena* arena, cbkv_seq** out) {
+    Seq* s = nullptr;
+    int32_t rc = seq_create(reinterpret_cast<Arena*>(arena), &s);
+    if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_seq*>(s);
+    return rc;
+}
+int32_t cbkv_seq_destroy(cbkv_seq* seq) { return seq_destroy(reinterpret_cast<Seq*>(seq)); }
+
+int32_t cbkv_seq_fork_prefix(cbkv_seq* parent, int64_t n_tokens, cbkv_seq** out) {
+    Seq* c = nullptr;
+    int32_t rc = seq_fork_prefix(reinterpret_cast<Seq*>(parent), n_tokens, &c);
+    if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_seq*>(c);
+    return rc;
+}
+
+int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens, const int64_t* pos,
+                        int32_t n_seqs, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
+    // The device must be reachable before any state is advanced: there is no CPU path.
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    rc = begin_step(a, reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs);
+    if (rc) return rc;
+    return upload_step(a, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void* v, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (!k || !v) { set_error("null k/v"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU_TRY(cudaSetDevice(dev_of(a)->device));
+    if ((rc = materialize(a, layer, st))) return rc;
+    return run_append(a, layer, k, v, st);
+}
+
+int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, void* out, double scale, int64_t window,
+                             void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (!q || !out) { set_error("null q/out"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU_TRY(cudaSetDevice(dev_of(a)->device));
+    if ((rc = materialize(a, layer, st))) return rc;
+    return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
+}
+
+int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const void* k, const void* v, void* out,
+                       double scale, int64_t window, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (!q || !k || !v || !out) { set_error("null tensor"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    if ((rc = materialize(a, layer, st))) return rc;
+    if (d->fast && a->step_is_decode) return run_attention(a, layer, q, k, v, out, scale, window, st);
+    if ((rc = run_append(a, layer, k, v, st))) return rc;
+    return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
+}
+
+int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
+                            const void* v_host, void* out_host, double scale, int64_t window, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (!q_host || !k_host || !v_host || !out_host) { set_error("null tensor"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    const size_t qb = (size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2;
+    const size_t kb = (size_t)a->step_tokens * a->cfg.n_kv_heads * a->cfg.head_dim * 2;
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t need = 2 * up(qb) + 2 * up(kb);
+    if (need > d->io_cap) {
+        CU_TRY(cudaStreamSynchronize(st));
+        if (d->io) cudaFree(d->io);
+        d->io_cap = need * 2;
+        CU_TRY(cudaMalloc(&d->io, d->io_cap));
+    }
+    uint8_t* qd = d->io;
+    uint8_t* od = qd + up(qb);
+    uint8_t* kd = od + up(qb);
+    uint8_t* vd = kd + up(kb);
+    CU_TRY(cudaMemcpyAsync(qd, q_host, qb, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(kd, k_host, kb, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(vd, v_host, kb, cudaMemcpyHostToDevice, st));
+    rc = cbkv_attention(arena, layer, qd, kd, vd, od, scale, window, stream);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(out_host, od, qb, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return CBKV_OK;
+}
+
+int32_t cbkv_host_alloc(size_t bytes, void** out) {
+    if (!out) { set_error("null argument"); return CBKV_ERR_ARG; }
+    CU_TRY(cudaMallocHost(out, bytes));
+    return CBKV_OK;
+}
+int32_t cbkv_host_free(void* p) {
+    if (p) CU_TRY(cudaFreeHost(p));
+    return CBKV_OK;
+}
+
+int32_t cbkv_popn(cbkv_seq* seq, int64_t n, int64_t* popped) { return popn(reinterpret_cast<Seq*>(seq), n, popped); }
+int32_t cbkv_reset(cbkv_seq* seq) { return reset(reinterpret_cast<Seq*>(seq)); }
+int64_t cbkv_seq_len(const cbkv_seq* seq) { return reinterpret_cast<const Seq*>(seq)->seq_len; }
+int64_t cbkv_pages_used(const cbkv_seq* seq) { return (int64_t)reinterpret_cast<const Seq*>(seq)->table.size(); }
+int64_t cbkv_num_free_pages(const cbkv_arena* arena) { return reinterpret_cast<const Arena*>(arena)->alloc.num_free(); }
+
+int32_t cbkv_page_stats(const cbkv_seq* seq, cbkv_page_stats_t* out) {
+    const Seq* s = reinterpret_cast<const Seq*>(seq);
+    if (!s || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
+    int64_t mat = 0;
+    if (s->arena->dev)
+        for (auto& L : static_cast<DeviceState*>(s->arena->dev)->layers) if (L.base) mat++;
+    page_stats(s, mat, out);
+    return CBKV_OK;
+}
+
+int64_t cbkv_page_bytes(const cbkv_arena* arena) {
+    const Arena* a = reinterpret_cast<const Arena*>(arena);
+    return (int64_t)a->cfg.page_size * a->cfg.n_kv_heads * a->cfg.head_dim * 2 * 2 * a->cfg.num_layers;
+}
+
+int64_t cbkv_export_block_table(const cbkv_seq* seq, int64_t* out, int64_t cap) {
+    const Seq* s = reinterpret_cast<const Seq*>(seq);
+    for (int64_t i = 0; i < (int64_t)s->table.size() && i < cap; i++) out[i] = s->table[(size_t)i];
+    return (int64_t)s->table.size();
+}
+
+int64_t cbkv_export_free_list(const cbkv_arena* arena, int64_t* out, int64_t cap) {
+    const auto& st = reinterpret_cast<const Arena*>(arena)->alloc.stack();
+    for (int64_t i = 0; i < (int64_t)st.size() && i < cap; i++) out[i] = st[(size_t)i];
+    return (int64_t)st.size();
+}
+
+int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k_out_host, void* v_out_host, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !k_out_host || !v_out_host) { set_error("null argument"); return CBKV_ERR_ARG; }
+    if (layer < 0 || layer >= a->cfg.num_layers || page < 0 || page >= a->num_pages) { set_error("layer or page out of range"); return CBKV_ERR_ARG; }
+    const size_t tile = (size_t)a->cfg.page_size * a->cfg.head_dim * 2;  // one head's K (or V) rows, bytes
+    const int H = a->cfg.n_kv_heads;
+    if (!a->dev || !dev_of(a)->layers[(size_t)layer].base) {
+        memset(k_out_host, 0, tile * H);
+        memset(v_out_host, 0, tile * H);
+        return CBKV_OK;
+    }
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    CU_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    std::vector<uint8_t> buf(tile * 2 * H);
+    CU_TRY(cudaMemcpy(buf.data(), (uint8_t*)d->layers[(size_t)layer].base + (size_t)page * tile * 2 * H, buf.size(),
+                      cudaMemcpyDeviceToHost));
+    for (int h = 0; h < H; h++) {  // [h][K|V][slot][d] -> K [h][slot][d], V [h][slot][d]
+        memcpy((uint8_t*)k_out_host + h * tile, buf.data() + (size_t)(2 * h) * tile, tile);
+        memcpy((uint8_t*)v_out_host + h * tile, buf.data() + (size_t)(2 * h + 1) * tile, tile);
+    }
+    return CBKV_OK;
+}
+
+int32_t cbkv_page_refcount(const cbkv_arena* arena, int64_t page) {
+    const Arena* a = reinterpret_cast<const Arena*>(arena);
+    if (page < 0 || page >= a->num_pages) return -1;
+    return a->refcnt[(size_t)page];
+}
+
+int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !status) { set_error("null argument"); return CBKV_ERR_ARG; }
+    *status = 0;
+    if (!a->dev) return CBKV_OK;
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    CU_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    CU_TRY(cudaMemcpy(status, d->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (*status) {
+        CU_TRY(cudaMemset(d->status, 0, sizeof(int32_t)));
+        if (d->seg_counter) CU_TRY(cudaMemset(d->seg_counter, 0, d->counter_cap * sizeof(int32_t)));
+        set_error("kernel status word = " + std::to_string(*status));
+        return CBKV_ERR_DEVICE;
+    }
+    return CBKV_OK;
+}
+
+int64_t cbkv_launch_count(void) { return g_launches.load(); }
+
+int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    dev_of(a)->profile = on != 0;
+    dev_of(a)->prof_used = 0;
+    return CBKV_OK;
+}
+
+int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !a->dev || !total_ms || !launches) { set_error("null argument"); return CBKV_ERR_ARG; }
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    CU_TRY(cudaDeviceSynchronize());
+    double sum = 0;
+    for (size_t i = 0; i < d->prof_used; i++) {
+        float ms = 0;
+        CU_TRY(cudaEventElapsedTime(&ms, d->prof[i].first, d->prof[i].second));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = (int64_t)d->prof_used;
+    d->prof_used = 0;
+    return CBKV_OK;
+}
+
+int32_t cbkv_set_decode_ctas_per_sm(cbkv_arena* arena, int32_t n) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || n < 0 || n > 8) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    dev_of(a)->decode_ctas_per_sm = n;
+    return CBKV_OK;
+}
+
+// Host-only view of the decode work split for the step in flight (used by the CPU
+// tests of the partition): out = [n_ctas, n_segs, n_units, n_parts, cta_unit_begin...,
+// seg_unit_begin..., seg_page_lo..., seg_first_cta..., seg_nparts..., seg_part_base..., cta_first_seg...].
+int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t* out, int64_t cap) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || a->step_meta.empty()) return -1;
+    DecodePlan pl;
+    build_decode_plan(*a, window, n_ctas, &pl);
+    std::vector<int32_t> flat = {pl.n_ctas, pl.n_segs, pl.n_units, pl.n_parts};
+    for (auto* v : {&pl.cta_unit_begin, &pl.seg_unit_begin, &pl.seg_page_lo, &pl.seg_first_cta, &pl.seg_nparts,
+                    &pl.seg_part_base, &pl.cta_first_seg})
+        flat.insert(flat.end(), v->begin(), v->end());
+    for (int64_t i = 0; i < (int64_t)flat.size() && i < cap; i++) out[i] = flat[(size_t)i];
+    return (int64_t)flat.size();
+}
+
+// Host-only bookkeeping of a step without touching a device (CPU tests of the manager).
+int32_t cbkv_debug_begin_step_host(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
+                                   const int64_t* pos, int32_t n_seqs) {
+    return begin_step(reinterpret_cast<Arena*>(arena), reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs);
+}
+
+}  // extern "C"

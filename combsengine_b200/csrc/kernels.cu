@@ -1,0 +1,759 @@
+// CUDA kernels of the paged KV path, written for sm_100a.
+//
+//   append_kernel   scatter of a step's new K/V rows into page slots
+//                   (reference: the slice_assign loop, kv.rs:721-734)
+//   decode_kernel   GQA decode attention read in place from the pages, with the
+//                   append fused in: no gather copy (kv.rs:611-636), no repeat_kv
+//                   (kv.rs:177-187), no f32 upcast pass (kv.rs:213-215)
+//   chunk_kernel    attention of a chunk of new tokens over paged prefix + chunk
+//                   (causal, bottom-right aligned, optional window; kv.rs:243-268)
+//   generic_kernel  any page size / head_dim; one warp per query row
+//
+// Layout of one layer in HBM: pages [num_pages][n_kv][2][16][d] (f16/bf16).  One
+// (page, kv head) is 32 consecutive rows of d elements: its K tile then its V tile.
+// A tile reaches shared memory through one TMA box per 64-element column block
+// (32 rows x 128 B, 128-byte swizzle), so ldmatrix reads are bank-conflict free.
+//
+// Math per tile (16 tokens) in a warp, all in registers:
+//   S^T[16 tok x 8 col] = K[16 x d] . Q^T[d x 8 col]      mma.m16n8k16, f32 accumulate
+//   online softmax over tokens: warp shuffles across the 8 row groups
+//   O^T[d x 8 col]     += V^T[d x 16 tok] . P^T[16 tok x 8 col]
+// A "column" is one (query token, q head of the kv group): for decode the 8 columns
+// are the q heads that share the kv head, so K/V are read once for the whole group.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "kernels.hpp"
+
+namespace cbkv {
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait: gives up after `limit_ns` of wall time and returns false (the caller
+// records it in the status word and stops consuming; nothing spins forever).
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns = 100000000ull) {
+    for (int i = 0; i < 64; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    while (!mbar_try_wait(bar, parity))
+        if (global_ns() - t0 > limit_ns) return false;
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+template <bool BF16>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (BF16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t to_elem(float x) {
+    if constexpr (BF16) { __nv_bfloat16 v = __float2bfloat16_rn(x); return *reinterpret_cast<uint16_t*>(&v); }
+    else { __half v = __float2half_rn(x); return *reinterpret_cast<uint16_t*>(&v); }
+}
+template <bool BF16>
+__device__ __forceinline__ float from_elem(uint16_t x) {
+    if constexpr (BF16) { return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&x)); }
+    else { return __half2float(*reinterpret_cast<__half*>(&x)); }
+}
+
+// Byte offset of (row, 16-byte chunk j) inside one swizzled 32-row x 128-byte block.
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t j) { return row * 128u + ((j ^ (row & 7u)) << 4); }
+
+// One 16-token tile against NT blocks of 8 query columns.
+//   stage        shared address of the K|V tile ([D/64] blocks of 32 rows x 128 B)
+//   qf           Q^T fragments (B operand), loaded once per work item
+//   kpos0        absolute position of the tile's first token
+//   qpos         absolute query position of this thread's two columns per block
+template <int D, int NT, bool BF16>
+__device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)[NT][D / 16][2],
+                                            float (&o)[NT][D / 16][4], float (&m)[NT][2], float (&l)[NT][2],
+                                            int kpos0, const int (&qpos)[NT][2], int window, float scale_log2,
+                                            bool need_mask, int lane) {
+    const int g = lane >> 2;
+    float s[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+    // ---- S^T = K . Q^T
+    {
+        const uint32_t row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row of this lane's ldmatrix address
+        const uint32_t jsel = lane >> 4;                           // which of the two 16-byte chunks
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+            uint32_t a[4];
+            ldsm_x4(stage + (ks >> 2) * 4096u + swz(row, (ks & 3) * 2 + jsel), a);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma_16816<BF16>(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+        }
+    }
+    // ---- online softmax over the tile's 16 tokens (rows g and g+8 of the fragment)
+    uint32_t pb[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) s[nt][i] *= scale_log2;
+        if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                int kp = kpos0 + g + (i >> 1) * 8;
+                int qp = qpos[nt][i & 1];
+                bool ok = kp <= qp && (window <= 0 || kp + window > qp);  // keys in (p - w, p], kv.rs:252-257
+                if (!ok) s[nt][i] = -INFINITY;
+            }
+        }
+        float alpha[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float mx = fmaxf(s[nt][j], s[nt][j + 2]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            float m_new = fmaxf(m[nt][j], mx);
+            float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[j] = exp2f(m[nt][j] - m_use);
+            m[nt][j] = m_new;
+            float p0 = exp2f(s[nt][j] - m_use);
+            float p1 = exp2f(s[nt][j + 2] - m_use);
+            s[nt][j] = p0;
+            s[nt][j + 2] = p1;
+            l[nt][j] = l[nt][j] * alpha[j] + p0 + p1;  // this thread's share; reduced over row groups at the end
+        }
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            o[nt][mt][0] *= alpha[0]; o[nt][mt][1] *= alpha[1];
+            o[nt][mt][2] *= alpha[0]; o[nt][mt][3] *= alpha[1];
+        }
+        // P^T as the B operand: transpose the two 8x8 blocks across the warp
+        pb[nt][0] = movmatrix_trans(pack2<BF16>(s[nt][0], s[nt][1]));
+        pb[nt][1] = movmatrix_trans(pack2<BF16>(s[nt][2], s[nt][3]));
+    }
+    // ---- O^T += V^T . P^T   (V rows are 16..31 of the block)
+    {
+        const uint32_t row = 16 + (lane & 7) + (lane >> 4) * 8;  // token row
+        const uint32_t jsel = (lane >> 3) & 1;                   // d chunk
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            uint32_t a[4];
+            ldsm_x4_trans(stage + (mt >> 2) * 4096u + swz(row, (mt & 3) * 2 + jsel), a);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma_16816<BF16>(o[nt][mt], a, pb[nt][0], pb[nt][1]);
+        }
+    }
+}
+
+// Issue the TMA copies for one (page, kv head) tile: D/64 boxes of 32 rows x 64 elems.
+template <int D>
+__device__ __forceinline__ void issue_tile(const CUtensorMap* map, uint32_t stage, uint32_t bar, int row0) {
+    mbar_expect_tx(bar, 32u * D * 2u);
+#pragma unroll
+    for (int x = 0; x < D / 64; x++) tma_load_2d(stage + x * 4096u, map, x * 64, row0, bar);
+}
+
+// ------------------------------------------------------------------ append
+template <typename T>
+__global__ void append_kernel(const AppendArgs a) {
+    const int D8 = a.geo.d / 8;
+    const int64_t total = (int64_t)a.step.n_tokens * a.geo.n_kv * 2 * D8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(idx % D8);
+        int64_t rem = idx / D8;
+        int kv = (int)(rem & 1);
+        int64_t row = rem >> 1;  // packed row: sequence blocks of [n_kv][snew] rows
+        int lo = 0, hi = a.step.n_seqs - 1;  // last sequence whose first row is <= row
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if ((int64_t)a.step.seq_meta[mid].tok_off * a.geo.n_kv <= row) lo = mid; else hi = mid - 1;
+        }
+        const SeqMeta sm = a.step.seq_meta[lo];
+        int64_t local = row - (int64_t)sm.tok_off * a.geo.n_kv;
+        int h = (int)(local / sm.snew), r = (int)(local % sm.snew);
+        int gpos = sm.pos + r;                         // global = pos + written, kv.rs:725
+        int phys = a.step.tables[sm.tbl_off + gpos / a.geo.page_size];  // kv.rs:728
+        int slot = gpos % a.geo.page_size;             // kv.rs:726
+        if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); continue; }
+        const uint4* src = reinterpret_cast<const uint4*>(kv ? a.v : a.k) + row * D8 + c;
+        int64_t drow = (((int64_t)phys * a.geo.n_kv + h) * 2 + kv) * a.geo.page_size + slot;
+        reinterpret_cast<uint4*>(a.arena)[drow * D8 + c] = *src;
+    }
+}
+
+// ------------------------------------------------------------------ decode
+// Each CTA owns a contiguous range of (sequence, kv head, page) units; a range may
+// cover the tail of one segment, whole segments and the head of another ("pieces").
+// Warps of the CTA take the pages of a piece round-robin, each through its own ring
+// of TMA stages, and their running (max, sum, numerator) states are merged in shared
+// memory when the piece ends.  A segment cut across CTAs leaves partials in global
+// scratch; the CTA that finishes last (atomic ticket, no waiting) merges them.
+struct UnitCursor {
+    int seg, pb, pe, u;
+};
+
+template <int D, int W, int S, bool BF16>
+__global__ void __launch_bounds__(W * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
+    constexpr uint32_t UNIT = 32u * D * 2u;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    float* comb_o = reinterpret_cast<float*>(smem + (size_t)W * S * UNIT);  // [W][8][D]
+    float* comb_ml = comb_o + W * 8 * D;                                     // [W][8][2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(comb_ml + W * 16);          // [W][S]
+    int* flag = reinterpret_cast<int*>(bars + W * S);
+
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int cta = blockIdx.x;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
+        return;
+    }
+    const int u0 = a.cta_unit_begin[cta], u1 = a.cta_unit_begin[cta + 1];
+    if (u0 >= u1) return;
+
+    const uint32_t ring = smem_u32(smem) + (uint32_t)w * S * UNIT;
+    const uint32_t bar0 = smem_u32(bars + w * S);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < S; i++) mbar_init(bar0 + i * 8, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    const int Hkv = a.geo.n_kv, n_rep = a.geo.n_rep;
+    const int first_seg = a.cta_first_seg[cta];
+
+    // producer cursor: walks this warp's units across pieces, S tiles ahead of the math
+    UnitCursor pc;
+    pc.seg = first_seg; pc.pb = u0; pc.pe = min(u1, a.seg_unit_begin[first_seg + 1]); pc.u = u0 + w;
+    auto normalize = [&](UnitCursor& c) {
+        while (c.u >= c.pe && c.pe < u1) {
+            c.seg++; c.pb = c.pe; c.pe = min(u1, a.seg_unit_begin[c.seg + 1]); c.u = c.pb + w;
+        }
+    };
+    bool failed = false;
+    int fail_at = 0;
+    auto issue = [&](UnitCursor& c, int stage_idx) {
+        // lane 0 resolves the unit's physical page through the block table and issues the copy
+        if (lane == 0) {
+            int b = c.seg / Hkv, h = c.seg - b * Hkv;
+            int lp = a.seg_page_lo[c.seg] + (c.u - a.seg_unit_begin[c.seg]);
+            int phys = a.step.tables[a.step.seq_meta[b].tbl_off + lp];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            issue_tile<D>(&tmap, ring + stage_idx * UNIT, bar0 + stage_idx * 8, (phys * Hkv + h) * 32);
+        }
+    };
+    normalize(pc);
+    int issued = 0, consumed = 0;
+#pragma unroll 1
+    for (int i = 0; i < S; i++) {
+        if (pc.u < pc.pe) { issue(pc, i); issued++; pc.u += W; normalize(pc); }
+    }
+
+    int seg = first_seg, pb = u0;
+#pragma unroll 1
+    while (pb < u1) {
+        const int sb = a.seg_unit_begin[seg];
+        const int pe = min(u1, a.seg_unit_begin[seg + 1]);
+        const int b = seg / Hkv, h = seg - b * Hkv;
+        const SeqMeta sm = a.step.seq_meta[b];
+        const int q_pos = sm.pos + sm.snew - 1;  // decode: the one new token, at the end of the window
+        const int page_lo = a.seg_page_lo[seg];
+        const int page_last = q_pos >> 4;
+        const size_t blk = (size_t)sm.tok_off;   // packed token offset of this sequence (snew == 1)
+
+        // Q^T fragments of the kv group's q heads (columns >= n_rep are zero)
+        uint32_t qf[1][D / 16][2];
+        {
+            const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+                reinterpret_cast<const uint16_t*>(a.q) + (blk * a.geo.n_q + (size_t)h * n_rep + g) * D);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks++) {
+                qf[0][ks][0] = g < n_rep ? __ldg(qrow + ks * 8 + t) : 0u;
+                qf[0][ks][1] = g < n_rep ? __ldg(qrow + ks * 8 + 4 + t) : 0u;
+            }
+        }
+        float o[1][D / 16][4], m[1][2] = {{-INFINITY, -INFINITY}}, l[1][2] = {{0.f, 0.f}};
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) { o[0][mt][0] = o[0][mt][1] = o[0][mt][2] = o[0][mt][3] = 0.f; }
+        const int qpos[1][2] = {{q_pos, q_pos}};
+
+#pragma unroll 1
+        for (int u = pb + w; u < pe; u += W) {
+            const int st = consumed % S;
+            const uint32_t stage = ring + st * UNIT;
+            if (!failed && !mbar_wait_bounded(bar0 + st * 8, (consumed / S) & 1)) {
+                failed = true;
+                fail_at = consumed;
+                atomicOr(a.status, ST_WAIT_TIMEOUT);
+            }
+            const int lp = page_lo + (u - sb);
+            if (!failed) {
+                if (a.k_new != nullptr && lp == page_last) {
+                    // fused append: put the new K/V row into the tile just fetched and into its page
+                    const int slot = q_pos & 15;
+                    const int phys = a.step.tables[sm.tbl_off + lp];
+                    for (int c = lane; c < 2 * (D / 8); c += 32) {
+                        int kv = c / (D / 8), j = c - kv * (D / 8);
+                        const uint4 val = *(reinterpret_cast<const uint4*>(kv ? a.v_new : a.k_new) +
+                                            (blk * Hkv + h) * (D / 8) + j);
+                        uint32_t row = kv * 16 + slot;
+                        uint32_t addr = stage + (j >> 3) * 4096u + swz(row, j & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+                        if (phys >= 0 && phys < a.geo.num_pages) {
+                            size_t drow = (((size_t)phys * Hkv + h) * 2 + kv) * 16 + slot;
+                            reinterpret_cast<uint4*>(a.arena)[drow * (D / 8) + j] = val;
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                }
+                const bool need_mask = (lp * 16 + 15 > q_pos) || (a.window > 0 && lp * 16 + a.window <= q_pos);
+                attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+            }
+            __syncwarp();
+            consumed++;
+            if (pc.u < pc.pe) { if (!failed) { issue(pc, st); issued++; } pc.u += W; normalize(pc); }
+        }
+
+        // ---- merge the warps' states for this piece
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 4);
+            l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 8);
+            l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 16);
+        }
+        float* co = comb_o + (size_t)w * 8 * D;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            co[(2 * t) * D + mt * 16 + g] = o[0][mt][0];
+            co[(2 * t + 1) * D + mt * 16 + g] = o[0][mt][1];
+            co[(2 * t) * D + mt * 16 + g + 8] = o[0][mt][2];
+            co[(2 * t + 1) * D + mt * 16 + g + 8] = o[0][mt][3];
+        }
+        if (g == 0) {
+            comb_ml[(w * 8 + 2 * t) * 2 + 0] = m[0][0]; comb_ml[(w * 8 + 2 * t) * 2 + 1] = l[0][0];
+            comb_ml[(w * 8 + 2 * t + 1) * 2 + 0] = m[0][1]; comb_ml[(w * 8 + 2 * t + 1) * 2 + 1] = l[0][1];
+        }
+        __syncthreads();
+        const int nparts = a.seg_nparts[seg];
+        const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + (blk * a.geo.n_q + (size_t)h * n_rep) * D;
+        for (int idx = tid; idx < n_rep * D; idx += W * 32) {
+            int col = idx / D, j = idx - col * D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int ww = 0; ww < W; ww++) M = fmaxf(M, comb_ml[(ww * 8 + col) * 2]);
+            float acc = 0.f, ls = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < W; ww++) {
+                float mw = comb_ml[(ww * 8 + col) * 2];
+                float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+                acc += f * comb_o[((size_t)ww * 8 + col) * D + j];
+                ls += f * comb_ml[(ww * 8 + col) * 2 + 1];
+            }
+            if (nparts == 1) {
+                out_row[idx] = to_elem<BF16>(acc / ls);
+            } else {
+                a.part_o[((size_t)slot * 8 + col) * D + j] = acc;
+                if (j == 0) { a.part_ml[((size_t)slot * 8 + col) * 2] = M; a.part_ml[((size_t)slot * 8 + col) * 2 + 1] = ls; }
+            }
+        }
+        if (nparts > 1) {
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                int ticket = atomicAdd(a.seg_counter + seg, 1);
+                *flag = (ticket == nparts - 1);
+                if (ticket == nparts - 1) a.seg_counter[seg] = 0;  // ready for the next launch
+            }
+            __syncthreads();
+            if (*flag) {
+                __threadfence();
+                const int base = a.seg_part_base[seg];
+                for (int idx = tid; idx < n_rep * D; idx += W * 32) {
+                    int col = idx / D, j = idx - col * D;
+                    float M = -INFINITY;
+                    for (int p = 0; p < nparts; p++) M = fmaxf(M, __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2));
+                    float acc = 0.f, ls = 0.f;
+                    for (int p = 0; p < nparts; p++) {
+                        float mp = __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2);
+                        float f = (mp == -INFINITY) ? 0.f : exp2f(mp - M);
+                        acc += f * __ldcg(a.part_o + ((size_t)(base + p) * 8 + col) * D + j);
+                        ls += f * __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2 + 1);
+                    }
+                    out_row[idx] = to_elem<BF16>(acc / ls);
+                }
+            }
+        }
+        __syncthreads();  // comb buffers and flag are reused by the next piece
+        seg++;
+        pb = pe;
+    }
+    // a warp that gave up still waits (bounded) for the copies it has in flight
+    if (failed) {
+        for (int i = fail_at; i < issued; i++) mbar_wait_bounded(bar0 + (i % S) * 8, (i / S) & 1, 20000000ull);
+    }
+}
+
+// ------------------------------------------------------------------ chunk (prefill)
+// One warp per item = (sequence, kv head, block of 8*NT query columns); column c of a
+// sequence is (new token c / n_rep, q head c % n_rep of the kv group).  Every warp
+// streams the pages its columns can see through its own TMA ring.
+template <int D, int NT, int W, int S, bool BF16>
+__global__ void __launch_bounds__(W * 32) chunk_kernel(const __grid_constant__ CUtensorMap tmap, const ChunkArgs a) {
+    constexpr uint32_t UNIT = 32u * D * 2u;
+    constexpr int CPI = 8 * NT;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)W * S * UNIT);
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
+        return;
+    }
+    const int item = blockIdx.x * W + w;
+    if (item >= a.n_items) return;
+    const uint32_t ring = smem_u32(smem) + (uint32_t)w * S * UNIT;
+    const uint32_t bar0 = smem_u32(bars + w * S);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < S; i++) mbar_init(bar0 + i * 8, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
+
+    int lo = 0, hi = a.step.n_seqs - 1;  // last sequence whose first item is <= item
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (a.item_begin[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    const int b = lo;
+    const SeqMeta sm = a.step.seq_meta[b];
+    const int Hkv = a.geo.n_kv, n_rep = a.geo.n_rep;
+    const int ncols = sm.snew * n_rep;
+    const int ncb = (ncols + CPI - 1) / CPI;
+    const int local = item - a.item_begin[b];
+    const int h = local / ncb, cb = local - h * ncb;
+    const int c_lo = cb * CPI, c_hi = min(c_lo + CPI, ncols) - 1;
+    const int q_min = sm.pos + c_lo / n_rep, q_max = sm.pos + c_hi / n_rep;
+    const int lo_key = a.window > 0 ? max(0, q_min - a.window + 1) : 0;
+    const int p_lo = lo_key >> 4, p_hi = q_max >> 4;
+    const size_t blk = (size_t)sm.tok_off * a.geo.n_q;  // first packed q row of this sequence
+
+    uint32_t qf[NT][D / 16][2];
+    int qpos[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        int c = c_lo + nt * 8 + g;  // the column this lane feeds into the B operand
+        bool ok = c < ncols;
+        int r = ok ? c / n_rep : 0, rep = ok ? c - r * n_rep : 0;
+        const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+            reinterpret_cast<const uint16_t*>(a.q) + (blk + (size_t)(h * n_rep + rep) * sm.snew + r) * D);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+            qf[nt][ks][0] = ok ? __ldg(qrow + ks * 8 + t) : 0u;
+            qf[nt][ks][1] = ok ? __ldg(qrow + ks * 8 + 4 + t) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            int cc = min(c_lo + nt * 8 + 2 * t + j, ncols - 1);  // columns past the end mimic the last one
+            qpos[nt][j] = sm.pos + cc / n_rep;
+        }
+    }
+    float o[NT][D / 16][4], m[NT][2], l[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        m[nt][0] = m[nt][1] = -INFINITY; l[nt][0] = l[nt][1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) { o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f; }
+    }
+
+    auto issue = [&](int lp, int stage_idx) {
+        if (lane == 0) {
+            int phys = a.step.tables[sm.tbl_off + lp];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            issue_tile<D>(&tmap, ring + stage_idx * UNIT, bar0 + stage_idx * 8, (phys * Hkv + h) * 32);
+        }
+    };
+    int next = p_lo;
+#pragma unroll 1
+    for (int i = 0; i < S && next <= p_hi; i++, next++) issue(next, i);
+    bool failed = false;
+    int consumed = 0, issued = next - p_lo, fail_at = 0;
+#pragma unroll 1
+    for (int lp = p_lo; lp <= p_hi; lp++) {
+        const int st = consumed % S;
+        if (!failed && !mbar_wait_bounded(bar0 + st * 8, (consumed / S) & 1)) {
+            failed = true;
+            fail_at = consumed;
+            atomicOr(a.status, ST_WAIT_TIMEOUT);
+        }
+        if (!failed) {
+            const bool need_mask = (lp * 16 + 15 > q_min) || (a.window > 0 && lp * 16 + a.window <= q_max);
+            attend_tile<D, NT, BF16>(ring + st * UNIT, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+        }
+        __syncwarp();
+        consumed++;
+        if (next <= p_hi) { if (!failed) { issue(next, st); issued++; } next++; }
+    }
+    if (failed) {  // wait (bounded) for the copies still in flight, then leave without storing
+        for (int i = fail_at; i < issued; i++) mbar_wait_bounded(bar0 + (i % S) * 8, (i / S) & 1, 20000000ull);
+        return;
+    }
+
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float ls = l[nt][j];
+            ls += __shfl_xor_sync(0xffffffffu, ls, 4);
+            ls += __shfl_xor_sync(0xffffffffu, ls, 8);
+            ls += __shfl_xor_sync(0xffffffffu, ls, 16);
+            int c = c_lo + nt * 8 + 2 * t + j;
+            if (c < ncols) {
+                int r = c / n_rep, rep = c - r * n_rep;
+                uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (blk + (size_t)(h * n_rep + rep) * sm.snew + r) * D;
+                float inv = 1.f / ls;
+#pragma unroll
+                for (int mt = 0; mt < D / 16; mt++) {
+                    orow[mt * 16 + g] = to_elem<BF16>(o[nt][mt][j] * inv);
+                    orow[mt * 16 + g + 8] = to_elem<BF16>(o[nt][mt][j + 2] * inv);
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ generic
+// Any page size and head_dim (multiple of 8, <= 512); one warp per query row.
+template <bool BF16>
+__global__ void generic_kernel(const GenericArgs a) {
+    __shared__ float qs[4][512];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t rid = (int64_t)blockIdx.x * 4 + w;  // packed q row: sequence blocks of [n_q][snew]
+    if (rid >= (int64_t)a.step.n_tokens * a.geo.n_q) return;
+    const int D = a.geo.d, P = a.geo.page_size, Hkv = a.geo.n_kv;
+    int lo = 0, hi = a.step.n_seqs - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if ((int64_t)a.step.seq_meta[mid].tok_off * a.geo.n_q <= rid) lo = mid; else hi = mid - 1;
+    }
+    const SeqMeta sm = a.step.seq_meta[lo];
+    const int64_t local = rid - (int64_t)sm.tok_off * a.geo.n_q;
+    const int hq = (int)(local / sm.snew), r = (int)(local % sm.snew);
+    const int h = hq / a.geo.n_rep;  // repeat_kv: q head i reads kv head i / n_rep, kv.rs:177-187
+    const int q_pos = sm.pos + r;
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(a.q) + rid * D;
+    for (int j = lane; j < D; j += 32) qs[w][j] = from_elem<BF16>(q[j]);
+    __syncwarp();
+    const uint16_t* arena = reinterpret_cast<const uint16_t*>(a.arena);
+    const int t_lo = a.window > 0 ? max(0, q_pos - a.window + 1) : 0;
+    float m = -INFINITY, l = 0.f, acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc[i] = 0.f;
+    for (int t0 = t_lo; t0 <= q_pos; t0 += 32) {
+        const int tk = t0 + lane;
+        const bool ok = tk <= q_pos;
+        float s = -INFINITY;
+        if (ok) {
+            int phys = a.step.tables[sm.tbl_off + tk / P];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            const uint16_t* krow = arena + ((((int64_t)phys * Hkv + h) * 2 + 0) * P + tk % P) * D;
+            float d = 0.f;
+            for (int j = 0; j < D; j++) d += qs[w][j] * from_elem<BF16>(krow[j]);
+            s = d * a.scale;
+        }
+        float mx = s;
+        for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float m_new = fmaxf(m, mx);
+        const float alpha = __expf(m - m_new);
+        const float p = ok ? __expf(s - m_new) : 0.f;
+        float ps = p;
+        for (int off = 16; off; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+        l = l * alpha + ps;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] *= alpha;
+        const int cnt = min(32, q_pos - t0 + 1);
+        for (int kk = 0; kk < cnt; kk++) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            const int tv = t0 + kk;
+            int phys = a.step.tables[sm.tbl_off + tv / P];
+            if (phys < 0 || phys >= a.geo.num_pages) phys = 0;
+            const uint16_t* vrow = arena + ((((int64_t)phys * Hkv + h) * 2 + 1) * P + tv % P) * D;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                int j = lane + 32 * i;
+                if (j < D) acc[i] += pk * from_elem<BF16>(vrow[j]);
+            }
+        }
+    }
+    uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + rid * D;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        int j = lane + 32 * i;
+        if (j < D) orow[j] = to_elem<BF16>(acc[i] / l);
+    }
+}
+
+// ------------------------------------------------------------------ launchers
+template <int D> struct DecodeCfg;
+template <> struct DecodeCfg<64>  { static constexpr int W = 4, S = 4, CTAS = 3; };
+template <> struct DecodeCfg<128> { static constexpr int W = 4, S = 3, CTAS = 2; };
+template <> struct DecodeCfg<256> { static constexpr int W = 4, S = 3, CTAS = 1; };
+
+template <int D> constexpr int decode_smem() {
+    return DecodeCfg<D>::W * DecodeCfg<D>::S * 32 * D * 2 + DecodeCfg<D>::W * 8 * D * 4 + DecodeCfg<D>::W * 16 * 4 +
+           DecodeCfg<D>::W * DecodeCfg<D>::S * 8 + 16;
+}
+
+template <int D> struct ChunkCfg;
+template <> struct ChunkCfg<64>  { static constexpr int W = 4, S = 4, NT = 4; };
+template <> struct ChunkCfg<128> { static constexpr int W = 4, S = 3, NT = 2; };
+template <> struct ChunkCfg<256> { static constexpr int W = 4, S = 2, NT = 1; };
+
+template <int D> constexpr int chunk_smem() { return ChunkCfg<D>::W * ChunkCfg<D>::S * 32 * D * 2 + ChunkCfg<D>::W * ChunkCfg<D>::S * 8; }
+
+DecodeConfig decode_config(int d) {
+    switch (d) {
+        case 64: return {DecodeCfg<64>::W, DecodeCfg<64>::S, decode_smem<64>(), DecodeCfg<64>::CTAS};
+        case 128: return {DecodeCfg<128>::W, DecodeCfg<128>::S, decode_smem<128>(), DecodeCfg<128>::CTAS};
+        case 256: return {DecodeCfg<256>::W, DecodeCfg<256>::S, decode_smem<256>(), DecodeCfg<256>::CTAS};
+        default: return {0, 0, 0, 0};
+    }
+}
+ChunkConfig chunk_config(int d) {
+    switch (d) {
+        case 64: return {ChunkCfg<64>::W, ChunkCfg<64>::S, chunk_smem<64>(), 8 * ChunkCfg<64>::NT};
+        case 128: return {ChunkCfg<128>::W, ChunkCfg<128>::S, chunk_smem<128>(), 8 * ChunkCfg<128>::NT};
+        case 256: return {ChunkCfg<256>::W, ChunkCfg<256>::S, chunk_smem<256>(), 8 * ChunkCfg<256>::NT};
+        default: return {0, 0, 0, 0};
+    }
+}
+
+template <int D, bool BF16> static cudaError_t set_attrs() {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, DecodeCfg<D>::W, DecodeCfg<D>::S, BF16>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(chunk_kernel<D, ChunkCfg<D>::NT, ChunkCfg<D>::W, ChunkCfg<D>::S, BF16>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_smem<D>());
+}
+
+cudaError_t kernels_init() {
+    cudaError_t e;
+    if ((e = set_attrs<64, false>()) != cudaSuccess) return e;
+    if ((e = set_attrs<64, true>()) != cudaSuccess) return e;
+    if ((e = set_attrs<128, false>()) != cudaSuccess) return e;
+    if ((e = set_attrs<128, true>()) != cudaSuccess) return e;
+    if ((e = set_attrs<256, false>()) != cudaSuccess) return e;
+    if ((e = set_attrs<256, true>()) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st) {
+    (void)bf16;  // a bit copy: the element type does not matter
+    int64_t total = (int64_t)a.step.n_tokens * a.geo.n_kv * 2 * (a.geo.d / 8);
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    if (blocks <= 0) return cudaSuccess;
+    append_kernel<uint16_t><<<blocks, 256, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, cudaStream_t st) {
+    decode_kernel<D, DecodeCfg<D>::W, DecodeCfg<D>::S, BF16><<<n_ctas, DecodeCfg<D>::W * 32, decode_smem<D>(), st>>>(map, a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, bool bf16, cudaStream_t st) {
+    switch (a.geo.d) {
+        case 64: return bf16 ? launch_decode_t<64, true>(map, a, n_ctas, st) : launch_decode_t<64, false>(map, a, n_ctas, st);
+        case 128: return bf16 ? launch_decode_t<128, true>(map, a, n_ctas, st) : launch_decode_t<128, false>(map, a, n_ctas, st);
+        case 256: return bf16 ? launch_decode_t<256, true>(map, a, n_ctas, st) : launch_decode_t<256, false>(map, a, n_ctas, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <int D, bool BF16>
+static cudaError_t launch_chunk_t(const CUtensorMap& map, const ChunkArgs& a, cudaStream_t st) {
+    int blocks = (a.n_items + ChunkCfg<D>::W - 1) / ChunkCfg<D>::W;
+    if (blocks <= 0) return cudaSuccess;
+    chunk_kernel<D, ChunkCfg<D>::NT, ChunkCfg<D>::W, ChunkCfg<D>::S, BF16><<<blocks, ChunkCfg<D>::W * 32, chunk_smem<D>(), st>>>(map, a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st) {
+    switch (a.geo.d) {
+        case 64: return bf16 ? launch_chunk_t<64, true>(map, a, st) : launch_chunk_t<64, false>(map, a, st);
+        case 128: return bf16 ? launch_chunk_t<128, true>(map, a, st) : launch_chunk_t<128, false>(map, a, st);
+        case 256: return bf16 ? launch_chunk_t<256, true>(map, a, st) : launch_chunk_t<256, false>(map, a, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st) {
+    int64_t rows = (int64_t)a.step.n_tokens * a.geo.n_q;
+    int blocks = (int)((rows + 3) / 4);
+    if (blocks <= 0) return cudaSuccess;
+    if (bf16) generic_kernel<true><<<blocks, 128, 0, st>>>(a);
+    else generic_kernel<false><<<blocks, 128, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace cbkv

@@ -1,0 +1,107 @@
+// Kernel argument blocks and launchers (kernels.cu).  Plain C++ types only.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "manager.hpp"
+
+namespace cbkv {
+
+// Status bits the kernels OR into the arena's status word instead of trapping.
+enum : int32_t {
+    ST_BAD_PAGE = 1,       // a block-table entry was outside the arena
+    ST_WAIT_TIMEOUT = 2,   // a bounded mbarrier wait ran out
+    ST_SMEM_ALIGN = 4,     // dynamic shared memory was not 1024-byte aligned
+    ST_BAD_ARG = 8
+};
+
+// One layer's arena in HBM: pages [num_pages][n_kv][2 (K,V)][16 slots][d], so one
+// (page, kv head) holds its K tile and its V tile back to back (32 rows of d).
+struct LayerArena {
+    void* base = nullptr;
+    CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
+    CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile)
+};
+
+struct StepDev {
+    const SeqMeta* seq_meta;
+    const int32_t* tables;
+    int32_t n_seqs;
+    int32_t n_tokens;
+};
+
+struct GeomDev {
+    int32_t n_q, n_kv, n_rep, d, page_size, num_pages;
+};
+
+struct DecodeArgs {
+    StepDev step;
+    GeomDev geo;
+    const int32_t* seg_unit_begin;
+    const int32_t* seg_page_lo;
+    const int32_t* seg_first_cta;
+    const int32_t* seg_nparts;
+    const int32_t* seg_part_base;
+    const int32_t* cta_unit_begin;
+    const int32_t* cta_first_seg;
+    int32_t n_segs;
+    const void* q;
+    void* out;
+    const void* k_new;  // non-null: write the step's new row into its page and attend it (fused append)
+    const void* v_new;
+    void* arena;        // this layer's pages (for the fused append's global write)
+    float* part_o;      // [n_parts][8][d] partial numerators
+    float* part_ml;     // [n_parts][8][2] running max (log2 domain) and denominator
+    int32_t* seg_counter;
+    int32_t* status;
+    int32_t window;
+    float scale_log2;
+};
+
+struct ChunkArgs {
+    StepDev step;
+    GeomDev geo;
+    const int32_t* item_begin;
+    int32_t n_items;
+    const void* q;
+    void* out;
+    int32_t* status;
+    int32_t window;
+    float scale_log2;
+};
+
+struct AppendArgs {
+    StepDev step;
+    GeomDev geo;
+    const void* k;
+    const void* v;
+    void* arena;
+    int32_t* status;
+};
+
+struct GenericArgs {
+    StepDev step;
+    GeomDev geo;
+    const void* q;
+    void* out;
+    const void* arena;
+    int32_t* status;
+    int32_t window;
+    float scale;
+};
+
+// Decode kernel configuration for a head_dim (0 warps = not supported by the fast path).
+struct DecodeConfig { int warps, stages, smem_bytes, ctas_per_sm; };
+DecodeConfig decode_config(int d);
+struct ChunkConfig { int warps, stages, smem_bytes, cols_per_item; };
+ChunkConfig chunk_config(int d);
+
+cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, bool bf16, cudaStream_t st);
+cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process
+
+}  // namespace cbkv

@@ -1,0 +1,201 @@
+/*
+ * combs_kv.h — C ABI of the B200 paged KV cache + attention library (libcombskv.so).
+ *
+ * Drop-in boundary for one path of CombsEngine: the `KVCache` operator surface of
+ * engine/core/combs-models/src/kv.rs (trait at kv.rs:92-151, `PagedKVCache` at
+ * kv.rs:477-855).  A Rust `impl KVCache<B>` binds these symbols one-to-one; each
+ * declaration cites the reference item it replaces.
+ *
+ * Conventions (those of the reference's own C ABI, combs-ffi/src/lib.rs:41-71):
+ *   - opaque handles, plain pointers and sizes, no C++ or torch types;
+ *   - every call returns int32_t: 0 = ok, negative = error; nothing aborts;
+ *     on error the cache state is untouched (all-or-nothing, kv.rs:805-806);
+ *   - cbkv_last_error() is thread-local, borrowed, valid until the next call on
+ *     the same thread; it carries the reference's panic texts verbatim;
+ *   - handles are not thread-safe (the trait is Send, not Sync): one owner
+ *     thread at a time per arena;
+ *   - device work is enqueued on the caller's cudaStream_t (passed as void*);
+ *     nothing synchronises except the cbkv_export_* and *_host calls.
+ *
+ * Tensor layouts are the reference's: Q [1, n_q, seq, d], K/V [1, n_kv, seq, d]
+ * (kv.rs:89-91).  A batch of sequences is the concatenation of per-sequence
+ * blocks in the order given to cbkv_begin_step: sequence b contributes one
+ * contiguous block [n_heads, seq_b, d].
+ */
+#ifndef COMBS_KV_H
+#define COMBS_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cbkv_arena cbkv_arena; /* arenas + free-list shared by its sequences */
+typedef struct cbkv_seq cbkv_seq;     /* one sequence == one reference PagedKVCache  */
+
+enum {
+    CBKV_OK = 0,
+    CBKV_ERR_POS = -1,       /* "paged cache expects dense contiguous appends"  kv.rs:671-674 */
+    CBKV_ERR_CAPACITY = -2,  /* "paged cache capacity exceeded"                 kv.rs:679-683 */
+    CBKV_ERR_EXHAUSTED = -3, /* "page allocator exhausted"                      kv.rs:552-555 */
+    CBKV_ERR_ARG = -4,       /* bad argument / bad geometry (kv.rs:513-516)     */
+    CBKV_ERR_CUDA = -5,      /* a CUDA runtime or driver call failed            */
+    CBKV_ERR_STATE = -6,     /* call out of order (no step begun, layer mismatch) */
+    CBKV_ERR_DEVICE = -7     /* a kernel reported a problem in its status word   */
+};
+
+enum { CBKV_F16 = 0, CBKV_BF16 = 1 };
+
+/* CacheConfig (kv.rs:40-85) plus the model geometry the reference reads off its
+ * tensors, plus the per-layer windows of PagedKVCache::new_with_windows
+ * (kv.rs:508-527). */
+typedef struct {
+    int32_t num_layers;
+    int32_t n_q_heads;
+    int32_t n_kv_heads;
+    int32_t head_dim;
+    int32_t page_size;            /* CacheConfig::DEFAULT_PAGE_SIZE = 16 (kv.rs:59) */
+    int32_t dtype;                /* CBKV_F16 (the reference's f16 build) or CBKV_BF16 */
+    int64_t max_seq_len;          /* per-sequence capacity, CacheConfig::max_seq_len */
+    int64_t num_pages;            /* 0 => ceil(max_seq_len / page_size) (kv.rs:82-84);
+                                     larger when several sequences share the arena */
+    const int64_t* layer_windows; /* NULL or num_layers entries; 0 = global, w >= 2 = sliding */
+    int32_t sliding_popn_refuses; /* 1 = popn refuses once a sliding layer would have
+                                     evicted (kv.rs:812-816); 0 = windows are pure masks */
+    int32_t device;               /* CUDA device ordinal */
+} cbkv_config;
+
+/* PageStats (kv.rs:153-175), same eight counters in the same order. */
+typedef struct {
+    int64_t pages_used;
+    int64_t pages_free;
+    int64_t num_pages;
+    int64_t page_size;
+    int64_t seq_len;
+    int64_t layers_materialized;
+    int64_t layers_total;
+    int64_t layers_sliding;
+} cbkv_page_stats_t;
+
+/* Thread-local text of the last failure, or "" (combs_last_error, combs-ffi/src/lib.rs:52-58). */
+const char* cbkv_last_error(void);
+
+/* ---- construction ------------------------------------------------------- */
+
+/* PagedKVCache::new_with_windows (kv.rs:508-527): validates geometry and windows,
+ * builds the free-list (page 0 first, kv.rs:424-429).  Touches no device memory:
+ * arenas appear lazily on a layer's first write (kv.rs:695-713). */
+int32_t cbkv_arena_create(const cbkv_config* cfg, cbkv_arena** out);
+int32_t cbkv_arena_destroy(cbkv_arena* arena);
+
+/* Extension (no reference counterpart; the reference order 0,1,2,... is the
+ * default): replace the initial free-list order; ids[0] is handed out first.
+ * Only on an arena no page of which is in use. */
+int32_t cbkv_set_free_list(cbkv_arena* arena, const int64_t* ids, int64_t n);
+
+/* A new empty sequence over the arena (the per-request `create_kv_cache`,
+ * traits.rs:26 / llama.rs:377-390).  Destroying it returns its pages in
+ * table.pop() order (kv.rs:830-833). */
+int32_t cbkv_seq_create(cbkv_arena* arena, cbkv_seq** out);
+int32_t cbkv_seq_destroy(cbkv_seq* seq);
+
+/* Extension: cross-sequence prefix sharing.  The child starts with seq_len =
+ * n_tokens and aliases the parent's first n_tokens / page_size pages (whole pages
+ * only); a shared page returns to the free-list when its last holder drops it. */
+int32_t cbkv_seq_fork_prefix(cbkv_seq* parent, int64_t n_tokens, cbkv_seq** out);
+
+/* ---- one forward pass ---------------------------------------------------- */
+
+/* The layer-0 prologue of attention_opts (kv.rs:665-683) and ensure_pages
+ * (kv.rs:549-559) for every sequence of the step, in the order given:
+ * requires pos[b] == seq_len (pass pos = NULL to skip the check), advances
+ * seq_len by new_tokens[b], allocates pages, and uploads the step's block tables
+ * and work partition to the device on `stream`. */
+int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
+                        const int64_t* pos, int32_t n_seqs, void* stream);
+
+/* The append loop (kv.rs:721-734) for the step's sequences: scatters the new K/V
+ * rows into their page slots.  k, v: device, packed per sequence [n_kv, seq_b, d]. */
+int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void* v, void* stream);
+
+/* gather_window + attend (kv.rs:735-736,790 and 201-269) without the gather:
+ * attention of the step's queries over the paged prefix plus the rows just
+ * appended.  window: 0 = none; the arena's own layer window wins (kv.rs:688-693).
+ * q, out: device, packed per sequence [n_q, seq_b, d]. */
+int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, void* out,
+                             double scale, int64_t window, void* stream);
+
+/* KVCache::attention_opts (kv.rs:116-125, 655-791) for one layer of the step begun:
+ * append + attention in one call (one fused launch on the decode path). */
+int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const void* k, const void* v,
+                       void* out, double scale, int64_t window, void* stream);
+
+/* The same call with HOST buffers (what a caller holding host tensors makes):
+ * copies q, k, v to the device, runs cbkv_attention, copies `out` back and waits
+ * for it.  Buffers from cbkv_host_alloc are pinned and copy asynchronously. */
+int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
+                            const void* v_host, void* out_host, double scale, int64_t window, void* stream);
+int32_t cbkv_host_alloc(size_t bytes, void** out);
+int32_t cbkv_host_free(void* p);
+
+/* ---- rollback / reset / counters ----------------------------------------- */
+
+/* KVCache::popn (kv.rs:807-835): *popped = tokens dropped; 0 = refused. */
+int32_t cbkv_popn(cbkv_seq* seq, int64_t n, int64_t* popped);
+/* KVCache::reset (kv.rs:837-846).  Alone in its arena: allocator back to its
+ * initial order.  Otherwise only this sequence's pages are released. */
+int32_t cbkv_reset(cbkv_seq* seq);
+int64_t cbkv_seq_len(const cbkv_seq* seq);              /* kv.rs:793-795 */
+int64_t cbkv_pages_used(const cbkv_seq* seq);           /* kv.rs:848-850 */
+int64_t cbkv_num_free_pages(const cbkv_arena* arena);   /* kv.rs:529-532 */
+int32_t cbkv_page_stats(const cbkv_seq* seq, cbkv_page_stats_t* out); /* kv.rs:535-546 */
+/* kv_page_bytes (combs-runtime/src/engine.rs:475-498): bytes one page id costs
+ * across K, V and all paged layers. */
+int64_t cbkv_page_bytes(const cbkv_arena* arena);
+
+/* ---- state export (parity checks, checkpoints) ---------------------------- */
+
+/* logical -> physical page ids (kv.rs:481); returns the table length. */
+int64_t cbkv_export_block_table(const cbkv_seq* seq, int64_t* out, int64_t cap);
+/* free stack bottom-to-top (the last entry is handed out next, kv.rs:431-437). */
+int64_t cbkv_export_free_list(const cbkv_arena* arena, int64_t* out, int64_t cap);
+/* One page of one layer as the reference lays it out, [n_kv, page_size, d] for K
+ * and for V (kv.rs:450-451), copied to host; zeros if the layer has not
+ * materialised.  Synchronises `stream`. */
+int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k_out_host,
+                         void* v_out_host, void* stream);
+int32_t cbkv_page_refcount(const cbkv_arena* arena, int64_t page);
+
+/* ---- diagnostics ----------------------------------------------------------- */
+
+/* Reads and clears the status word the kernels write instead of trapping
+ * (0 = clean).  Synchronises `stream`. */
+int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status);
+/* Kernel launches issued by this library in this process so far. */
+int64_t cbkv_launch_count(void);
+/* Per-kernel device timing: when on, CUDA events bracket every attention launch;
+ * cbkv_profile_read returns their summed duration and count and clears them. */
+int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on);
+int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches);
+/* Tuning knob for measurements: CTAs per SM of the decode kernel (0 = default). */
+int32_t cbkv_set_decode_ctas_per_sm(cbkv_arena* arena, int32_t n);
+
+
+/* ---- test hooks (host only, no device is touched) --------------------------- */
+
+/* The bookkeeping half of cbkv_begin_step alone (no reference counterpart beyond
+ * kv.rs:665-683 itself): lets the manager be exercised where no GPU exists. */
+int32_t cbkv_debug_begin_step_host(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
+                                   const int64_t* pos, int32_t n_seqs);
+/* The decode work split for the step in flight, flattened into `out`:
+ * [n_ctas, n_segs, n_units, n_parts, cta_unit_begin(n_ctas+1), seg_unit_begin(n_segs+1),
+ *  seg_page_lo, seg_first_cta, seg_nparts, seg_part_base (n_segs each), cta_first_seg(n_ctas)].
+ * Returns the number of words, or -1 without a step. */
+int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t* out, int64_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COMBS_KV_H */

@@ -55,6 +55,7 @@ def _lib(kind: str) -> C.CDLL:
     lib.orc_begin.argtypes = [P, I64, I64]
     for name in ("orc_layer", "orc_attention", "orc_contig_attention"):
         getattr(lib, name).argtypes = [P, C.c_int, P, P, P, P, C.c_int, I64, I64, C.c_double, I64]
+    lib.orc_append_only.argtypes = [P, C.c_int, P, P, I64, I64]
     lib.orc_popn.restype = I64
     lib.orc_popn.argtypes = [P, I64]
     lib.orc_reset.argtypes = [P]
@@ -213,6 +214,13 @@ class OracleSeq:
 
     def layer(self, layer, q, k, v, pos, scale, window=None):
         return self._call(self.lib.orc_layer, layer, q, k, v, pos, scale, window)
+
+    def append_only(self, layer, k, v, pos):
+        """Fill rows without attending (benchmark set-up); k, v [n_kv, seq, d]."""
+        dt = self.arena.np_dtype
+        k = np.ascontiguousarray(k, dtype=dt)
+        v = np.ascontiguousarray(v, dtype=dt)
+        self._check(self.lib.orc_append_only(self.h, layer, _ptr(k), _ptr(v), k.shape[-2], pos))
 
     def grow(self, total):
         self._check(self.lib.orc_grow(self.h, total))

@@ -418,6 +418,31 @@ int orc_layer(orc_seq* s, int layer, const elem_t* q, const elem_t* k, const ele
     return ORC_OK;
 }
 
+/* EXTENSION (benchmark set-up only): the append loop of kv.rs:723-734 without the
+ * attention that follows it, to fill long contexts cheaply.  k, v [n_kv, seq, d]. */
+int orc_append_only(orc_seq* s, int layer, const elem_t* k, const elem_t* v, int64_t seq, int64_t pos) {
+    orc_arena* a = s->a;
+    int H = a->n_kv, d = a->d, P = a->page_size;
+    if (pos + seq != s->seq_len) { snprintf(g_err, sizeof g_err, "layer call does not match the step begun"); return ORC_ERR_POS; }
+    if (!a->k[layer]) {
+        size_t n = (size_t)a->num_pages * H * P * d;
+        a->k[layer] = (elem_t*)calloc(n, sizeof(elem_t));
+        a->v[layer] = (elem_t*)calloc(n, sizeof(elem_t));
+    }
+    int64_t written = 0;
+    while (written < seq) {
+        int64_t global = pos + written, slot = global % P;
+        int64_t run = (P - slot) < (seq - written) ? (P - slot) : (seq - written);
+        int64_t phys = s->table[global / P];
+        for (int h = 0; h < H; h++) {
+            memcpy(a->k[layer] + (((size_t)phys * H + h) * P + slot) * d, k + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
+            memcpy(a->v[layer] + (((size_t)phys * H + h) * P + slot) * d, v + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
+        }
+        written += run;
+    }
+    return ORC_OK;
+}
+
 /* The reference call: layer 0 advances the sequence (kv.rs:670-678). */
 int orc_attention(orc_seq* s, int layer, const elem_t* q, const elem_t* k, const elem_t* v, elem_t* out,
                   int n_q, int64_t seq, int64_t pos, double scale, int64_t window) {

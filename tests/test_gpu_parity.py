@@ -1,0 +1,156 @@
+"""CUDA path vs oracle on identical seeded inputs, through the C ABI (needs a B200).
+
+Small versions of the five benchmark configurations plus the reference's own test
+patterns; page contents, block tables and free-list are compared bit for bit,
+attention outputs within |err| <= 2e-3 + 1e-2 |ref| (f16 storage, f32 accumulation).
+"""
+import numpy as np
+import pytest
+import torch
+
+from kvcase import Pair, assert_attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def test_cfg1_smollm2_prefill_decode_popn_reappend():
+    # 9 q heads, 3 kv heads, d 64, one layer, 64 pages in a seeded shuffle
+    p = Pair(1, 9, 3, 64, 1024, shuffle_free_list=True, seed=0xC0B50001)
+    s = p.new_seq()
+    p.step([s], [512])
+    assert s[0].pages_used() == 32
+    for _ in range(128):
+        p.step([s], [1])
+    assert s[0].seq_len() == 640
+    p.assert_state_equal()
+    assert s[0].popn(32) == 32 and s[1].popn(32) == 32
+    p.assert_state_equal()
+    for _ in range(32):
+        p.step([s], [1])
+    p.assert_state_equal()  # stale rows of popped tokens were overwritten identically
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_cfg2_qwen_batched_decode_scattered_pages(fused):
+    p = Pair(2, 28, 4, 128, 4096, num_pages=512, shuffle_free_list=True, seed=0xC0B50002)
+    seqs = [p.new_seq() for _ in range(8)]
+    lens = [int(x) for x in p.rng.integers(60, 700, len(seqs))]
+    lens[0], lens[1] = 15, 16  # page edges
+    p.step(seqs, lens, check=False)
+    for _ in range(20):
+        p.step(seqs, [1] * len(seqs), fused=fused)
+    p.assert_state_equal(pages="used")
+
+
+def test_cfg3_gemma_windows_over_paged_kv():
+    # 5 local : 1 global, d 256; window shortened so that it slides within the test
+    windows = [96, 96, None, 96]
+    p = Pair(4, 8, 4, 256, 2048, num_pages=256, windows=windows, seed=0xC0B50003)
+    seqs = [p.new_seq() for _ in range(4)]
+    p.step(seqs, [40, 95, 96, 300])
+    for _ in range(40):
+        p.step(seqs, [1, 1, 1, 1])
+    p.assert_state_equal(pages="used")
+    assert seqs[0][0].popn(1) == 0  # a sliding layer would have evicted: refused, kv.rs:812-816
+
+
+def test_cfg3_explicit_window_argument_on_global_layers():  # kv.rs:1001-1030, the masked-global side
+    p = Pair(1, 8, 4, 256, 1024, seed=5)
+    s = p.new_seq()
+    p.step([s], [7], scale=0.9 / 16, window=5)
+    for _ in range(30):
+        p.step([s], [1], scale=0.9 / 16, window=5)
+
+
+def test_cfg4_llama_chunked_prefill():
+    p = Pair(2, 32, 8, 128, 2048, num_pages=256, shuffle_free_list=True, seed=0xC0B50004)
+    seqs = [p.new_seq(), p.new_seq()]
+    for _ in range(3):
+        p.step(seqs, [128, 128])
+    p.step(seqs, [100, 37])      # ragged, not page aligned
+    p.step(seqs, [1, 64])        # a decode row next to a chunk
+    p.assert_state_equal(pages="used")
+
+
+def test_cfg5_prefix_sharing_and_churn():
+    p = Pair(2, 28, 4, 128, 4096, num_pages=400, shuffle_free_list=True, seed=0xC0B50005, popn_refuses=False)
+    root = p.new_seq()
+    p.step([root], [64])
+    live = [p.fork(root, 64) for _ in range(12)]
+    suffix = np.round(np.exp(p.rng.uniform(np.log(8), np.log(300), len(live)))).astype(int)
+    p.step(live, [int(x) for x in suffix], check=False)
+    for it in range(3):
+        for _ in range(6):
+            p.step(live, [1] * len(live))
+        evict = [live[i] for i in p.rng.permutation(len(live))[:2]]
+        for e in evict:  # back to the shared prefix; private pages return to the LIFO free-list
+            n = e[0].seq_len() - 64
+            assert e[0].popn(n) == n and e[1].popn(n) == n
+        p.assert_state_equal(pages="used")
+        for e in evict:
+            live.remove(e)
+            p.drop(e)
+            live.append(p.fork(root, 64))
+        p.step(live[-2:], [int(x) for x in p.rng.integers(20, 90, 2)], check=False)
+    p.step(live, [1] * len(live))
+    p.assert_state_equal(pages="used")
+
+
+@pytest.mark.parametrize("chunks", [[5, 7, 1, 1, 1], [3, 6, 5, 2]])
+def test_reference_chunk_patterns_at_reference_geometry(chunks):
+    # tests/kv_cache.rs:63-146: page size 4, 4 q / 2 kv heads, d 8 -> the generic kernel
+    p = Pair(2, 4, 2, 8, 64, page_size=4, seed=7)
+    s = p.new_seq()
+    for n in chunks:
+        p.step([s], [n], scale=0.35)
+    assert s[0].pages_used() == 4
+    p.assert_state_equal()
+
+
+def test_reference_popn_rollback_then_new_tokens():  # tests/kv_cache.rs:95-126
+    p = Pair(2, 4, 2, 64, 64, seed=8)
+    s = p.new_seq()
+    p.step([s], [40], scale=0.35)
+    assert s[0].popn(24) == 24 and s[1].popn(24) == 24
+    assert s[0].pages_used() == 1
+    p.step([s], [3], scale=0.35)
+    assert s[0].seq_len() == 19
+    p.assert_state_equal()
+    s[0].reset(); s[1].reset()   # tests/kv_cache.rs:149-164
+    p.step([s], [5], scale=0.35)
+    p.assert_state_equal()
+
+
+def test_bf16_storage_runs_and_tracks_f32_math():
+    from combsengine_b200 import KVArena
+    torch.manual_seed(0)
+    a = KVArena(1, 8, 2, 128, 512, dtype=torch.bfloat16)
+    s = a.new_seq()
+    a.begin_step([s], [200])
+    q = torch.randn(8, 200, 128, device="cuda").bfloat16()
+    k = torch.randn(2, 200, 128, device="cuda").bfloat16()
+    v = torch.randn(2, 200, 128, device="cuda").bfloat16()
+    out = a.attention(0, q, k, v, 128 ** -0.5).float()
+    kk, vv = k.float().repeat_interleave(4, 0), v.float().repeat_interleave(4, 0)
+    sc = torch.einsum("hqd,hkd->hqk", q.float(), kk) * 128 ** -0.5
+    sc = sc.masked_fill(torch.ones(200, 200, device="cuda").triu(1).bool(), float("-inf"))
+    ref = torch.einsum("hqk,hkd->hqd", sc.softmax(-1), vv)
+    assert (out - ref).abs().max().item() < 3e-2  # bf16 probabilities and output
+    assert a.device_status() == 0
+
+
+def test_host_buffer_entry_point_matches_device_one():
+    p = Pair(1, 28, 4, 128, 1024, seed=11)
+    s = p.new_seq()
+    p.step([s], [300], check=False)
+    g = p.g
+    g.begin_step([s[0]], [1])
+    q = torch.randn(28 * 128).half().pin_memory()
+    k = torch.randn(4 * 128).half().pin_memory()
+    v = torch.randn(4 * 128).half().pin_memory()
+    out = torch.empty_like(q).pin_memory()
+    g.attention_host(0, q, k, v, out, 0.1)
+    s[0].popn(1)
+    g.begin_step([s[0]], [1])
+    ref = g.attention(0, q.cuda(), k.cuda(), v.cuda(), 0.1).cpu()
+    assert torch.equal(out, ref)
