@@ -329,7 +329,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctas-per-sm", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer than the 28 layers (small ncu case)")
     args = ap.parse_args()
+    if args.layers:
+        global LAYERS
+        LAYERS = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

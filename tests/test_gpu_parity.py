@@ -51,7 +51,9 @@ def test_cfg3_gemma_windows_over_paged_kv():
     for _ in range(40):
         p.step(seqs, [1, 1, 1, 1])
     p.assert_state_equal(pages="used")
-    assert seqs[0][0].popn(1) == 0  # a sliding layer would have evicted: refused, kv.rs:812-816
+    assert seqs[3][0].popn(1) == 0  # a sliding layer would have evicted: refused, kv.rs:812-816
+    assert seqs[3][0].seq_len() == 340
+    assert seqs[0][0].popn(1) == 1  # 80 tokens <= w - 1: nothing evicted yet
 
 
 def test_cfg3_explicit_window_argument_on_global_layers():  # kv.rs:1001-1030, the masked-global side
