@@ -174,8 +174,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     total_steps = 3 * (args.steps + args.warmup) + 16
     arena = KVArena(LAYERS, N_Q, N_KV, D, CTX_HI + total_steps + 64, PAGE, ARENA_PAGES, device=local_rank)
     arena.set_free_list(np.random.default_rng(SEED + 7 + rank).permutation(ARENA_PAGES))
-    if args.ctas_per_sm:
-        arena.set_decode_ctas_per_sm(args.ctas_per_sm)
+    if args.ctas_per_sm or args.stages or args.consumers or args.no_overlap:
+        arena.set_decode_tuning(args.ctas_per_sm, args.stages, args.consumers, 0, not args.no_overlap)
     seqs = [arena.new_seq() for _ in range(BATCH)]
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
 
@@ -309,7 +309,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "hbm_gbs": bytes_step * world / (ms / args.steps * 1e-3) / 1e9,
         "hbm_frac_of_8tbs": bytes_step / (ms / args.steps * 1e-3) / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "decode_kernel<128,4,3,f16>", "us_per_launch": kms / kn * 1e3,
+                     "traffic": None, "kernel": "decode_kernel<d=128,f16>", "us_per_launch": kms / kn * 1e3,
                      "algorithmic_bytes_per_launch": bytes_launch, "peak_source": peak_src},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ems / args.steps},
@@ -327,7 +327,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ctas-per-sm", type=int, default=0)
+    ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")
+    ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
+    ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8)")
+    ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer than the 28 layers (small ncu case)")
     args = ap.parse_args()

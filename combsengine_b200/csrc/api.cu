@@ -79,7 +79,9 @@ struct DeviceState {
     int32_t* seg_counter = nullptr;
     size_t counter_cap = 0;
     int32_t* status = nullptr;
-    int decode_ctas_per_sm = 0;
+    int decode_ctas_per_sm = 0, decode_stages = 0, decode_consumers = 0, decode_max_ctas = 0;
+    bool pdl = true;
+    int last_kv_writer = -1;  // layer whose pages the most recent launch wrote (-1: none since the last upload)
     // host-buffer entry point staging
     uint8_t* io = nullptr;
     size_t io_cap = 0;
@@ -225,6 +227,7 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->step.n_seqs = (int32_t)a->step_meta.size();
     d->step.n_tokens = (int32_t)a->step_tokens;
     d->uploaded_step = a->step_id;
+    d->last_kv_writer = -1;  // the upload is a full stream dependency
     return CBKV_OK;
 }
 
@@ -237,13 +240,14 @@ int32_t get_decode_plan(Arena* a, int64_t window, cudaStream_t st, DecodePlanDev
     DeviceState* d = dev_of(a);
     auto it = d->decode_plans.find(window);
     if (it != d->decode_plans.end()) { *out = &it->second; return CBKV_OK; }
-    DecodeConfig dc = decode_config(a->cfg.head_dim);
-    int per_sm = d->decode_ctas_per_sm > 0 ? d->decode_ctas_per_sm : dc.ctas_per_sm;
+    DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
     DecodePlanDev pd{};
-    // at least one page per warp, at most one resident wave of CTAs
-    build_decode_plan(*a, window, d->sm_count * per_sm, &pd.host);
+    // at least one page per consumer warp, at most one resident wave of CTAs
+    int max_ctas = d->sm_count * dc.ctas_per_sm;
+    if (d->decode_max_ctas > 0) max_ctas = std::min(max_ctas, d->decode_max_ctas);
+    build_decode_plan(*a, window, max_ctas, &pd.host);
     {
-        int want = std::max(1, (pd.host.n_units + dc.warps - 1) / dc.warps);
+        int want = std::max(1, (pd.host.n_units + dc.consumers - 1) / dc.consumers);
         if (want < pd.host.n_ctas) build_decode_plan(*a, window, want, &pd.host);
     }
     std::vector<int32_t> flat;
@@ -321,6 +325,7 @@ int32_t run_append(Arena* a, int layer, const void* k, const void* v, cudaStream
     AppendArgs args{d->step, geom(a), k, v, d->layers[(size_t)layer].base, d->status};
     CU_TRY(launch_append(args, a->cfg.dtype == CBKV_BF16, st));
     g_launches++;
+    d->last_kv_writer = layer;
     return CBKV_OK;
 }
 
@@ -345,9 +350,13 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.q = q; args.out = out; args.k_new = k_fused; args.v_new = v_fused; args.arena = L.base;
         args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
         args.window = (int32_t)w; args.scale_log2 = scale_log2;
+        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
+        args.n_stages = dc.stages; args.comb_cols = dc.comb_cols;
+        args.kv_dep = d->last_kv_writer == layer ? 1 : 0;
         ProfScope ps(d, st);
-        CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, bf16, st));
+        CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st));
         g_launches++;
+        d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
     }
     if (d->fast) {
@@ -629,12 +638,26 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
     return CBKV_OK;
 }
 
-int32_t cbkv_set_decode_ctas_per_sm(cbkv_arena* arena, int32_t n) {
+int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
+                               int32_t max_ctas, int32_t overlap_launches) {
     Arena* a = reinterpret_cast<Arena*>(arena);
-    if (!a || n < 0 || n > 8) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    if (!a || ctas_per_sm < 0 || ctas_per_sm > 8 || stages < 0 || stages > 64 || max_ctas < 0 ||
+        !(consumers == 0 || consumers == 4 || consumers == 6 || consumers == 8)) {
+        set_error("bad argument"); return CBKV_ERR_ARG;
+    }
     int32_t rc = ensure_device(a);
     if (rc) return rc;
-    dev_of(a)->decode_ctas_per_sm = n;
+    DeviceState* d = dev_of(a);
+    if (d->fast) {
+        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), ctas_per_sm, stages, consumers);
+        if (dc.smem_bytes > 227 * 1024) { set_error("that many stages do not fit in shared memory"); return CBKV_ERR_ARG; }
+    }
+    d->decode_ctas_per_sm = ctas_per_sm;
+    d->decode_stages = stages;
+    d->decode_consumers = consumers;
+    d->decode_max_ctas = max_ctas;
+    d->pdl = overlap_launches != 0;
+    d->decode_plans.clear();  // the split depends on the CTA count
     return CBKV_OK;
 }
 

@@ -130,10 +130,13 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
                                             int kpos0, const int (&qpos)[NT][2], int window, float scale_log2,
                                             bool need_mask, int lane) {
     const int g = lane >> 2;
-    float s[NT][4];
+    float s[NT][4], s2[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
-    // ---- S^T = K . Q^T
+    for (int nt = 0; nt < NT; nt++) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+    }
+    // ---- S^T = K . Q^T  (two accumulator chains, summed at the end)
     {
         const uint32_t row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row of this lane's ldmatrix address
         const uint32_t jsel = lane >> 4;                           // which of the two 16-byte chunks
@@ -142,7 +145,15 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
             uint32_t a[4];
             ldsm_x4(stage + (ks >> 2) * 4096u + swz(row, (ks & 3) * 2 + jsel), a);
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) mma_16816<BF16>(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+            for (int nt = 0; nt < NT; nt++) {
+                if (ks & 1) mma_16816<BF16>(s2[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+                else mma_16816<BF16>(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) s[nt][i] += s2[nt][i];
         }
     }
     // ---- online softmax over the tile's 16 tokens (rows g and g+8 of the fragment)
@@ -239,24 +250,77 @@ __global__ void append_kernel(const AppendArgs a) {
 // ------------------------------------------------------------------ decode
 // Each CTA owns a contiguous range of (sequence, kv head, page) units; a range may
 // cover the tail of one segment, whole segments and the head of another ("pieces").
-// Warps of the CTA take the pages of a piece round-robin, each through its own ring
-// of TMA stages, and their running (max, sum, numerator) states are merged in shared
-// memory when the piece ends.  A segment cut across CTAs leaves partials in global
-// scratch; the CTA that finishes last (atomic ticket, no waiting) merges them.
-struct UnitCursor {
-    int seg, pb, pe, u;
+//
+// Warp 0 is the producer: its lanes resolve physical pages through the block table
+// (a round of lanes at a time, one look-up round ahead) and issue the TMA copies
+// into a CTA-wide ring of NS stages.  The other C warps consume: tile n of the CTA
+// lives in stage n % NS and belongs to consumer warp n % C, and NS is a multiple of
+// C, so every stage has one producer and one consumer that visit it in order (an
+// mbarrier parity wait is only unambiguous for a waiter at most one phase ahead).
+// Each consumer keeps a running (max, sum, numerator) state in registers; the
+// states are merged in shared memory when a piece ends.  A
+// segment cut across CTAs leaves partials in global scratch; the CTA that finishes
+// last (atomic ticket, nobody waits) merges them.
+//
+// Every wait is bounded; a warp that gives up records it in the status word and
+// falls through the remaining barriers without computing.
+struct Piece {
+    int sb, se;        // unit range of the segment
+    int b, h;
+    int q_pos, page_lo, page_last, tbl_off, tok_off;
 };
 
-template <int D, int W, int S, bool BF16>
-__global__ void __launch_bounds__(W * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
+__device__ __forceinline__ Piece load_piece(const DecodeArgs& a, int seg) {
+    Piece p;
+    p.sb = a.seg_unit_begin[seg];
+    p.se = a.seg_unit_begin[seg + 1];
+    p.b = seg / a.geo.n_kv;
+    p.h = seg - p.b * a.geo.n_kv;
+    const SeqMeta sm = a.step.seq_meta[p.b];
+    p.q_pos = sm.pos + sm.snew - 1;  // decode: the one new token, at the end of the window
+    p.page_lo = a.seg_page_lo[seg];
+    p.page_last = p.q_pos >> 4;
+    p.tbl_off = sm.tbl_off;
+    p.tok_off = sm.tok_off;
+    return p;
+}
+
+template <int D>
+__device__ __forceinline__ void load_q_frags(const DecodeArgs& a, const Piece& p, int g, int t, uint32_t (&qf)[1][D / 16][2]) {
+    // Q^T fragments of the kv group's q heads (columns >= n_rep are zero)
+    const int n_rep = a.geo.n_rep;
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+        reinterpret_cast<const uint16_t*>(a.q) + ((size_t)p.tok_off * a.geo.n_q + (size_t)p.h * n_rep + (g < n_rep ? g : 0)) * D);
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks++) {
+        qf[0][ks][0] = g < n_rep ? __ldg(qrow + ks * 8 + t) : 0u;
+        qf[0][ks][1] = g < n_rep ? __ldg(qrow + ks * 8 + 4 + t) : 0u;
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync(int nthreads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <int D, int C, bool BF16>
+__global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
     constexpr uint32_t UNIT = 32u * D * 2u;
     extern __shared__ __align__(1024) uint8_t smem[];
-    float* comb_o = reinterpret_cast<float*>(smem + (size_t)W * S * UNIT);  // [W][8][D]
-    float* comb_ml = comb_o + W * 8 * D;                                     // [W][8][2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(comb_ml + W * 16);          // [W][S]
-    int* flag = reinterpret_cast<int*>(bars + W * S);
+    const int NS = a.n_stages;            // multiple of C (checked by the host)
+    const int R = NS < 8 ? NS : 8;        // producer lanes per round; R <= NS keeps a round free of self-dependencies
+    const int ccols = a.comb_cols;
+    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [C][ccols][D]
+    float* comb_ml = comb_o + (size_t)C * ccols * D;                          // [C][8][2]
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + C * 16);      // [NS]
+    uint64_t* bar_empty = bar_full + NS;                                      // [NS]
+    int* flag = reinterpret_cast<int*>(bar_empty + NS);                       // [0] merge ticket, [1] failure
 
-    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
     if ((smem_u32(smem) & 1023u) != 0) {
         if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
@@ -264,147 +328,160 @@ __global__ void __launch_bounds__(W * 32) decode_kernel(const __grid_constant__ 
     }
     const int u0 = a.cta_unit_begin[cta], u1 = a.cta_unit_begin[cta + 1];
     if (u0 >= u1) return;
-
-    const uint32_t ring = smem_u32(smem) + (uint32_t)w * S * UNIT;
-    const uint32_t bar0 = smem_u32(bars + w * S);
-    if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < S; i++) mbar_init(bar0 + i * 8, 1);
+    const int ntiles = u1 - u0;
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t full0 = smem_u32(bar_full), empty0 = smem_u32(bar_empty);
+    if (tid == 0) {
+        for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
+        flag[0] = 0; flag[1] = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
-    __syncwarp();
-
-    const int Hkv = a.geo.n_kv, n_rep = a.geo.n_rep;
+    __syncthreads();
+    pdl_launch_dependents();
+    const int Hkv = a.geo.n_kv;
     const int first_seg = a.cta_first_seg[cta];
 
-    // producer cursor: walks this warp's units across pieces, S tiles ahead of the math
-    UnitCursor pc;
-    pc.seg = first_seg; pc.pb = u0; pc.pe = min(u1, a.seg_unit_begin[first_seg + 1]); pc.u = u0 + w;
-    auto normalize = [&](UnitCursor& c) {
-        while (c.u >= c.pe && c.pe < u1) {
-            c.seg++; c.pb = c.pe; c.pe = min(u1, a.seg_unit_begin[c.seg + 1]); c.u = c.pb + w;
-        }
-    };
-    bool failed = false;
-    int fail_at = 0;
-    auto issue = [&](UnitCursor& c, int stage_idx) {
-        // lane 0 resolves the unit's physical page through the block table and issues the copy
-        if (lane == 0) {
-            int b = c.seg / Hkv, h = c.seg - b * Hkv;
-            int lp = a.seg_page_lo[c.seg] + (c.u - a.seg_unit_begin[c.seg]);
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        // The pages read here were written by earlier steps; only when the previous
+        // launch wrote this same layer must it be waited for.
+        if (a.kv_dep) pdl_wait();
+        int seg = first_seg;  // per-lane scan position (monotonic)
+        auto lookup = [&](int n) -> int {
+            if (lane >= R || n >= ntiles) return -1;
+            const int u = u0 + n;
+            while (u >= a.seg_unit_begin[seg + 1]) seg++;
+            const int b = seg / Hkv, h = seg - b * Hkv;
+            const int lp = a.seg_page_lo[seg] + (u - a.seg_unit_begin[seg]);
             int phys = a.step.tables[a.step.seq_meta[b].tbl_off + lp];
             if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-            issue_tile<D>(&tmap, ring + stage_idx * UNIT, bar0 + stage_idx * 8, (phys * Hkv + h) * 32);
-        }
-    };
-    normalize(pc);
-    int issued = 0, consumed = 0;
+            return (phys * Hkv + h) * 32;
+        };
+        int row0 = lookup(lane);
+        bool failed = false;
+        int issued_end = 0;
 #pragma unroll 1
-    for (int i = 0; i < S; i++) {
-        if (pc.u < pc.pe) { issue(pc, i); issued++; pc.u += W; normalize(pc); }
+        for (int base = 0; base < ntiles && !failed; base += R) {
+            const int row0_next = lookup(base + R + lane);  // in flight while this round waits for free stages
+            const int n = base + lane;
+            if (lane < R && n < ntiles) {
+                const int st = n % NS;
+                if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, ((n / NS) - 1) & 1)) failed = true;
+                if (!failed) issue_tile<D>(&tmap, ring + st * UNIT, full0 + st * 8, row0);
+            }
+            failed = __any_sync(0xffffffffu, failed);
+            if (!failed) issued_end = min(ntiles, base + R);
+            row0 = row0_next;
+        }
+        if (failed) {
+            if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+            // wait (bounded) for the copies still in flight before leaving
+            for (int n = max(0, issued_end - NS) + lane; n < issued_end; n += 32)
+                mbar_wait_bounded(full0 + (n % NS) * 8, (n / NS) & 1, 20000000ull);
+        }
+        return;
     }
 
+    // ---------------------------------------------------------------- consumers
+    const int cw = warp - 1, ctid = tid - 32, g = lane >> 2, t = lane & 3;
+    const int n_rep = a.geo.n_rep;
+    pdl_wait();  // q, k_new, v_new and the scratch come from earlier work in the stream
+    Piece cur = load_piece(a, first_seg);
+    uint32_t qf[1][D / 16][2];
+    load_q_frags<D>(a, cur, g, t, qf);
+    bool failed = false;
     int seg = first_seg, pb = u0;
 #pragma unroll 1
     while (pb < u1) {
-        const int sb = a.seg_unit_begin[seg];
-        const int pe = min(u1, a.seg_unit_begin[seg + 1]);
-        const int b = seg / Hkv, h = seg - b * Hkv;
-        const SeqMeta sm = a.step.seq_meta[b];
-        const int q_pos = sm.pos + sm.snew - 1;  // decode: the one new token, at the end of the window
-        const int page_lo = a.seg_page_lo[seg];
-        const int page_last = q_pos >> 4;
-        const size_t blk = (size_t)sm.tok_off;   // packed token offset of this sequence (snew == 1)
-
-        // Q^T fragments of the kv group's q heads (columns >= n_rep are zero)
-        uint32_t qf[1][D / 16][2];
-        {
-            const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
-                reinterpret_cast<const uint16_t*>(a.q) + (blk * a.geo.n_q + (size_t)h * n_rep + g) * D);
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ks++) {
-                qf[0][ks][0] = g < n_rep ? __ldg(qrow + ks * 8 + t) : 0u;
-                qf[0][ks][1] = g < n_rep ? __ldg(qrow + ks * 8 + 4 + t) : 0u;
-            }
+        const int pe = min(u1, cur.se);
+        Piece nxt = cur;
+        uint32_t qf_next[1][D / 16][2];
+        const bool more = pe < u1;
+        if (more) {  // next piece's metadata and queries arrive while this one is processed
+            nxt = load_piece(a, seg + 1);
+            load_q_frags<D>(a, nxt, g, t, qf_next);
         }
         float o[1][D / 16][4], m[1][2] = {{-INFINITY, -INFINITY}}, l[1][2] = {{0.f, 0.f}};
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) { o[0][mt][0] = o[0][mt][1] = o[0][mt][2] = o[0][mt][3] = 0.f; }
-        const int qpos[1][2] = {{q_pos, q_pos}};
+        const int qpos[1][2] = {{cur.q_pos, cur.q_pos}};
 
+        const int n0 = pb - u0;
 #pragma unroll 1
-        for (int u = pb + w; u < pe; u += W) {
-            const int st = consumed % S;
+        for (int u = pb + (cw - n0 % C + C) % C; u < pe; u += C) {
+            const int n = u - u0, st = n % NS;  // n % C == cw
             const uint32_t stage = ring + st * UNIT;
-            if (!failed && !mbar_wait_bounded(bar0 + st * 8, (consumed / S) & 1)) {
+            if (!failed && !mbar_wait_bounded(full0 + st * 8, (n / NS) & 1)) {
                 failed = true;
-                fail_at = consumed;
-                atomicOr(a.status, ST_WAIT_TIMEOUT);
+                if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             }
-            const int lp = page_lo + (u - sb);
+            const int lp = cur.page_lo + (u - cur.sb);
             if (!failed) {
-                if (a.k_new != nullptr && lp == page_last) {
+                if (a.k_new != nullptr && lp == cur.page_last) {
                     // fused append: put the new K/V row into the tile just fetched and into its page
-                    const int slot = q_pos & 15;
-                    const int phys = a.step.tables[sm.tbl_off + lp];
+                    const int slot = cur.q_pos & 15;
+                    const int phys = a.step.tables[cur.tbl_off + lp];
                     for (int c = lane; c < 2 * (D / 8); c += 32) {
                         int kv = c / (D / 8), j = c - kv * (D / 8);
                         const uint4 val = *(reinterpret_cast<const uint4*>(kv ? a.v_new : a.k_new) +
-                                            (blk * Hkv + h) * (D / 8) + j);
+                                            ((size_t)cur.tok_off * Hkv + cur.h) * (D / 8) + j);
                         uint32_t row = kv * 16 + slot;
                         uint32_t addr = stage + (j >> 3) * 4096u + swz(row, j & 7);
                         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
                         if (phys >= 0 && phys < a.geo.num_pages) {
-                            size_t drow = (((size_t)phys * Hkv + h) * 2 + kv) * 16 + slot;
+                            size_t drow = (((size_t)phys * Hkv + cur.h) * 2 + kv) * 16 + slot;
                             reinterpret_cast<uint4*>(a.arena)[drow * (D / 8) + j] = val;
                         }
                     }
                     fence_proxy_async();
                     __syncwarp();
                 }
-                const bool need_mask = (lp * 16 + 15 > q_pos) || (a.window > 0 && lp * 16 + a.window <= q_pos);
+                const bool need_mask = (lp * 16 + 15 > cur.q_pos) || (a.window > 0 && lp * 16 + a.window <= cur.q_pos);
                 attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
             }
             __syncwarp();
-            consumed++;
-            if (pc.u < pc.pe) { if (!failed) { issue(pc, st); issued++; } pc.u += W; normalize(pc); }
+            if (lane == 0) mbar_arrive(empty0 + st * 8);  // the stage may be refilled
         }
 
-        // ---- merge the warps' states for this piece
+        // ---- merge the consumer warps' states for this piece
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 4);
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 8);
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 16);
         }
-        float* co = comb_o + (size_t)w * 8 * D;
+        float* co = comb_o + (size_t)cw * ccols * D;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
-            co[(2 * t) * D + mt * 16 + g] = o[0][mt][0];
-            co[(2 * t + 1) * D + mt * 16 + g] = o[0][mt][1];
-            co[(2 * t) * D + mt * 16 + g + 8] = o[0][mt][2];
-            co[(2 * t + 1) * D + mt * 16 + g + 8] = o[0][mt][3];
+            if (2 * t < ccols) {
+                co[(2 * t) * D + mt * 16 + g] = o[0][mt][0];
+                co[(2 * t) * D + mt * 16 + g + 8] = o[0][mt][2];
+            }
+            if (2 * t + 1 < ccols) {
+                co[(2 * t + 1) * D + mt * 16 + g] = o[0][mt][1];
+                co[(2 * t + 1) * D + mt * 16 + g + 8] = o[0][mt][3];
+            }
         }
         if (g == 0) {
-            comb_ml[(w * 8 + 2 * t) * 2 + 0] = m[0][0]; comb_ml[(w * 8 + 2 * t) * 2 + 1] = l[0][0];
-            comb_ml[(w * 8 + 2 * t + 1) * 2 + 0] = m[0][1]; comb_ml[(w * 8 + 2 * t + 1) * 2 + 1] = l[0][1];
+            comb_ml[(cw * 8 + 2 * t) * 2 + 0] = m[0][0]; comb_ml[(cw * 8 + 2 * t) * 2 + 1] = l[0][0];
+            comb_ml[(cw * 8 + 2 * t + 1) * 2 + 0] = m[0][1]; comb_ml[(cw * 8 + 2 * t + 1) * 2 + 1] = l[0][1];
         }
-        __syncthreads();
+        consumer_sync(C * 32);
         const int nparts = a.seg_nparts[seg];
         const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
-        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + (blk * a.geo.n_q + (size_t)h * n_rep) * D;
-        for (int idx = tid; idx < n_rep * D; idx += W * 32) {
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)cur.tok_off * a.geo.n_q + (size_t)cur.h * n_rep) * D;
+        for (int idx = ctid; idx < n_rep * D; idx += C * 32) {
             int col = idx / D, j = idx - col * D;
             float M = -INFINITY;
 #pragma unroll
-            for (int ww = 0; ww < W; ww++) M = fmaxf(M, comb_ml[(ww * 8 + col) * 2]);
+            for (int ww = 0; ww < C; ww++) M = fmaxf(M, comb_ml[(ww * 8 + col) * 2]);
             float acc = 0.f, ls = 0.f;
 #pragma unroll
-            for (int ww = 0; ww < W; ww++) {
+            for (int ww = 0; ww < C; ww++) {
                 float mw = comb_ml[(ww * 8 + col) * 2];
                 float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-                acc += f * comb_o[((size_t)ww * 8 + col) * D + j];
+                acc += f * comb_o[((size_t)ww * ccols + col) * D + j];
                 ls += f * comb_ml[(ww * 8 + col) * 2 + 1];
             }
             if (nparts == 1) {
@@ -416,17 +493,17 @@ __global__ void __launch_bounds__(W * 32) decode_kernel(const __grid_constant__ 
         }
         if (nparts > 1) {
             __threadfence();
-            __syncthreads();
-            if (tid == 0) {
+            consumer_sync(C * 32);
+            if (ctid == 0) {
                 int ticket = atomicAdd(a.seg_counter + seg, 1);
-                *flag = (ticket == nparts - 1);
+                flag[0] = (ticket == nparts - 1);
                 if (ticket == nparts - 1) a.seg_counter[seg] = 0;  // ready for the next launch
             }
-            __syncthreads();
-            if (*flag) {
+            consumer_sync(C * 32);
+            if (flag[0]) {
                 __threadfence();
                 const int base = a.seg_part_base[seg];
-                for (int idx = tid; idx < n_rep * D; idx += W * 32) {
+                for (int idx = ctid; idx < n_rep * D; idx += C * 32) {
                     int col = idx / D, j = idx - col * D;
                     float M = -INFINITY;
                     for (int p = 0; p < nparts; p++) M = fmaxf(M, __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2));
@@ -441,13 +518,15 @@ __global__ void __launch_bounds__(W * 32) decode_kernel(const __grid_constant__ 
                 }
             }
         }
-        __syncthreads();  // comb buffers and flag are reused by the next piece
+        consumer_sync(C * 32);  // comb buffers and flag are reused by the next piece
+        if (flag[1]) failed = true;  // the producer gave up: stop waiting for tiles
         seg++;
         pb = pe;
-    }
-    // a warp that gave up still waits (bounded) for the copies it has in flight
-    if (failed) {
-        for (int i = fail_at; i < issued; i++) mbar_wait_bounded(bar0 + (i % S) * 8, (i / S) & 1, 20000000ull);
+        if (more) {
+            cur = nxt;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
+        }
     }
 }
 
@@ -653,14 +732,14 @@ __global__ void generic_kernel(const GenericArgs a) {
 }
 
 // ------------------------------------------------------------------ launchers
+// default consumer warps per CTA and CTAs per SM of the decode kernel
 template <int D> struct DecodeCfg;
-template <> struct DecodeCfg<64>  { static constexpr int W = 4, S = 4, CTAS = 3; };
-template <> struct DecodeCfg<128> { static constexpr int W = 4, S = 3, CTAS = 2; };
-template <> struct DecodeCfg<256> { static constexpr int W = 4, S = 3, CTAS = 1; };
+template <> struct DecodeCfg<64>  { static constexpr int C = 4, CTAS = 3; };
+template <> struct DecodeCfg<128> { static constexpr int C = 4, CTAS = 2; };
+template <> struct DecodeCfg<256> { static constexpr int C = 6, CTAS = 1; };
 
-template <int D> constexpr int decode_smem() {
-    return DecodeCfg<D>::W * DecodeCfg<D>::S * 32 * D * 2 + DecodeCfg<D>::W * 8 * D * 4 + DecodeCfg<D>::W * 16 * 4 +
-           DecodeCfg<D>::W * DecodeCfg<D>::S * 8 + 16;
+static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols) {
+    return stages * 32 * d * 2 + consumers * comb_cols * d * 4 + consumers * 16 * 4 + stages * 16 + 16;
 }
 
 template <int D> struct ChunkCfg;
@@ -670,13 +749,27 @@ template <> struct ChunkCfg<256> { static constexpr int W = 4, S = 2, NT = 1; };
 
 template <int D> constexpr int chunk_smem() { return ChunkCfg<D>::W * ChunkCfg<D>::S * 32 * D * 2 + ChunkCfg<D>::W * ChunkCfg<D>::S * 8; }
 
-DecodeConfig decode_config(int d) {
+// Stage count: the largest multiple of the consumer count that fits next to the merge
+// buffers when `ctas_per_sm` CTAs share the SM's shared memory (1 KB per CTA is
+// reserved by the system), at most 6 stages per consumer.
+DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers) {
+    int c, ctas;
     switch (d) {
-        case 64: return {DecodeCfg<64>::W, DecodeCfg<64>::S, decode_smem<64>(), DecodeCfg<64>::CTAS};
-        case 128: return {DecodeCfg<128>::W, DecodeCfg<128>::S, decode_smem<128>(), DecodeCfg<128>::CTAS};
-        case 256: return {DecodeCfg<256>::W, DecodeCfg<256>::S, decode_smem<256>(), DecodeCfg<256>::CTAS};
-        default: return {0, 0, 0, 0};
+        case 64: c = DecodeCfg<64>::C; ctas = DecodeCfg<64>::CTAS; break;
+        case 128: c = DecodeCfg<128>::C; ctas = DecodeCfg<128>::CTAS; break;
+        case 256: c = DecodeCfg<256>::C; ctas = DecodeCfg<256>::CTAS; break;
+        default: return {0, 0, 0, 0, 0};
     }
+    if (consumers == 4 || consumers == 6 || consumers == 8) c = consumers;
+    if (ctas_per_sm > 0) ctas = ctas_per_sm;
+    const int comb_cols = std::min(8, (n_rep + 1) & ~1);
+    const int budget = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
+    if (stages <= 0) {
+        stages = 6 * c;
+        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols) > budget) stages -= c;
+    }
+    stages = std::max(c, (stages / c) * c);
+    return {c, stages, decode_smem_bytes(d, c, stages, comb_cols), ctas, comb_cols};
 }
 ChunkConfig chunk_config(int d) {
     switch (d) {
@@ -688,8 +781,12 @@ ChunkConfig chunk_config(int d) {
 }
 
 template <int D, bool BF16> static cudaError_t set_attrs() {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, DecodeCfg<D>::W, DecodeCfg<D>::S, BF16>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+    cudaError_t e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 4, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 6, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 8, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(chunk_kernel<D, ChunkCfg<D>::NT, ChunkCfg<D>::W, ChunkCfg<D>::S, BF16>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_smem<D>());
@@ -715,17 +812,37 @@ cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-template <int D, bool BF16>
-static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, cudaStream_t st) {
-    decode_kernel<D, DecodeCfg<D>::W, DecodeCfg<D>::S, BF16><<<n_ctas, DecodeCfg<D>::W * 32, decode_smem<D>(), st>>>(map, a);
-    return cudaGetLastError();
+template <int D, int C, bool BF16>
+static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int smem, bool pdl, cudaStream_t st) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)n_ctas);
+    cfg.blockDim = dim3((C + 1) * 32);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, decode_kernel<D, C, BF16>, map, a);
 }
 
-cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, bool bf16, cudaStream_t st) {
+template <int D, bool BF16>
+static cudaError_t launch_decode_c(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, cudaStream_t st) {
+    switch (consumers) {
+        case 4: return launch_decode_t<D, 4, BF16>(map, a, n_ctas, smem, pdl, st);
+        case 6: return launch_decode_t<D, 6, BF16>(map, a, n_ctas, smem, pdl, st);
+        case 8: return launch_decode_t<D, 8, BF16>(map, a, n_ctas, smem, pdl, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, bool bf16, cudaStream_t st) {
+    if (a.n_stages < consumers || a.n_stages % consumers != 0) return cudaErrorInvalidValue;
     switch (a.geo.d) {
-        case 64: return bf16 ? launch_decode_t<64, true>(map, a, n_ctas, st) : launch_decode_t<64, false>(map, a, n_ctas, st);
-        case 128: return bf16 ? launch_decode_t<128, true>(map, a, n_ctas, st) : launch_decode_t<128, false>(map, a, n_ctas, st);
-        case 256: return bf16 ? launch_decode_t<256, true>(map, a, n_ctas, st) : launch_decode_t<256, false>(map, a, n_ctas, st);
+        case 64: return bf16 ? launch_decode_c<64, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<64, false>(map, a, n_ctas, consumers, smem, pdl, st);
+        case 128: return bf16 ? launch_decode_c<128, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<128, false>(map, a, n_ctas, consumers, smem, pdl, st);
+        case 256: return bf16 ? launch_decode_c<256, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<256, false>(map, a, n_ctas, consumers, smem, pdl, st);
         default: return cudaErrorInvalidValue;
     }
 }

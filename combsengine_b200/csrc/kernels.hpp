@@ -58,6 +58,9 @@ struct DecodeArgs {
     int32_t* status;
     int32_t window;
     float scale_log2;
+    int32_t n_stages;   // stages of the CTA's TMA ring
+    int32_t comb_cols;  // query columns kept in the merge buffers (n_rep rounded up to even)
+    int32_t kv_dep;     // 1: the previous launch in the stream wrote this layer's pages
 };
 
 struct ChunkArgs {
@@ -93,13 +96,13 @@ struct GenericArgs {
 };
 
 // Decode kernel configuration for a head_dim (0 warps = not supported by the fast path).
-struct DecodeConfig { int warps, stages, smem_bytes, ctas_per_sm; };
-DecodeConfig decode_config(int d);
+struct DecodeConfig { int consumers, stages, smem_bytes, ctas_per_sm, comb_cols; };
+DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers);
 struct ChunkConfig { int warps, stages, smem_bytes, cols_per_item; };
 ChunkConfig chunk_config(int d);
 
 cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
-cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, bool bf16, cudaStream_t st);
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st);
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process

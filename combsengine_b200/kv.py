@@ -271,8 +271,10 @@ class KVArena:
         check(self._lib.cbkv_profile_read(self._h, C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
-    def set_decode_ctas_per_sm(self, n: int) -> None:
-        check(self._lib.cbkv_set_decode_ctas_per_sm(self._h, n))
+    def set_decode_tuning(self, ctas_per_sm: int = 0, stages: int = 0, consumers: int = 0, max_ctas: int = 0,
+                          overlap_launches: bool = True) -> None:
+        check(self._lib.cbkv_set_decode_tuning(self._h, ctas_per_sm, stages, consumers, max_ctas,
+                                               1 if overlap_launches else 0))
 
     def debug_decode_plan(self, window: int, n_ctas: int) -> dict:
         cap = 8 + 2 * n_ctas + 8 * (self.n_kv_heads * 4096 + 8)

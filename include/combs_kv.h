@@ -179,9 +179,13 @@ int64_t cbkv_launch_count(void);
  * cbkv_profile_read returns their summed duration and count and clears them. */
 int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on);
 int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches);
-/* Tuning knob for measurements: CTAs per SM of the decode kernel (0 = default). */
-int32_t cbkv_set_decode_ctas_per_sm(cbkv_arena* arena, int32_t n);
-
+/* Tuning knobs for measurements and tests (0 = built-in default): CTAs per SM of the
+ * decode kernel, stages of its TMA ring (rounded down to a multiple of the consumer
+ * count), consumer warps per CTA (4, 6 or 8), an upper bound on the CTAs launched,
+ * and whether consecutive decode launches may overlap (programmatic dependent
+ * launch; 1 = default). */
+int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
+                               int32_t max_ctas, int32_t overlap_launches);
 
 /* ---- test hooks (host only, no device is touched) --------------------------- */
 

@@ -27,13 +27,15 @@ class Pair:
     """A CUDA arena and an oracle arena kept in lock-step."""
 
     def __init__(self, layers, n_q, n_kv, d, max_seq_len, num_pages=0, page_size=16, windows=None, seed=0,
-                 shuffle_free_list=False, popn_refuses=True):
+                 shuffle_free_list=False, popn_refuses=True, tuning=None):
         self.layers, self.n_q, self.n_kv, self.d = layers, n_q, n_kv, d
         self.g = KVArena(layers, n_q, n_kv, d, max_seq_len, page_size, num_pages, windows,
                          sliding_popn_refuses=popn_refuses)
         # sliding layers live in pages on both sides so that page contents can be compared
         self.o = OracleArena(layers, n_kv, d, max_seq_len, page_size, num_pages, windows=windows, rolling=False, dtype="f16")
         self.windows = windows
+        if tuning:
+            self.g.set_decode_tuning(**tuning)
         self.rng = np.random.default_rng(seed)
         self.seqs = []
         if shuffle_free_list:

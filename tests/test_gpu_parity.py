@@ -42,6 +42,18 @@ def test_cfg2_qwen_batched_decode_scattered_pages(fused):
     p.assert_state_equal(pages="used")
 
 
+@pytest.mark.parametrize("consumers,stages,overlap", [(4, 4, True), (4, 8, False), (6, 6, True), (8, 8, True), (8, 16, False)])
+def test_decode_ring_is_reused_many_times(consumers, stages, overlap):
+    # few CTAs and a short TMA ring: every stage is refilled dozens of times per launch
+    p = Pair(2, 28, 4, 128, 2048, num_pages=700, shuffle_free_list=True, seed=consumers * 100 + stages,
+             tuning=dict(stages=stages, consumers=consumers, max_ctas=3, overlap_launches=overlap))
+    seqs = [p.new_seq() for _ in range(6)]
+    p.step(seqs, [int(x) for x in p.rng.integers(500, 1500, len(seqs))], check=False)
+    for _ in range(4):
+        p.step(seqs, [1] * len(seqs))
+    p.assert_state_equal(pages="used")
+
+
 def test_cfg3_gemma_windows_over_paged_kv():
     # 5 local : 1 global, d 256; window shortened so that it slides within the test
     windows = [96, 96, None, 96]
