@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -85,6 +88,8 @@ struct DeviceState {
     // host-buffer entry point staging
     uint8_t* io = nullptr;
     size_t io_cap = 0;
+    unsigned long long* dbg_buf = nullptr;  // CBKV_DEBUG bit 4: per-CTA timestamps of the last decode launch
+    int dbg_ctas = 0;
     // profiling
     bool profile = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof;
@@ -132,13 +137,20 @@ int32_t ensure_device(Arena* a) {
     return CBKV_OK;
 }
 
-int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D, int box_rows) {
+int debug_flags() {
+    static int f = -1;
+    if (f < 0) { const char* e = getenv("CBKV_DEBUG"); f = e ? atoi(e) : 0; }
+    return f;
+}
+
+int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D, int box_rows, bool linear = false) {
     cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {linear ? (cuuint32_t)D : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode_fn()(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims,
-                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             linear ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
     return CBKV_OK;
@@ -159,6 +171,10 @@ int32_t materialize(Arena* a, int layer, cudaStream_t st) {
         if (rc) return rc;
         rc = encode_map(&L.map_k16, bf16, L.base, rows, a->cfg.head_dim, 16);
         if (rc) return rc;
+        if (a->cfg.head_dim <= 256 && (debug_flags() & 2)) {
+            rc = encode_map(&L.map_lin, bf16, L.base, rows, a->cfg.head_dim, 32, true);
+            if (rc) return rc;
+        }
     }
     return CBKV_OK;
 }
@@ -353,8 +369,15 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
         args.n_stages = dc.stages; args.comb_cols = dc.comb_cols;
         args.kv_dep = d->last_kv_writer == layer ? 1 : 0;
+        args.debug = debug_flags();
+        if (args.debug & 4) {
+            if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
+            CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
+            args.dbg_buf = d->dbg_buf;
+            d->dbg_ctas = pd->host.n_ctas;
+        }
         ProfScope ps(d, st);
-        CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st));
+        CU_TRY(launch_decode((args.debug & 2) ? L.map_lin : L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st));
         g_launches++;
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
@@ -631,6 +654,28 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         float ms = 0;
         CU_TRY(cudaEventElapsedTime(&ms, d->prof[i].first, d->prof[i].second));
         sum += ms;
+    }
+    if ((debug_flags() & 4) && d->dbg_buf && d->dbg_ctas > 0 && d->dbg_ctas <= 4096) {
+        std::vector<unsigned long long> h((size_t)d->dbg_ctas * 16);
+        cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
+        unsigned long long t0 = ~0ull;
+        for (int c = 0; c < d->dbg_ctas; c++) if (h[(size_t)c * 16]) t0 = std::min(t0, h[(size_t)c * 16]);
+        const char* names[8] = {"entry", "rows_resolved", "first_round_issued", "q_loaded", "first_tile_ready", "last_piece_arrived", "merger_exit", "producer_done"};
+        for (int s2 = 0; s2 < 8; s2++) {
+            double mn = 1e18, mx = 0, av = 0; int cnt = 0;
+            for (int c = 0; c < d->dbg_ctas; c++) { unsigned long long v = h[(size_t)c * 16 + s2]; if (!v) continue; double x = (double)(v - t0) * 1e-3; mn = std::min(mn, x); mx = std::max(mx, x); av += x; cnt++; }
+            if (cnt) fprintf(stderr, "[cbkv timeline] %-22s min %7.2f avg %7.2f max %7.2f us (%d CTAs)\n", names[s2], mn, av / cnt, mx, cnt);
+        }
+        std::vector<int> order(d->dbg_ctas);
+        for (int c = 0; c < d->dbg_ctas; c++) order[c] = c;
+        std::sort(order.begin(), order.end(), [&](int x, int y) { return h[(size_t)x * 16 + 6] > h[(size_t)y * 16 + 6]; });
+        auto us = [&](int c, int s2) { return h[(size_t)c * 16 + s2] ? (double)(h[(size_t)c * 16 + s2] - t0) * 1e-3 : -1.0; };
+        for (int i = 0; i < d->dbg_ctas; i += (i < 8 ? 1 : d->dbg_ctas / 8)) {
+            int c = order[i];
+            fprintf(stderr, "[cbkv cta] rank %3d cta %3d sm %3llu tiles %3llu pieces %llu merges %llu parts %llu | first_tile %.1f prod_done %.1f last_piece %.1f exit %.1f\n",
+                    i, c, h[(size_t)c * 16 + 11], h[(size_t)c * 16 + 12], h[(size_t)c * 16 + 8], h[(size_t)c * 16 + 9], h[(size_t)c * 16 + 10],
+                    us(c, 4), us(c, 7), us(c, 5), us(c, 6));
+        }
     }
     *total_ms = sum;
     *launches = (int64_t)d->prof_used;

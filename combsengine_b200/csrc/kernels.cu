@@ -307,18 +307,75 @@ __device__ __forceinline__ void consumer_sync(int nthreads) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// measurement only (debug bit 4): per-CTA timestamps, 8 slots each
+__device__ __forceinline__ void stamp(const DecodeArgs& a, int slot) {
+    if ((a.debug & 4) && a.dbg_buf) a.dbg_buf[(size_t)blockIdx.x * 16 + slot] = global_ns();
+}
+
+constexpr int ROWS_CAP = 512;  // tiles whose rows are resolved per batch (a multiple of the producer round)
+constexpr int SEG_CAP = 64;    // segments of a CTA's range kept in shared memory
+
+// Merge the partial results of one segment (log-sum-exp combine) and store its output.
+// Thread r of T takes every T-th (column, 4 d-values) item; the loads of up to eight
+// parts are issued together, so an item costs one round trip to memory.
+template <int D, bool BF16>
+__device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int nparts, uint16_t* out_row, int n_rep, int r, int T) {
+    constexpr int PER_COL = D / 4;
+    for (int idx = r; idx < n_rep * PER_COL; idx += T) {
+        const int col = idx / PER_COL, j4 = idx - col * PER_COL;
+        float M = -INFINITY, L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int p0 = 0; p0 < nparts; p0 += 8) {
+            float2 ml[8];
+            float4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const bool ok = p0 + q < nparts;
+                const size_t rec = (size_t)(base + p0 + (ok ? q : 0)) * 8 + col;
+                ml[q] = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + rec);
+                v[q] = __ldcg(reinterpret_cast<const float4*>(a.part_o + rec * D) + j4);
+                if (!ok) ml[q] = make_float2(-INFINITY, 0.f);
+            }
+            float Mnew = M;
+#pragma unroll
+            for (int q = 0; q < 8; q++) Mnew = fmaxf(Mnew, ml[q].x);
+            const float so = (M == -INFINITY) ? 0.f : exp2f(M - Mnew);
+            acc.x *= so; acc.y *= so; acc.z *= so; acc.w *= so;
+            L *= so;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float f = (ml[q].x == -INFINITY) ? 0.f : exp2f(ml[q].x - Mnew);
+                acc.x += f * v[q].x; acc.y += f * v[q].y; acc.z += f * v[q].z; acc.w += f * v[q].w;
+                L += f * ml[q].y;
+            }
+            M = Mnew;
+        }
+        const float inv = 1.f / L;
+        uint2 pk;
+        pk.x = pack2<BF16>(acc.x * inv, acc.y * inv);
+        pk.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out_row + col * D + j4 * 4) = pk;
+    }
+}
+
+// Warp roles: 0 = producer, 1..C = consumers, C+1 = merger.
 template <int D, int C, bool BF16>
-__global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
+__global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
     constexpr uint32_t UNIT = 32u * D * 2u;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int NS = a.n_stages;            // multiple of C (checked by the host)
-    const int R = NS < 8 ? NS : 8;        // producer lanes per round; R <= NS keeps a round free of self-dependencies
+    const int R = NS < 8 ? 4 : 8;         // producer lanes per round; R <= NS keeps a round free of self-dependencies
     const int ccols = a.comb_cols;
-    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [C][ccols][D]
-    float* comb_ml = comb_o + (size_t)C * ccols * D;                          // [C][8][2]
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + C * 16);      // [NS]
-    uint64_t* bar_empty = bar_full + NS;                                      // [NS]
-    int* flag = reinterpret_cast<int*>(bar_empty + NS);                       // [0] merge ticket, [1] failure
+    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [2][C][ccols][D]
+    float* comb_ml = comb_o + (size_t)2 * C * ccols * D;                      // [2][C][8][2]
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + 2 * C * 16);  // [NS] tile landed
+    uint64_t* bar_empty = bar_full + NS;                                      // [NS] tile consumed
+    uint64_t* bar_cfull = bar_empty + NS;                                     // [2] all consumers stored their states
+    uint64_t* bar_cempty = bar_cfull + 2;                                     // [2] merger is done with the buffer
+    int* flag = reinterpret_cast<int*>(bar_cempty + 2);                       // [1] a warp gave up
+    int* rows = flag + 4;                                                     // [ROWS_CAP] first arena row of each tile
+    int* segtab = rows + ROWS_CAP;                                            // [SEG_CAP][3] unit begin, first page, table offset
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
@@ -328,52 +385,90 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
     }
     const int u0 = a.cta_unit_begin[cta], u1 = a.cta_unit_begin[cta + 1];
     if (u0 >= u1) return;
+    if (tid == 0) stamp(a, 0);
     const int ntiles = u1 - u0;
     const uint32_t ring = smem_u32(smem);
     const uint32_t full0 = smem_u32(bar_full), empty0 = smem_u32(bar_empty);
+    const uint32_t cfull0 = smem_u32(bar_cfull), cempty0 = smem_u32(bar_cempty);
+    const int Hkv = a.geo.n_kv;
+    const int first_seg = a.cta_first_seg[cta];
     if (tid == 0) {
         for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(cfull0 + i * 8, C); mbar_init(cempty0 + i * 8, 1); }
         flag[0] = 0; flag[1] = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
+    // the segments this range can touch: one round of independent loads
+    const int nseg_tab = min(SEG_CAP, a.n_segs - first_seg);
+    for (int i = tid; i < nseg_tab; i += (C + 2) * 32) {
+        const int sg = first_seg + i;
+        segtab[i * 3 + 0] = a.seg_unit_begin[sg];
+        segtab[i * 3 + 1] = a.seg_page_lo[sg];
+        segtab[i * 3 + 2] = a.step.seq_meta[sg / Hkv].tbl_off;
+    }
     __syncthreads();
     pdl_launch_dependents();
-    const int Hkv = a.geo.n_kv;
-    const int first_seg = a.cta_first_seg[cta];
+
+    // Physical rows of the CTA's tiles through the block table: one more round of loads.
+    auto resolve_rows = [&](int from, int to, int t0, int nthreads) {
+        for (int n = from + t0; n < to; n += nthreads) {
+            const int u = u0 + n;
+            int i = 0;
+            while (i + 1 < nseg_tab && segtab[(i + 1) * 3] <= u) i++;
+            int sg = first_seg + i, sub = segtab[i * 3], plo = segtab[i * 3 + 1], toff = segtab[i * 3 + 2];
+            if (i + 1 == nseg_tab && sg + 1 < a.n_segs && a.seg_unit_begin[sg + 1] <= u) {
+                // range longer than the table (many tiny sequences): search the global arrays
+                int lo = sg, hi = a.n_segs - 1;
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (a.seg_unit_begin[mid] <= u) lo = mid; else hi = mid - 1;
+                }
+                sg = lo; sub = a.seg_unit_begin[lo]; plo = a.seg_page_lo[lo]; toff = a.step.seq_meta[lo / Hkv].tbl_off;
+            }
+            const int h = sg % Hkv;
+            int phys = a.step.tables[toff + plo + (u - sub)];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            rows[n % ROWS_CAP] = (phys * Hkv + h) * 32;
+        }
+    };
+    resolve_rows(0, min(ntiles, ROWS_CAP), tid, (C + 2) * 32);
+    __syncthreads();
+    if (tid == 0) stamp(a, 1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         // The pages read here were written by earlier steps; only when the previous
         // launch wrote this same layer must it be waited for.
         if (a.kv_dep) pdl_wait();
-        int seg = first_seg;  // per-lane scan position (monotonic)
-        auto lookup = [&](int n) -> int {
-            if (lane >= R || n >= ntiles) return -1;
-            const int u = u0 + n;
-            while (u >= a.seg_unit_begin[seg + 1]) seg++;
-            const int b = seg / Hkv, h = seg - b * Hkv;
-            const int lp = a.seg_page_lo[seg] + (u - a.seg_unit_begin[seg]);
-            int phys = a.step.tables[a.step.seq_meta[b].tbl_off + lp];
-            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-            return (phys * Hkv + h) * 32;
-        };
-        int row0 = lookup(lane);
         bool failed = false;
         int issued_end = 0;
 #pragma unroll 1
         for (int base = 0; base < ntiles && !failed; base += R) {
-            const int row0_next = lookup(base + R + lane);  // in flight while this round waits for free stages
+            if (base > 0 && base % ROWS_CAP == 0) {  // long ranges: next batch of rows (all tiles before `base` are issued)
+                __syncwarp();
+                resolve_rows(base, min(ntiles, base + ROWS_CAP), lane, 32);
+                __syncwarp();
+            }
             const int n = base + lane;
             if (lane < R && n < ntiles) {
                 const int st = n % NS;
+                const int row0 = rows[n % ROWS_CAP];
                 if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, ((n / NS) - 1) & 1)) failed = true;
-                if (!failed) issue_tile<D>(&tmap, ring + st * UNIT, full0 + st * 8, row0);
+                if (!failed) {
+                    if (a.debug & 2) {  // measurement only: one unswizzled box per tile (math would be wrong)
+                        mbar_expect_tx(full0 + st * 8, UNIT);
+                        tma_load_2d(ring + st * UNIT, &tmap, 0, row0, full0 + st * 8);
+                    } else {
+                        issue_tile<D>(&tmap, ring + st * UNIT, full0 + st * 8, row0);
+                    }
+                }
             }
             failed = __any_sync(0xffffffffu, failed);
             if (!failed) issued_end = min(ntiles, base + R);
-            row0 = row0_next;
+            if (base == 0 && lane == 0) stamp(a, 2);
         }
+        if (lane == 0) stamp(a, 7);
         if (failed) {
             if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             // wait (bounded) for the copies still in flight before leaving
@@ -383,15 +478,128 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
         return;
     }
 
-    // ---------------------------------------------------------------- consumers
-    const int cw = warp - 1, ctid = tid - 32, g = lane >> 2, t = lane & 3;
     const int n_rep = a.geo.n_rep;
-    pdl_wait();  // q, k_new, v_new and the scratch come from earlier work in the stream
-    Piece cur = load_piece(a, first_seg);
+    if (warp == C + 1) {
+        // -------------------------------------------------------------- merger
+        // Combines the consumers' states of each piece, writes the output (or a partial
+        // plus a ticket; the last ticket holder merges the segment's partials), and hands
+        // the buffer back.  The consumers never wait on global memory.
+        pdl_wait();  // out and the scratch are shared with earlier launches
+        int seg = first_seg, pb = u0, k = 0;
+        int dbg_merges = 0, dbg_parts = 0;
+        int final_merge = 0, final_seg = 0;
+#pragma unroll 1
+        while (pb < u1) {
+            const int pe = min(u1, a.seg_unit_begin[seg + 1]);
+            const int b = seg / Hkv, h = seg - b * Hkv;
+            const int tok_off = a.step.seq_meta[b].tok_off;
+            const int nparts = a.seg_nparts[seg];
+            const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
+            const int buf = k & 1;
+            if (!mbar_wait_bounded(cfull0 + buf * 8, (k >> 1) & 1, 400000000ull)) {
+                if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+                break;
+            }
+            if (pe >= u1 && lane == 0) stamp(a, 5);
+            const float* co = comb_o + (size_t)buf * C * ccols * D;
+            const float* cml = comb_ml + buf * C * 16;
+            uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
+            // lane owns 4 consecutive d-values (per pass of 128) of every query column
+            constexpr int PASSES = (D + 127) / 128;
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ps++) {
+                const int j4 = ps * 32 + lane;  // float4 index within a row of D
+                if (j4 * 4 < D) {
+#pragma unroll
+                    for (int col = 0; col < 8; col++) {
+                        if (col < n_rep) {
+                            float M = -INFINITY;
+#pragma unroll
+                            for (int ww = 0; ww < C; ww++) M = fmaxf(M, cml[(ww * 8 + col) * 2]);
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                            float ls = 0.f;
+#pragma unroll
+                            for (int ww = 0; ww < C; ww++) {
+                                const float mw = cml[(ww * 8 + col) * 2];
+                                const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+                                const float4 v = *reinterpret_cast<const float4*>(co + ((size_t)ww * ccols + col) * D + j4 * 4);
+                                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+                                ls += f * cml[(ww * 8 + col) * 2 + 1];
+                            }
+                            if (nparts == 1) {
+                                const float inv = 1.f / ls;
+                                uint2 pk;
+                                pk.x = pack2<BF16>(acc.x * inv, acc.y * inv);
+                                pk.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+                                *reinterpret_cast<uint2*>(out_row + col * D + j4 * 4) = pk;
+                            } else {
+                                *reinterpret_cast<float4*>(a.part_o + ((size_t)slot * 8 + col) * D + j4 * 4) = acc;
+                                if (j4 == 0) *reinterpret_cast<float2*>(a.part_ml + ((size_t)slot * 8 + col) * 2) = make_float2(M, ls);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cempty0 + buf * 8);  // the consumers may store the next piece here
+            if (nparts > 1) {
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence();  // the warp's partial (ordered before by __syncwarp) becomes visible before the ticket
+                    const int ticket = atomicAdd(a.seg_counter + seg, 1);
+                    last = ticket == nparts - 1;
+                    if (last) { a.seg_counter[seg] = 0; __threadfence(); }  // ready for the next launch; acquire the others' partials
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    dbg_merges++; dbg_parts += nparts;
+                    if (pe >= u1) {
+                        final_merge = 1;  // the idle consumers help with the CTA's last piece (below)
+                        final_seg = seg;
+                    } else {
+                        merge_parts<D, BF16>(a, a.seg_part_base[seg], nparts, out_row, n_rep, lane, 32);
+                    }
+                }
+            }
+            k++;
+            seg++;
+            pb = pe;
+        }
+        // tell the consumers whether the last piece's segment is theirs to merge too
+        if (lane == 0) { flag[2] = final_merge; flag[3] = final_seg; }
+        __syncwarp();
+        consumer_sync((C + 1) * 32);
+        if (final_merge) {
+            const int b = final_seg / Hkv, h = final_seg - b * Hkv;
+            uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
+                                ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
+            merge_parts<D, BF16>(a, a.seg_part_base[final_seg], a.seg_nparts[final_seg], out_row, n_rep, C * 32 + lane, (C + 1) * 32);
+        }
+        if (lane == 0) {
+            stamp(a, 6);
+            if ((a.debug & 4) && a.dbg_buf) {
+                unsigned smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 8] = (unsigned long long)k;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 9] = (unsigned long long)dbg_merges;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 10] = (unsigned long long)dbg_parts;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 11] = (unsigned long long)smid;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 12] = (unsigned long long)ntiles;
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int cw = warp - 1, g = lane >> 2, t = lane & 3;
+    Piece cur = load_piece(a, first_seg);  // plan and block tables were uploaded by a copy: always visible
+    pdl_wait();  // q, k_new and v_new come from earlier work in the stream
     uint32_t qf[1][D / 16][2];
     load_q_frags<D>(a, cur, g, t, qf);
+    if (tid == 32) stamp(a, 3);
     bool failed = false;
-    int seg = first_seg, pb = u0;
+    int seg = first_seg, pb = u0, k = 0;
+    bool first_tile = true;
 #pragma unroll 1
     while (pb < u1) {
         const int pe = min(u1, cur.se);
@@ -416,8 +624,9 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
                 failed = true;
                 if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             }
+            if (first_tile && tid == 32) { stamp(a, 4); first_tile = false; }
             const int lp = cur.page_lo + (u - cur.sb);
-            if (!failed) {
+            if (!failed && !(a.debug & 1)) {
                 if (a.k_new != nullptr && lp == cur.page_last) {
                     // fused append: put the new K/V row into the tile just fetched and into its page
                     const int slot = cur.q_pos & 15;
@@ -444,14 +653,21 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
             if (lane == 0) mbar_arrive(empty0 + st * 8);  // the stage may be refilled
         }
 
-        // ---- merge the consumer warps' states for this piece
+        // ---- hand this warp's state for the piece to the merger (double-buffered)
+        const int buf = k & 1;
+        if (*reinterpret_cast<volatile int*>(flag + 1)) failed = true;  // another warp gave up: stop waiting
+        if (k >= 2 && !failed && !mbar_wait_bounded(cempty0 + buf * 8, ((k >> 1) - 1) & 1, 400000000ull)) {
+            failed = true;
+            if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+        }
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 4);
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 8);
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 16);
         }
-        float* co = comb_o + (size_t)cw * ccols * D;
+        float* co = comb_o + ((size_t)buf * C + cw) * ccols * D;
+        float* cml = comb_ml + (buf * C + cw) * 16;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
             if (2 * t < ccols) {
@@ -464,62 +680,12 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
             }
         }
         if (g == 0) {
-            comb_ml[(cw * 8 + 2 * t) * 2 + 0] = m[0][0]; comb_ml[(cw * 8 + 2 * t) * 2 + 1] = l[0][0];
-            comb_ml[(cw * 8 + 2 * t + 1) * 2 + 0] = m[0][1]; comb_ml[(cw * 8 + 2 * t + 1) * 2 + 1] = l[0][1];
+            cml[(2 * t) * 2 + 0] = m[0][0]; cml[(2 * t) * 2 + 1] = l[0][0];
+            cml[(2 * t + 1) * 2 + 0] = m[0][1]; cml[(2 * t + 1) * 2 + 1] = l[0][1];
         }
-        consumer_sync(C * 32);
-        const int nparts = a.seg_nparts[seg];
-        const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
-        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)cur.tok_off * a.geo.n_q + (size_t)cur.h * n_rep) * D;
-        for (int idx = ctid; idx < n_rep * D; idx += C * 32) {
-            int col = idx / D, j = idx - col * D;
-            float M = -INFINITY;
-#pragma unroll
-            for (int ww = 0; ww < C; ww++) M = fmaxf(M, comb_ml[(ww * 8 + col) * 2]);
-            float acc = 0.f, ls = 0.f;
-#pragma unroll
-            for (int ww = 0; ww < C; ww++) {
-                float mw = comb_ml[(ww * 8 + col) * 2];
-                float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-                acc += f * comb_o[((size_t)ww * ccols + col) * D + j];
-                ls += f * comb_ml[(ww * 8 + col) * 2 + 1];
-            }
-            if (nparts == 1) {
-                out_row[idx] = to_elem<BF16>(acc / ls);
-            } else {
-                a.part_o[((size_t)slot * 8 + col) * D + j] = acc;
-                if (j == 0) { a.part_ml[((size_t)slot * 8 + col) * 2] = M; a.part_ml[((size_t)slot * 8 + col) * 2 + 1] = ls; }
-            }
-        }
-        if (nparts > 1) {
-            __threadfence();
-            consumer_sync(C * 32);
-            if (ctid == 0) {
-                int ticket = atomicAdd(a.seg_counter + seg, 1);
-                flag[0] = (ticket == nparts - 1);
-                if (ticket == nparts - 1) a.seg_counter[seg] = 0;  // ready for the next launch
-            }
-            consumer_sync(C * 32);
-            if (flag[0]) {
-                __threadfence();
-                const int base = a.seg_part_base[seg];
-                for (int idx = ctid; idx < n_rep * D; idx += C * 32) {
-                    int col = idx / D, j = idx - col * D;
-                    float M = -INFINITY;
-                    for (int p = 0; p < nparts; p++) M = fmaxf(M, __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2));
-                    float acc = 0.f, ls = 0.f;
-                    for (int p = 0; p < nparts; p++) {
-                        float mp = __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2);
-                        float f = (mp == -INFINITY) ? 0.f : exp2f(mp - M);
-                        acc += f * __ldcg(a.part_o + ((size_t)(base + p) * 8 + col) * D + j);
-                        ls += f * __ldcg(a.part_ml + ((size_t)(base + p) * 8 + col) * 2 + 1);
-                    }
-                    out_row[idx] = to_elem<BF16>(acc / ls);
-                }
-            }
-        }
-        consumer_sync(C * 32);  // comb buffers and flag are reused by the next piece
-        if (flag[1]) failed = true;  // the producer gave up: stop waiting for tiles
+        __syncwarp();
+        if (lane == 0) mbar_arrive(cfull0 + buf * 8);
+        k++;
         seg++;
         pb = pe;
         if (more) {
@@ -527,6 +693,15 @@ __global__ void __launch_bounds__((C + 1) * 32) decode_kernel(const __grid_const
 #pragma unroll
             for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
         }
+    }
+    // idle now: if this CTA holds the last ticket of its final segment, help merge it
+    consumer_sync((C + 1) * 32);
+    if (flag[2]) {
+        const int fseg = flag[3];
+        const int b = fseg / Hkv, h = fseg - b * Hkv;
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
+                            ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
+        merge_parts<D, BF16>(a, a.seg_part_base[fseg], a.seg_nparts[fseg], out_row, n_rep, cw * 32 + lane, (C + 1) * 32);
     }
 }
 
@@ -739,7 +914,8 @@ template <> struct DecodeCfg<128> { static constexpr int C = 4, CTAS = 2; };
 template <> struct DecodeCfg<256> { static constexpr int C = 6, CTAS = 1; };
 
 static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols) {
-    return stages * 32 * d * 2 + consumers * comb_cols * d * 4 + consumers * 16 * 4 + stages * 16 + 16;
+    return stages * 32 * d * 2 + 2 * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 16 +
+           ROWS_CAP * 4 + SEG_CAP * 12;
 }
 
 template <int D> struct ChunkCfg;
@@ -816,7 +992,7 @@ template <int D, int C, bool BF16>
 static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int smem, bool pdl, cudaStream_t st) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)n_ctas);
-    cfg.blockDim = dim3((C + 1) * 32);
+    cfg.blockDim = dim3((C + 2) * 32);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];

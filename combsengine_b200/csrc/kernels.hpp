@@ -23,6 +23,7 @@ struct LayerArena {
     void* base = nullptr;
     CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
     CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile)
+    CUtensorMap map_lin; // measurement only: box 32 rows x d elems, no swizzle
 };
 
 struct StepDev {
@@ -61,6 +62,8 @@ struct DecodeArgs {
     int32_t n_stages;   // stages of the CTA's TMA ring
     int32_t comb_cols;  // query columns kept in the merge buffers (n_rep rounded up to even)
     int32_t kv_dep;     // 1: the previous launch in the stream wrote this layer's pages
+    unsigned long long* dbg_buf;  // measurement only: per-CTA timestamps
+    int32_t debug;      // measurement switches (0 in production): 1 = skip the math, 2 = one linear box per tile
 };
 
 struct ChunkArgs {
