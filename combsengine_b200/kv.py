@@ -294,6 +294,35 @@ class KVArena:
         return out
 
 
+def decode_attention_static(kv_pages: torch.Tensor, block_tables: torch.Tensor, seq_lens: Sequence[int],
+                            n_q_heads: int, n_kv_heads: int, head_dim: int, q: torch.Tensor,
+                            out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                            window: Optional[int] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Decode attention over caller-owned pages without any device allocation inside the library.
+
+    For callers that may not allocate while they run (the GPU's memory belongs to their
+    own pool, or the host process forbids late allocations): the kernel's working memory
+    is a fixed array in the library, shared by every call on the device, so calls must
+    not overlap on the GPU and sizes are capped (128 sequences, 1024 sequence x kv-head
+    pairs).  ``kv_pages`` is one layer ``[num_pages, n_kv, 2, 16, head_dim]``,
+    ``block_tables`` int32 ``[n_seqs, stride]`` on the device, ``seq_lens`` host integers
+    (cached tokens including the one being decoded), ``q``/``out`` ``[n_seqs, n_q, head_dim]``.
+    Pass ``out`` to keep even the output allocation on the caller's side.
+    """
+    lib = _lib.load()
+    n = len(seq_lens)
+    if out is None:
+        out = torch.empty_like(q)
+    lens = (C.c_int32 * n)(*[int(x) for x in seq_lens])
+    if block_tables.dtype != torch.int32 or not block_tables.is_contiguous() or not kv_pages.is_contiguous():
+        raise CbkvError(-4, "block_tables must be contiguous int32 and kv_pages contiguous")
+    check(lib.cbkv_decode_attention_static(
+        kv_pages.data_ptr(), kv_pages.shape[0], block_tables.data_ptr(), block_tables.shape[1], lens, n,
+        n_q_heads, n_kv_heads, head_dim, _DTYPES[kv_pages.dtype], q.data_ptr(), out.data_ptr(),
+        float(head_dim ** -0.5 if scale is None else scale), 0 if window is None else int(window), _stream_ptr(stream)))
+    return out
+
+
 def launch_count() -> int:
     """Kernel launches issued by the library in this process."""
     return _lib.load().cbkv_launch_count()

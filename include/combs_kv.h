@@ -140,6 +140,25 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
 int32_t cbkv_host_alloc(size_t bytes, void** out);
 int32_t cbkv_host_free(void* p);
 
+/* No counterpart in the reference.  Decode attention over pages the CALLER owns, for
+ * callers that must not allocate device memory while they run (a server that gave
+ * the whole GPU to its own pool at start-up, a plugin inside a host that forbids
+ * late allocations): nothing is allocated or freed, the kernel's working memory is a
+ * fixed ~4 MB array inside the library image.  Limits: at most 128 sequences and
+ * 1024 sequence x kv-head pairs per call, head_dim 64/128/256, at most 8 q heads per
+ * kv head, 16-token pages; larger problems return CBKV_ERR_ARG.
+ *   kv_pages      device, one layer's pages [num_pages][n_kv][2 (K,V)][16][head_dim]
+ *   block_tables  device, [n_seqs][table_stride] physical page ids
+ *   seq_lens_host HOST, [n_seqs]: cached tokens including the one being decoded
+ *   q, out        device, [n_seqs][n_q][head_dim]
+ * All calls on a device share the working memory: calls that overlap on the GPU
+ * race, so keep them on one stream or order them.  The first call on a device does a
+ * one-time set-up and should be made before any stream capture begins. */
+int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t num_pages, const int32_t* block_tables,
+                                     int32_t table_stride, const int32_t* seq_lens_host, int32_t n_seqs,
+                                     int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
+                                     const void* q, void* out, double scale, int64_t window, void* stream);
+
 /* ---- rollback / reset / counters ----------------------------------------- */
 
 /* KVCache::popn (kv.rs:807-835): *popped = tokens dropped; 0 = refused. */
