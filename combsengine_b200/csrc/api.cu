@@ -367,7 +367,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
         args.window = (int32_t)w; args.scale_log2 = scale_log2;
         DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
-        args.n_stages = dc.stages; args.comb_cols = dc.comb_cols;
+        args.n_stages = dc.stages; args.comb_cols = dc.comb_cols; args.comb_bufs = dc.comb_bufs;
         args.kv_dep = d->last_kv_writer == layer ? 1 : 0;
         args.debug = debug_flags();
         if (args.debug & 4) {

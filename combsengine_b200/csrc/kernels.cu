@@ -367,14 +367,15 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     const int NS = a.n_stages;            // multiple of C (checked by the host)
     const int R = NS < 8 ? 4 : 8;         // producer lanes per round; R <= NS keeps a round free of self-dependencies
     const int ccols = a.comb_cols;
-    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [2][C][ccols][D]
-    float* comb_ml = comb_o + (size_t)2 * C * ccols * D;                      // [2][C][8][2]
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + 2 * C * 16);  // [NS] tile landed
+    const int NB = a.comb_bufs;           // 1 or 2 state buffers between consumers and merger
+    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [NB][C][ccols][D]
+    float* comb_ml = comb_o + (size_t)NB * C * ccols * D;                     // [NB][C][8][2]
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + NB * C * 16); // [NS] tile landed
     uint64_t* bar_empty = bar_full + NS;                                      // [NS] tile consumed
     uint64_t* bar_cfull = bar_empty + NS;                                     // [2] all consumers stored their states
     uint64_t* bar_cempty = bar_cfull + 2;                                     // [2] merger is done with the buffer
-    int* flag = reinterpret_cast<int*>(bar_cempty + 2);                       // [1] a warp gave up
-    int* rows = flag + 4;                                                     // [ROWS_CAP] first arena row of each tile
+    int* flag = reinterpret_cast<int*>(bar_cempty + 2);                       // [1] a warp gave up, [2] deferred merges, [4..7] their segments
+    int* rows = flag + 8;                                                     // [ROWS_CAP] first arena row of each tile
     int* segtab = rows + ROWS_CAP;                                            // [SEG_CAP][3] unit begin, first page, table offset
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -393,9 +394,10 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     const int Hkv = a.geo.n_kv;
     const int first_seg = a.cta_first_seg[cta];
     if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
         for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
         for (int i = 0; i < 2; i++) { mbar_init(cfull0 + i * 8, C); mbar_init(cempty0 + i * 8, 1); }
-        flag[0] = 0; flag[1] = 0;
+        flag[0] = 0; flag[1] = 0; flag[2] = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         pdl_wait();  // out and the scratch are shared with earlier launches
         int seg = first_seg, pb = u0, k = 0;
         int dbg_merges = 0, dbg_parts = 0;
-        int final_merge = 0, final_seg = 0;
+        int deferred[4] = {0, 0, 0, 0}, n_deferred = 0;
 #pragma unroll 1
         while (pb < u1) {
             const int pe = min(u1, a.seg_unit_begin[seg + 1]);
@@ -495,8 +497,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             const int tok_off = a.step.seq_meta[b].tok_off;
             const int nparts = a.seg_nparts[seg];
             const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
-            const int buf = k & 1;
-            if (!mbar_wait_bounded(cfull0 + buf * 8, (k >> 1) & 1, 400000000ull)) {
+            const int buf = NB == 2 ? (k & 1) : 0, use = NB == 2 ? (k >> 1) : k;
+            if (!mbar_wait_bounded(cfull0 + buf * 8, use & 1, 400000000ull)) {
                 if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
                 break;
             }
@@ -553,27 +555,29 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
                     dbg_merges++; dbg_parts += nparts;
-                    if (pe >= u1) {
-                        final_merge = 1;  // the idle consumers help with the CTA's last piece (below)
-                        final_seg = seg;
-                    } else {
-                        merge_parts<D, BF16>(a, a.seg_part_base[seg], nparts, out_row, n_rep, lane, 32);
-                    }
+                    // Merging is deferred to the end of the CTA, where the consumer warps are idle
+                    // and help (below); only a fifth segment in one CTA is merged here and now.
+                    if (n_deferred < 4) deferred[n_deferred++] = seg;
+                    else merge_parts<D, BF16>(a, a.seg_part_base[seg], nparts, out_row, n_rep, lane, 32);
                 }
             }
             k++;
             seg++;
             pb = pe;
         }
-        // tell the consumers whether the last piece's segment is theirs to merge too
-        if (lane == 0) { flag[2] = final_merge; flag[3] = final_seg; }
+        // hand the deferred segments to the whole CTA
+        if (lane == 0) {
+            flag[2] = n_deferred;
+            for (int i = 0; i < 4; i++) flag[4 + i] = deferred[i];
+        }
         __syncwarp();
         consumer_sync((C + 1) * 32);
-        if (final_merge) {
-            const int b = final_seg / Hkv, h = final_seg - b * Hkv;
+        for (int i = 0; i < n_deferred; i++) {
+            const int sg = deferred[i];
+            const int b = sg / Hkv, h = sg - b * Hkv;
             uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
                                 ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
-            merge_parts<D, BF16>(a, a.seg_part_base[final_seg], a.seg_nparts[final_seg], out_row, n_rep, C * 32 + lane, (C + 1) * 32);
+            merge_parts<D, BF16>(a, a.seg_part_base[sg], a.seg_nparts[sg], out_row, n_rep, C * 32 + lane, (C + 1) * 32);
         }
         if (lane == 0) {
             stamp(a, 6);
@@ -654,9 +658,9 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         }
 
         // ---- hand this warp's state for the piece to the merger (double-buffered)
-        const int buf = k & 1;
+        const int buf = NB == 2 ? (k & 1) : 0, use = NB == 2 ? (k >> 1) : k;
         if (*reinterpret_cast<volatile int*>(flag + 1)) failed = true;  // another warp gave up: stop waiting
-        if (k >= 2 && !failed && !mbar_wait_bounded(cempty0 + buf * 8, ((k >> 1) - 1) & 1, 400000000ull)) {
+        if (use >= 1 && !failed && !mbar_wait_bounded(cempty0 + buf * 8, (use - 1) & 1, 400000000ull)) {
             failed = true;
             if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
         }
@@ -694,14 +698,15 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
         }
     }
-    // idle now: if this CTA holds the last ticket of its final segment, help merge it
+    // idle now: help merge the segments whose last ticket this CTA drew
     consumer_sync((C + 1) * 32);
-    if (flag[2]) {
-        const int fseg = flag[3];
-        const int b = fseg / Hkv, h = fseg - b * Hkv;
+    const int n_deferred = flag[2];
+    for (int i = 0; i < n_deferred; i++) {
+        const int sg = flag[4 + i];
+        const int b = sg / Hkv, h = sg - b * Hkv;
         uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
                             ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
-        merge_parts<D, BF16>(a, a.seg_part_base[fseg], a.seg_nparts[fseg], out_row, n_rep, cw * 32 + lane, (C + 1) * 32);
+        merge_parts<D, BF16>(a, a.seg_part_base[sg], a.seg_nparts[sg], out_row, n_rep, cw * 32 + lane, (C + 1) * 32);
     }
 }
 
@@ -909,12 +914,12 @@ __global__ void generic_kernel(const GenericArgs a) {
 // ------------------------------------------------------------------ launchers
 // default consumer warps per CTA and CTAs per SM of the decode kernel
 template <int D> struct DecodeCfg;
-template <> struct DecodeCfg<64>  { static constexpr int C = 4, CTAS = 3; };
-template <> struct DecodeCfg<128> { static constexpr int C = 4, CTAS = 2; };
+template <> struct DecodeCfg<64>  { static constexpr int C = 6, CTAS = 1; };
+template <> struct DecodeCfg<128> { static constexpr int C = 6, CTAS = 1; };
 template <> struct DecodeCfg<256> { static constexpr int C = 6, CTAS = 1; };
 
-static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols) {
-    return stages * 32 * d * 2 + 2 * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 16 +
+static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols, int comb_bufs) {
+    return stages * 32 * d * 2 + comb_bufs * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 32 +
            ROWS_CAP * 4 + SEG_CAP * 12;
 }
 
@@ -927,25 +932,28 @@ template <int D> constexpr int chunk_smem() { return ChunkCfg<D>::W * ChunkCfg<D
 
 // Stage count: the largest multiple of the consumer count that fits next to the merge
 // buffers when `ctas_per_sm` CTAs share the SM's shared memory (1 KB per CTA is
-// reserved by the system), at most 6 stages per consumer.
+// reserved by the system), at most 8 stages per consumer.  Bytes in flight matter
+// more than a second merge buffer: the merge area is double-buffered only when that
+// costs no stage.
 DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers) {
     int c, ctas;
     switch (d) {
         case 64: c = DecodeCfg<64>::C; ctas = DecodeCfg<64>::CTAS; break;
         case 128: c = DecodeCfg<128>::C; ctas = DecodeCfg<128>::CTAS; break;
         case 256: c = DecodeCfg<256>::C; ctas = DecodeCfg<256>::CTAS; break;
-        default: return {0, 0, 0, 0, 0};
+        default: return {0, 0, 0, 0, 0, 0};
     }
     if (consumers == 4 || consumers == 6 || consumers == 8) c = consumers;
     if (ctas_per_sm > 0) ctas = ctas_per_sm;
     const int comb_cols = std::min(8, (n_rep + 1) & ~1);
     const int budget = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
     if (stages <= 0) {
-        stages = 6 * c;
-        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols) > budget) stages -= c;
+        stages = 8 * c;
+        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols, 1) > budget) stages -= c;
     }
     stages = std::max(c, (stages / c) * c);
-    return {c, stages, decode_smem_bytes(d, c, stages, comb_cols), ctas, comb_cols};
+    const int bufs = decode_smem_bytes(d, c, stages, comb_cols, 2) <= budget ? 2 : 1;
+    return {c, stages, decode_smem_bytes(d, c, stages, comb_cols, bufs), ctas, comb_cols, bufs};
 }
 ChunkConfig chunk_config(int d) {
     switch (d) {

@@ -61,6 +61,7 @@ struct DecodeArgs {
     float scale_log2;
     int32_t n_stages;   // stages of the CTA's TMA ring
     int32_t comb_cols;  // query columns kept in the merge buffers (n_rep rounded up to even)
+    int32_t comb_bufs;  // 1 or 2 merge buffers
     int32_t kv_dep;     // 1: the previous launch in the stream wrote this layer's pages
     unsigned long long* dbg_buf;  // measurement only: per-CTA timestamps
     int32_t debug;      // measurement switches (0 in production): 1 = skip the math, 2 = one linear box per tile
@@ -99,7 +100,7 @@ struct GenericArgs {
 };
 
 // Decode kernel configuration for a head_dim (0 warps = not supported by the fast path).
-struct DecodeConfig { int consumers, stages, smem_bytes, ctas_per_sm, comb_cols; };
+struct DecodeConfig { int consumers, stages, smem_bytes, ctas_per_sm, comb_cols, comb_bufs; };
 DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers);
 struct ChunkConfig { int warps, stages, smem_bytes, cols_per_item; };
 ChunkConfig chunk_config(int d);

@@ -205,7 +205,7 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
     args.status = reinterpret_cast<int32_t*>(S + kOffStatus);
     args.window = (int32_t)window;
     args.scale_log2 = (float)(scale * 1.4426950408889634);
-    args.n_stages = dc.stages; args.comb_cols = dc.comb_cols;
+    args.n_stages = dc.stages; args.comb_cols = dc.comb_cols; args.comb_bufs = dc.comb_bufs;
     args.kv_dep = 1;  // the pages are the caller's: assume the previous work in the stream wrote them
     args.dbg_buf = nullptr; args.debug = 0;
     e = launch_decode(map, args, pl.n_ctas, dc.consumers, dc.smem_bytes, /*pdl=*/false, dtype == CBKV_BF16, st);
