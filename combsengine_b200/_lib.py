@@ -42,6 +42,8 @@ PROTOTYPES = {
     "cbkv_attention": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_attention_host": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_decode_attention_static": (I32, [P, I64, P, I32, C.POINTER(I32), I32, I32, I32, I32, I32, P, P, F64, I64, P]),
+    "cbkv_attention_host_async": (I32, [P, I32, P, P, P, P, F64, I64, P]),
+    "cbkv_host_sync": (I32, [P]),
     "cbkv_host_alloc": (I32, [C.c_size_t, C.POINTER(P)]),
     "cbkv_host_free": (I32, [P]),
     "cbkv_popn": (I32, [P, I64, C.POINTER(I64)]),

@@ -88,6 +88,16 @@ struct DeviceState {
     // host-buffer entry point staging
     uint8_t* io = nullptr;
     size_t io_cap = 0;
+    // pipelined host-buffer entry point: copy streams, rotating staging slots
+    struct IoSlot {
+        uint8_t* dev = nullptr;
+        size_t cap = 0;
+        cudaEvent_t in_done = nullptr, k_done = nullptr, out_done = nullptr;
+        bool used = false;
+    };
+    IoSlot io_slots[4];
+    int io_cur = 0;
+    cudaStream_t h2d = nullptr, d2h = nullptr;
     unsigned long long* dbg_buf = nullptr;  // CBKV_DEBUG bit 4: per-CTA timestamps of the last decode launch
     int dbg_ctas = 0;
     // profiling
@@ -424,6 +434,11 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
         if (d->seg_counter) cudaFree(d->seg_counter);
         if (d->status) cudaFree(d->status);
         if (d->io) cudaFree(d->io);
+        for (auto& sl : d->io_slots) {
+            if (sl.dev) cudaFree(sl.dev);
+            if (sl.in_done) { cudaEventDestroy(sl.in_done); cudaEventDestroy(sl.k_done); cudaEventDestroy(sl.out_done); }
+        }
+        if (d->h2d) { cudaStreamDestroy(d->h2d); cudaStreamDestroy(d->d2h); }
         for (auto& p : d->prof) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
         delete d;
     }
@@ -537,6 +552,66 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
     if (rc) return rc;
     CU_TRY(cudaMemcpyAsync(out_host, od, qb, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
+    return CBKV_OK;
+}
+
+int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
+                                  const void* v_host, void* out_host, double scale, int64_t window, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (!q_host || !k_host || !v_host || !out_host) { set_error("null tensor"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    if (!d->h2d) {
+        CU_TRY(cudaStreamCreateWithFlags(&d->h2d, cudaStreamNonBlocking));
+        CU_TRY(cudaStreamCreateWithFlags(&d->d2h, cudaStreamNonBlocking));
+    }
+    const size_t qb = (size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2;
+    const size_t kb = (size_t)a->step_tokens * a->cfg.n_kv_heads * a->cfg.head_dim * 2;
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t need = 2 * up(qb) + 2 * up(kb);
+    DeviceState::IoSlot& sl = d->io_slots[d->io_cur];
+    d->io_cur = (d->io_cur + 1) % 4;
+    if (!sl.in_done) {
+        CU_TRY(cudaEventCreateWithFlags(&sl.in_done, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreateWithFlags(&sl.k_done, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreateWithFlags(&sl.out_done, cudaEventDisableTiming));
+    }
+    if (sl.used) CU_TRY(cudaEventSynchronize(sl.out_done));  // the slot's previous round trip is over
+    if (need > sl.cap) {
+        if (sl.dev) CU_TRY(cudaFree(sl.dev));
+        sl.cap = need * 2;
+        CU_TRY(cudaMalloc(&sl.dev, sl.cap));
+    }
+    uint8_t* qd = sl.dev;
+    uint8_t* od = qd + up(qb);
+    uint8_t* kd = od + up(qb);
+    uint8_t* vd = kd + up(kb);
+    CU_TRY(cudaMemcpyAsync(qd, q_host, qb, cudaMemcpyHostToDevice, d->h2d));
+    CU_TRY(cudaMemcpyAsync(kd, k_host, kb, cudaMemcpyHostToDevice, d->h2d));
+    CU_TRY(cudaMemcpyAsync(vd, v_host, kb, cudaMemcpyHostToDevice, d->h2d));
+    CU_TRY(cudaEventRecord(sl.in_done, d->h2d));
+    CU_TRY(cudaStreamWaitEvent(st, sl.in_done, 0));
+    rc = cbkv_attention(arena, layer, qd, kd, vd, od, scale, window, stream);
+    if (rc) return rc;
+    CU_TRY(cudaEventRecord(sl.k_done, st));
+    CU_TRY(cudaStreamWaitEvent(d->d2h, sl.k_done, 0));
+    CU_TRY(cudaMemcpyAsync(out_host, od, qb, cudaMemcpyDeviceToHost, d->d2h));
+    CU_TRY(cudaEventRecord(sl.out_done, d->d2h));
+    sl.used = true;
+    return CBKV_OK;
+}
+
+int32_t cbkv_host_sync(cbkv_arena* arena) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
+    if (!a->dev) return CBKV_OK;
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    for (auto& sl : d->io_slots)
+        if (sl.used) CU_TRY(cudaEventSynchronize(sl.out_done));
     return CBKV_OK;
 }
 

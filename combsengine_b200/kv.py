@@ -232,6 +232,19 @@ class KVArena:
                                             float(scale), 0 if window is None else int(window), _stream_ptr(stream)))
         return out
 
+    def attention_host_async(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                             scale: float, window: Optional[int] = None, stream=None) -> None:
+        """attention_host without the wait; `out` is valid after host_sync()."""
+        for t in (q, k, v, out):
+            if t.is_cuda or not t.is_contiguous() or t.dtype != self.dtype:
+                raise CbkvError(-4, "attention_host_async takes contiguous host tensors of the arena dtype")
+        check(self._lib.cbkv_attention_host_async(self._h, layer, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                  out.data_ptr(), float(scale), 0 if window is None else int(window),
+                                                  _stream_ptr(stream)))
+
+    def host_sync(self) -> None:
+        check(self._lib.cbkv_host_sync(self._h))
+
     # ---- counters / export
     def num_free_pages(self) -> int:
         return self._lib.cbkv_num_free_pages(self._h)

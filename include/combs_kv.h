@@ -137,6 +137,13 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
  * for it.  Buffers from cbkv_host_alloc are pinned and copy asynchronously. */
 int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
                             const void* v_host, void* out_host, double scale, int64_t window, void* stream);
+/* The same call without the wait: the copies run on the library's own copy streams
+ * so that layer l+1's inputs and layer l's output move while a kernel runs; `out_host`
+ * is valid after cbkv_host_sync.  Needs pinned buffers to overlap; up to four calls are
+ * in flight, a fifth waits for the oldest. */
+int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
+                                  const void* v_host, void* out_host, double scale, int64_t window, void* stream);
+int32_t cbkv_host_sync(cbkv_arena* arena);
 int32_t cbkv_host_alloc(size_t bytes, void** out);
 int32_t cbkv_host_free(void* p);
 

@@ -168,3 +168,18 @@ def test_host_buffer_entry_point_matches_device_one():
     g.begin_step([s[0]], [1])
     ref = g.attention(0, q.cuda(), k.cuda(), v.cuda(), 0.1).cpu()
     assert torch.equal(out, ref)
+    # pipelined variant: six calls in flight over four staging slots, outputs valid after host_sync
+    outs = [torch.empty_like(q).pin_memory() for _ in range(6)]
+    qs = [torch.randn(28 * 128).half().pin_memory() for _ in range(6)]
+    refs = []
+    for i in range(6):
+        s[0].popn(1)
+        g.begin_step([s[0]], [1])
+        g.attention_host_async(0, qs[i], k, v, outs[i], 0.1)
+    g.host_sync()
+    for i in range(6):
+        s[0].popn(1)
+        g.begin_step([s[0]], [1])
+        refs.append(g.attention(0, qs[i].cuda(), k.cuda(), v.cuda(), 0.1).cpu())
+    for o, r in zip(outs, refs):
+        assert torch.equal(o, r)
