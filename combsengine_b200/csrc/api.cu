@@ -76,6 +76,11 @@ struct DeviceState {
     bool chunk_plan_ok = false;
     ChunkPlan chunk_host;
     const int32_t* chunk_item_begin = nullptr;
+    bool tc_ok = false;       // the tcgen05 chunk kernel covers this geometry
+    int chunk_mode = 0;       // 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel
+    bool tile_plan_ok = false;
+    ChunkPlan tile_host;
+    const int32_t* tile_item_begin = nullptr;
     float* part_o = nullptr;
     float* part_ml = nullptr;
     size_t part_cap = 0;
@@ -138,6 +143,11 @@ int32_t ensure_device(Arena* a) {
         cudaError_t ke = kernels_init();
         if (ke != cudaSuccess) { delete d; set_error(std::string("kernels_init: ") + cudaGetErrorString(ke)); return CBKV_ERR_CUDA; }
         if (!encode_fn()) { delete d; set_error("cuTensorMapEncodeTiled not available from the driver"); return CBKV_ERR_CUDA; }
+        if (chunk_tc_supported(D)) {
+            ke = chunk_tc_init();
+            if (ke != cudaSuccess) { delete d; set_error(std::string("chunk_tc_init: ") + cudaGetErrorString(ke)); return CBKV_ERR_CUDA; }
+            d->tc_ok = true;
+        }
     }
     cudaError_t se = cudaMalloc(&d->status, sizeof(int32_t));
     if (se != cudaSuccess) { delete d; set_error(std::string("cudaMalloc: ") + cudaGetErrorString(se)); return CBKV_ERR_CUDA; }
@@ -219,6 +229,7 @@ int32_t slot_upload(DeviceState* d, const void* src, size_t bytes, cudaStream_t 
                 for (auto pp : arr) { p = *pp; fix(p); *pp = (const int32_t*)p; }
             }
             p = d->chunk_item_begin; fix(p); d->chunk_item_begin = (const int32_t*)p;
+            p = d->tile_item_begin; fix(p); d->tile_item_begin = (const int32_t*)p;
             cudaFreeHost(s.host);
             cudaFree(s.dev);
         }
@@ -242,6 +253,8 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->decode_plans.clear();
     d->chunk_plan_ok = false;
     d->chunk_item_begin = nullptr;
+    d->tile_plan_ok = false;
+    d->tile_item_begin = nullptr;
     d->step = StepDev{};
     const void* p = nullptr;
     int32_t rc = slot_upload(d, a->step_meta.data(), a->step_meta.size() * sizeof(SeqMeta), st, &p);
@@ -319,6 +332,24 @@ int32_t get_chunk_plan(Arena* a, cudaStream_t st) {
     return CBKV_OK;
 }
 
+int rep_slots_of(int n_rep) {
+    int rs = 1;
+    while (rs < n_rep) rs <<= 1;
+    return rs;
+}
+
+int32_t get_tile_plan(Arena* a, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    if (d->tile_plan_ok) return CBKV_OK;
+    build_chunk_tile_plan(*a, 128 / rep_slots_of(a->n_rep()), &d->tile_host);
+    const void* p = nullptr;
+    int32_t rc = slot_upload(d, d->tile_host.item_begin.data(), d->tile_host.item_begin.size() * sizeof(int32_t), st, &p);
+    if (rc) return rc;
+    d->tile_item_begin = (const int32_t*)p;
+    d->tile_plan_ok = true;
+    return CBKV_OK;
+}
+
 struct ProfScope {
     DeviceState* d;
     cudaStream_t st;
@@ -392,10 +423,23 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
     }
+    // tensor-core chunk kernel: worth it once the step has enough new tokens to fill 128-row tiles
+    const bool use_tc = d->fast && d->tc_ok && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
+    if (use_tc) {
+        int32_t rc = get_tile_plan(a, st);
+        if (rc) return rc;
+        ChunkArgs args{d->step, geom(a), d->tile_item_begin, d->tile_host.n_items, q, out, d->status, (int32_t)w, scale_log2,
+                       rep_slots_of(a->n_rep())};
+        ProfScope ps(d, st);
+        CU_TRY(launch_chunk_tc(L.map_k16, args, bf16, st));
+        g_launches++;
+        d->last_kv_writer = -1;
+        return CBKV_OK;
+    }
     if (d->fast) {
         int32_t rc = get_chunk_plan(a, st);
         if (rc) return rc;
-        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2};
+        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2, 0};
         ProfScope ps(d, st);
         CU_TRY(launch_chunk(L.map_kv, args, bf16, st));
         g_launches++;
@@ -778,6 +822,16 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
     d->decode_max_ctas = max_ctas;
     d->pdl = overlap_launches != 0;
     d->decode_plans.clear();  // the split depends on the CTA count
+    return CBKV_OK;
+}
+
+int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || mode < 0 || mode > 2) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64 and 128 with 16-token pages only"); return CBKV_ERR_ARG; }
+    dev_of(a)->chunk_mode = mode;
     return CBKV_OK;
 }
 

@@ -77,6 +77,7 @@ struct ChunkArgs {
     int32_t* status;
     int32_t window;
     float scale_log2;
+    int32_t rep_slots;  // tcgen05 kernel: q heads per kv head rounded up to a power of two (rows per token in a tile)
 };
 
 struct AppendArgs {
@@ -109,6 +110,10 @@ cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st);
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+// tcgen05 chunk kernel (prefill_tc.cu): head_dim 64 or 128; `map` is the 16-row box view
+bool chunk_tc_supported(int d);
+cudaError_t chunk_tc_init();
+cudaError_t launch_chunk_tc(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process
 
 }  // namespace cbkv

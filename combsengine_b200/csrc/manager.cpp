@@ -285,4 +285,17 @@ void build_chunk_plan(const Arena& a, int32_t cols_per_item, ChunkPlan* pl) {
     pl->n_items = (int32_t)items;
 }
 
+void build_chunk_tile_plan(const Arena& a, int32_t tokens_per_tile, ChunkPlan* pl) {
+    const int n = (int)a.step_meta.size();
+    pl->cols_per_item = tokens_per_tile;
+    pl->item_begin.assign((size_t)n + 1, 0);
+    int64_t items = 0;
+    for (int b = 0; b < n; b++) {
+        pl->item_begin[(size_t)b] = (int32_t)items;
+        items += (int64_t)a.cfg.n_kv_heads * ((a.step_meta[(size_t)b].snew + tokens_per_tile - 1) / tokens_per_tile);
+    }
+    pl->item_begin[(size_t)n] = (int32_t)items;
+    pl->n_items = (int32_t)items;
+}
+
 }  // namespace cbkv

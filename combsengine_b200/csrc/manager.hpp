@@ -111,5 +111,8 @@ void page_stats(const Seq* s, int64_t layers_materialized, cbkv_page_stats_t* ou
 // Builders used by the device layer (pure functions of the step state).
 void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, DecodePlan* plan);
 void build_chunk_plan(const Arena& a, int32_t cols_per_item, ChunkPlan* plan);
+// Work list of the tcgen05 chunk kernel: one item per (sequence, kv head, tile of
+// `tokens_per_tile` new tokens); `cols_per_item` records tokens_per_tile.
+void build_chunk_tile_plan(const Arena& a, int32_t tokens_per_tile, ChunkPlan* plan);
 
 }  // namespace cbkv

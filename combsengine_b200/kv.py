@@ -289,6 +289,10 @@ class KVArena:
         check(self._lib.cbkv_set_decode_tuning(self._h, ctas_per_sm, stages, consumers, max_ctas,
                                                1 if overlap_launches else 0))
 
+    def set_chunk_kernel(self, mode: int) -> None:
+        """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM chunk kernel."""
+        check(self._lib.cbkv_set_chunk_kernel(self._h, mode))
+
     def debug_decode_plan(self, window: int, n_ctas: int) -> dict:
         cap = 8 + 2 * n_ctas + 8 * (self.n_kv_heads * 4096 + 8)
         buf = (C.c_int32 * cap)()

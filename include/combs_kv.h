@@ -213,6 +213,11 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
 int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
                                int32_t max_ctas, int32_t overlap_launches);
 
+/* Which kernel runs a step that is not pure decode: 0 = the library chooses (tcgen05
+ * tiles once the step has at least 64 new tokens), 1 = the mma.sync kernel, 2 = the
+ * tcgen05/TMEM kernel (head_dim 64 or 128 only). */
+int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode);
+
 /* ---- test hooks (host only, no device is touched) --------------------------- */
 
 /* The bookkeeping half of cbkv_begin_step alone (no reference counterpart beyond

@@ -27,7 +27,7 @@ class Pair:
     """A CUDA arena and an oracle arena kept in lock-step."""
 
     def __init__(self, layers, n_q, n_kv, d, max_seq_len, num_pages=0, page_size=16, windows=None, seed=0,
-                 shuffle_free_list=False, popn_refuses=True, tuning=None):
+                 shuffle_free_list=False, popn_refuses=True, tuning=None, chunk_kernel=None):
         self.layers, self.n_q, self.n_kv, self.d = layers, n_q, n_kv, d
         self.g = KVArena(layers, n_q, n_kv, d, max_seq_len, page_size, num_pages, windows,
                          sliding_popn_refuses=popn_refuses)
@@ -36,6 +36,8 @@ class Pair:
         self.windows = windows
         if tuning:
             self.g.set_decode_tuning(**tuning)
+        if chunk_kernel is not None:
+            self.g.set_chunk_kernel(chunk_kernel)
         self.rng = np.random.default_rng(seed)
         self.seqs = []
         if shuffle_free_list:

