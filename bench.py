@@ -366,13 +366,77 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
+    """cfg4: chunked prefill into the paged cache, Llama-3-8B geometry (32 layers, 32/8/128),
+    8 prompts of 8192 tokens in 512-token chunks; per chunk and layer: append + causal attention
+    over the paged prefix plus the chunk.  A step = one full pass over the 16 chunks."""
+    import torch
+    from combsengine_b200 import KVArena, _lib
+
+    layers, n_q, n_kv, d, batch, prompt, chunk = 32, 32, 8, 128, 8, 8192, 512
+    if args.layers:
+        layers = args.layers
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    arena = KVArena(layers, n_q, n_kv, d, prompt + 64, 16, batch * (prompt // 16 + 4), device=local_rank)
+    arena.set_free_list(np.random.default_rng(0xC0B50004).permutation(arena.num_pages))
+    if args.chunk_kernel:
+        arena.set_chunk_kernel(args.chunk_kernel)
+    seqs = [arena.new_seq() for _ in range(batch)]
+    gen = torch.Generator(device=dev).manual_seed(0xC0B50004)
+    ntok = batch * chunk
+    q = torch.randn(ntok * n_q * d, device=dev, generator=gen).half()
+    k = torch.randn(ntok * n_kv * d, device=dev, generator=gen).half()
+    v = torch.randn(ntok * n_kv * d, device=dev, generator=gen).half()
+    out = torch.empty_like(q)
+    scale = d ** -0.5
+    stream = torch.cuda.current_stream()
+
+    def one_pass():
+        for c in range(prompt // chunk):
+            arena.begin_step(seqs, [chunk] * batch)
+            for layer in range(layers):
+                arena.attention(layer, q, k, v, scale, out=out)
+        for s in seqs:
+            s.popn(prompt)
+
+    for _ in range(max(1, args.warmup // 8)):
+        one_pass()
+    torch.cuda.synchronize()
+    passes = max(1, args.steps // 16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(passes):
+        one_pass()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / passes
+    assert arena.device_status() == 0
+    pairs = prompt * (prompt + 1) // 2
+    flops = 4.0 * n_q * d * pairs * layers * batch  # QK^T and PV over the causal pairs only
+    peaks = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks))["bf16_tflops"]) if os.path.exists(peaks) else 1590.0
+    tfl = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "chunked_prefill_attention_tokens_per_s", "value": batch * prompt / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": passes, "warmup": max(1, args.warmup // 8), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"cfg4 llama-3-8b geometry chunked prefill: {layers} layers, 32/8/128, 8 prompts x 8192 in 512-token "
+                               "chunks, append + causal attention over paged prefix + chunk",
+                   "chunk_kernel": {0: "auto (tcgen05)", 1: "mma.sync", 2: "tcgen05"}[args.chunk_kernel]},
+        "roofline": {"bound": "tensor", "achieved": tfl, "peak": peak, "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None,
+                     "algorithmic_flops_per_pass": flops},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg5"],
+    ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync kernel, 2 = tcgen05 kernel")
+    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload; cfg3 (windows, d=256) and cfg5 (shared prefix, long tails) on request")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
@@ -381,6 +445,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer than the 28 layers (small ncu case)")
     args = ap.parse_args()
+    if args.config == "cfg4":
+        return run_prefill(args, int(os.environ.get("RANK", "0")), 1, int(os.environ.get("LOCAL_RANK", "0")))
     select_config(args.config)
     if args.layers:
         global LAYERS, WINDOWS

@@ -424,14 +424,20 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         return CBKV_OK;
     }
     // tensor-core chunk kernel: worth it once the step has enough new tokens to fill 128-row tiles
-    const bool use_tc = d->fast && d->tc_ok && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
+    // (its softmax takes row maxima before scaling, which needs a positive scale)
+    const bool use_tc = d->fast && d->tc_ok && scale > 0 && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
     if (use_tc) {
         int32_t rc = get_tile_plan(a, st);
         if (rc) return rc;
         ChunkArgs args{d->step, geom(a), d->tile_item_begin, d->tile_host.n_items, q, out, d->status, (int32_t)w, scale_log2,
-                       rep_slots_of(a->n_rep())};
+                       rep_slots_of(a->n_rep()), nullptr};
+        if (debug_flags() & 8) {  // measurement only: per-role cycle counters of the first 4096 CTAs
+            if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
+            CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
+            if (d->tile_host.n_items <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
+        }
         ProfScope ps(d, st);
-        CU_TRY(launch_chunk_tc(L.map_k16, args, bf16, st));
+        CU_TRY(launch_chunk_tc(L.map_k16, L.map_kv, args, bf16, st));
         g_launches++;
         d->last_kv_writer = -1;
         return CBKV_OK;
@@ -439,7 +445,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     if (d->fast) {
         int32_t rc = get_chunk_plan(a, st);
         if (rc) return rc;
-        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2, 0};
+        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2, 0, nullptr};
         ProfScope ps(d, st);
         CU_TRY(launch_chunk(L.map_kv, args, bf16, st));
         g_launches++;
@@ -773,6 +779,20 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         float ms = 0;
         CU_TRY(cudaEventElapsedTime(&ms, d->prof[i].first, d->prof[i].second));
         sum += ms;
+    }
+    if ((debug_flags() & 8) && d->dbg_buf && d->dbg_ctas < 0) {
+        const int n = -d->dbg_ctas;
+        std::vector<unsigned long long> h((size_t)n * 16);
+        cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
+        const char* names[11] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue", "softmax wait_s",
+                                 "softmax tmem_ld", "softmax max+exp", "softmax wait_o", "softmax store_p+rescale", "softmax total"};
+        double tiles = 0;
+        for (int c = 0; c < n; c++) tiles += (double)h[(size_t)c * 16 + 15];
+        for (int s2 = 0; s2 < 11; s2++) {
+            double sum = 0;
+            for (int c = 0; c < n; c++) sum += (double)h[(size_t)c * 16 + s2];
+            fprintf(stderr, "[cbkv tc] %-26s %9.0f cycles per KV tile (mean over %d CTAs, %.1f tiles each)\n", names[s2], sum / tiles, n, tiles / n);
+        }
     }
     if ((debug_flags() & 4) && d->dbg_buf && d->dbg_ctas > 0 && d->dbg_ctas <= 4096) {
         std::vector<unsigned long long> h((size_t)d->dbg_ctas * 16);

@@ -78,6 +78,7 @@ struct ChunkArgs {
     int32_t window;
     float scale_log2;
     int32_t rep_slots;  // tcgen05 kernel: q heads per kv head rounded up to a power of two (rows per token in a tile)
+    unsigned long long* dbg_buf;  // measurement only: per-CTA cycle counters of the tcgen05 kernel
 };
 
 struct AppendArgs {
@@ -113,7 +114,7 @@ cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
 // tcgen05 chunk kernel (prefill_tc.cu): head_dim 64 or 128; `map` is the 16-row box view
 bool chunk_tc_supported(int d);
 cudaError_t chunk_tc_init();
-cudaError_t launch_chunk_tc(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_chunk_tc(const CUtensorMap& map16, const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process
 
 }  // namespace cbkv

@@ -125,6 +125,31 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 128 consecutive columns of this thread's lane: four 32-column loads in flight, one wait
+__device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%128];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%129];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95}, [%130];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127}, [%131];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]), "=r"(r[64]), "=r"(r[65]), "=r"(r[66]), "=r"(r[67]), "=r"(r[68]), "=r"(r[69]), "=r"(r[70]), "=r"(r[71]), "=r"(r[72]), "=r"(r[73]), "=r"(r[74]), "=r"(r[75]), "=r"(r[76]), "=r"(r[77]), "=r"(r[78]), "=r"(r[79]), "=r"(r[80]), "=r"(r[81]), "=r"(r[82]), "=r"(r[83]), "=r"(r[84]), "=r"(r[85]), "=r"(r[86]), "=r"(r[87]), "=r"(r[88]), "=r"(r[89]), "=r"(r[90]), "=r"(r[91]), "=r"(r[92]), "=r"(r[93]), "=r"(r[94]), "=r"(r[95]), "=r"(r[96]), "=r"(r[97]), "=r"(r[98]), "=r"(r[99]), "=r"(r[100]), "=r"(r[101]), "=r"(r[102]), "=r"(r[103]), "=r"(r[104]), "=r"(r[105]), "=r"(r[106]), "=r"(r[107]), "=r"(r[108]), "=r"(r[109]), "=r"(r[110]), "=r"(r[111]), "=r"(r[112]), "=r"(r[113]), "=r"(r[114]), "=r"(r[115]), "=r"(r[116]), "=r"(r[117]), "=r"(r[118]), "=r"(r[119]), "=r"(r[120]), "=r"(r[121]), "=r"(r[122]), "=r"(r[123]), "=r"(r[124]), "=r"(r[125]), "=r"(r[126]), "=r"(r[127])
+        : "r"(taddr), "r"(taddr + 32), "r"(taddr + 64), "r"(taddr + 96) : "memory");
+}
+__device__ __forceinline__ void tmem_st128(uint32_t taddr, const uint32_t (&r)[128]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35};\n\t"
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%1], {%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,%64,%65,%66,%67};\n\t"
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%2], {%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,%96,%97,%98,%99};\n\t"
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%3], {%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127,%128,%129,%130,%131};\n\t"
+        "tcgen05.wait::st.sync.aligned;"
+        :: "r"(taddr), "r"(taddr + 32), "r"(taddr + 64), "r"(taddr + 96), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63]), "r"(r[64]), "r"(r[65]), "r"(r[66]), "r"(r[67]), "r"(r[68]), "r"(r[69]), "r"(r[70]), "r"(r[71]), "r"(r[72]), "r"(r[73]), "r"(r[74]), "r"(r[75]), "r"(r[76]), "r"(r[77]), "r"(r[78]), "r"(r[79]), "r"(r[80]), "r"(r[81]), "r"(r[82]), "r"(r[83]), "r"(r[84]), "r"(r[85]), "r"(r[86]), "r"(r[87]), "r"(r[88]), "r"(r[89]), "r"(r[90]), "r"(r[91]), "r"(r[92]), "r"(r[93]), "r"(r[94]), "r"(r[95]), "r"(r[96]), "r"(r[97]), "r"(r[98]), "r"(r[99]), "r"(r[100]), "r"(r[101]), "r"(r[102]), "r"(r[103]), "r"(r[104]), "r"(r[105]), "r"(r[106]), "r"(r[107]), "r"(r[108]), "r"(r[109]), "r"(r[110]), "r"(r[111]), "r"(r[112]), "r"(r[113]), "r"(r[114]), "r"(r[115]), "r"(r[116]), "r"(r[117]), "r"(r[118]), "r"(r[119]), "r"(r[120]), "r"(r[121]), "r"(r[122]), "r"(r[123]), "r"(r[124]), "r"(r[125]), "r"(r[126]), "r"(r[127]) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {  // one MUFU op; -inf -> 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     if constexpr (BF16) {
@@ -136,20 +161,25 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     }
 }
 
+// measurement only: cycle counters per role, 16 slots per CTA
+#define TC_T0() const long long t0__ = a.dbg_buf ? clock64() : 0
+#define TC_ACC(var) do { if (a.dbg_buf) { const long long t1__ = clock64(); var += t1__ - tprev; tprev = t1__; } } while (0)
+
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
+constexpr int kPageCap = 2560;   // block-table entries staged in shared memory (40960 tokens); longer ranges read the rest from global memory
 
 template <int D>
 constexpr int tc_smem_bytes() {
     // Q + 2 K + 2 V tiles of 128 rows x D, P tile of 128 rows x 128 keys, barriers and flags; at least
     // 120 KB so that two CTAs never share an SM (each allocates all 512 tensor-memory columns)
-    return (5 * 128 * D * 2 + 128 * 128 * 2 + 256) < 120 * 1024 ? 120 * 1024 : (5 * 128 * D * 2 + 128 * 128 * 2 + 256);
+    return (5 * 128 * D * 2 + 128 * 128 * 2 + 256 + kPageCap * 4) < 120 * 1024 ? 120 * 1024 : (5 * 128 * D * 2 + 128 * 128 * 2 + 256 + kPageCap * 4);
 }
 
 }  // namespace
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ChunkArgs a) {
+__global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap32, const ChunkArgs a) {
     constexpr uint32_t TILE = 128u * D * 2u;   // one operand tile (Q, K or V)
     constexpr uint32_t BLK = 128u * 128u;      // one 64-element column block of a tile: 128 rows x 128 bytes
     constexpr int XB = D / 64;                 // column blocks per row
@@ -164,6 +194,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
     const uint32_t b_p_full = smem_u32(bars + 6), b_o_done = smem_u32(bars + 7);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile int* failed = reinterpret_cast<volatile int*>(bars + 9);
+    int* s_pages = reinterpret_cast<int*>(bars + 16);   // [kPageCap] physical pages of the KV range
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
@@ -202,6 +233,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    for (int i = tid; i <= p_hi - p_lo && i < kPageCap; i += kThreads) s_pages[i] = a.step.tables[sm.tbl_off + p_lo + i];
     // ---- Q tile: rows m = rep * TPT + i, K-major swizzled blocks; rows past the data are zero
     {
         const uint16_t* qbase = reinterpret_cast<const uint16_t*>(a.q) + (size_t)sm.tok_off * a.geo.n_q * D;
@@ -224,66 +256,83 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            for (int j = 0; j < n_tiles; j++) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait_bounded(b_kv_empty + st * 8, ((j >> 1) - 1) & 1)) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
-                if (*failed) break;
-                mbar_expect_tx(b_kv_full + st * 8, 2 * TILE);
-                for (int pg = 0; pg < 8; pg++) {
-                    // pages past the last visible one repeat it: finite data that the causal mask hides
-                    const int lp = min(p_lo + j * 8 + pg, p_hi);
-                    int phys = a.step.tables[sm.tbl_off + lp];
-                    if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-                    const int row = (phys * Hkv + h) * 32;
-#pragma unroll
-                    for (int x = 0; x < XB; x++) {
-                        tma_load_2d(smem_u32(sK + st * TILE + x * BLK + pg * 2048), &tmap, x * 64, row, b_kv_full + st * 8);
-                        tma_load_2d(smem_u32(sV + st * TILE + x * BLK + pg * 2048), &tmap, x * 64, row + 16, b_kv_full + st * 8);
-                    }
-                }
+        // The block-table entries of the whole KV range were staged in shared memory by all
+        // threads (below the Q load); every lane issues one box of a tile: lane = page * (2 XB) +
+        // column block * 2 + (K or V).
+        bool ok = true;
+        long long tprev = clock64(), c_wait = 0, c_issue = 0;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles && ok; j++) {
+            const int st = j & 1;
+            if (lane == 0) {
+                if (j >= 2 && !mbar_wait_bounded(b_kv_empty + st * 8, ((j >> 1) - 1) & 1)) ok = false;
+                TC_ACC(c_wait);
+                if (*failed) ok = false;
+                if (ok) mbar_expect_tx(b_kv_full + st * 8, 2 * TILE);
+                else { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            for (int bx = lane; bx < 8 * 2 * XB; bx += 32) {
+                const int pg = bx / (2 * XB), rem = bx - pg * (2 * XB), x = rem >> 1, kv = rem & 1;
+                // pages past the last visible one repeat it: finite data that the causal mask hides
+                const int idx = min(j * 8 + pg, p_hi - p_lo);
+                int phys = idx < kPageCap ? s_pages[idx] : a.step.tables[sm.tbl_off + p_lo + idx];
+                if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+                const int row = (phys * Hkv + h) * 32 + kv * 16;
+                tma_load_2d(smem_u32((kv ? sV : sK) + st * TILE + x * BLK + pg * 2048), &tmap, x * 64, row, b_kv_full + st * 8);
+            }
+            if (lane == 0) TC_ACC(c_issue);
         }
+        if (a.dbg_buf && lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t id_qk = instr_desc(BF16, 128, 128, false);
             const uint32_t id_pv = instr_desc(BF16, 128, D, true);
+            // descriptors differ only in the start address field (bits 0-13, address >> 4)
+            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sK), 16, 1024);
+            const uint64_t dp = smem_desc(smem_u32(sP), 16, 1024), dv = smem_desc(smem_u32(sV), BLK, 1024);
             auto issue_qk = [&](int j) {
-                const int st = j & 1;
-                const uint32_t ka = smem_u32(sK + st * TILE), qa = smem_u32(sQ);
+                const uint64_t kst = (uint64_t)(((j & 1) * TILE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ks++) {
-                    const uint32_t off = (ks >> 2) * BLK + (ks & 3) * 32;  // 16 elements = 32 bytes inside the swizzled row
-                    umma(tS0 + (j & 1) * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), id_qk, ks > 0);
+                    const uint64_t off = (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4);  // 16 elements = 32 bytes inside the swizzled row
+                    umma(tS0 + (j & 1) * 128, dq + off, dk + kst + off, id_qk, ks > 0);
                 }
                 umma_commit(b_s_full + (j & 1) * 8);
             };
+            long long tprev = clock64(), c_wkv = 0, c_wp = 0, c_iss = 0;
             bool ok = mbar_wait_bounded(b_kv_full, 0);
             if (ok) { tc_fence_after(); issue_qk(0); }
             for (int j = 0; ok && j < n_tiles; j++) {
                 if (j + 1 < n_tiles) {
+                    TC_ACC(c_iss);
                     ok = mbar_wait_bounded(b_kv_full + ((j + 1) & 1) * 8, ((j + 1) >> 1) & 1);
+                    TC_ACC(c_wkv);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(j + 1);
                 }
+                TC_ACC(c_iss);
                 ok = mbar_wait_bounded(b_p_full, j & 1) && !*failed;
+                TC_ACC(c_wp);
                 if (!ok) break;
                 tc_fence_after();
                 const int st = j & 1;
-                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * TILE);
+                const uint64_t vst = (uint64_t)((st * TILE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {  // 16 keys per step
                     // P: K-major, keys 16 ks.. inside key block ks / 4; V: MN-major, 64-wide d blocks BLK apart,
                     // groups of 8 keys 1024 bytes apart, 16 keys = 2048 bytes per step
-                    umma(tO, smem_desc(pa + (ks >> 2) * BLK + (ks & 3) * 32, 16, 1024), smem_desc(va + ks * 2048, BLK, 1024), id_pv,
+                    umma(tO, dp + (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4), dv + vst + (uint64_t)((ks * 2048) >> 4), id_pv,
                          (j > 0 || ks > 0));
                 }
                 umma_commit(b_kv_empty + st * 8);
                 umma_commit(b_o_done);
             }
             if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
+            if (a.dbg_buf) { a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss; }
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue, one row per thread
@@ -293,35 +342,62 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
         const bool row_ok = rep < n_rep && r < sm.snew;
         const int q_pos = sm.pos + min(r, sm.snew - 1);    // rows past the data mimic the last token
         const uint32_t lane_addr = (uint32_t)lane_base << 16;
-        float m_run = -INFINITY, l_run = 0.f;
+        // Exponents are taken against a reference maximum that is only moved when a row's maximum
+        // exceeds it by more than 8 (a factor 256): probabilities then stay below 256, exact enough in
+        // f16/bf16 with f32 sums, and O needs rescaling only on those rare moves.
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
+        long long tprev = clock64(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
+        const long long tstart = tprev;
+#pragma unroll 1
         for (int j = 0; j < n_tiles; j++) {
             ok = mbar_wait_bounded(b_s_full + (j & 1) * 8, (j >> 1) & 1) && !*failed;
             ok = __all_sync(0xffffffffu, ok);  // the tensor-memory accesses below need the whole warp
+            TC_ACC(c_ws);
             if (!ok) break;
             tc_fence_after();
             const uint32_t tS = tS0 + (j & 1) * 128 + lane_addr;
             const int kbase = k0 + j * 128;
             const bool need_mask = (kbase + 127 > q_min) || (a.window > 0 && kbase + a.window <= q_max);
-            // pass 1: row maximum
+            uint32_t sv[128];
+            tmem_ld128(tS, sv);
+            TC_ACC(c_ld);
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld32(tS + c * 32, v);
+            if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    float s = __uint_as_float(v[e]) * a.scale_log2;
-                    if (need_mask) {
-                        const int kp = kbase + c * 32 + e;
-                        if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) s = -INFINITY;
-                    }
-                    mx = fmaxf(mx, s);
+                for (int e = 0; e < 128; e++) {
+                    const int kp = kbase + e;
+                    if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) sv[e] = 0xff800000u;  // -inf
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = exp2f(m_run - m_use);
+            {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                for (int e = 0; e < 128; e += 4) {
+                    m0 = fmaxf(m0, __uint_as_float(sv[e])); m1 = fmaxf(m1, __uint_as_float(sv[e + 1]));
+                    m2 = fmaxf(m2, __uint_as_float(sv[e + 2])); m3 = fmaxf(m3, __uint_as_float(sv[e + 3]));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            }
+            mx *= a.scale_log2;  // scale > 0: the maximum commutes with the scaling
+            float alpha = 1.f;
+            if (mx > m_ref + 8.f || m_ref == -INFINITY) {
+                const float m_new = mx;
+                alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+                m_ref = m_new;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f, sum2 = 0.f;
+            uint32_t pk[64];
+#pragma unroll
+            for (int e = 0; e < 128; e += 2) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), a.scale_log2, -m_use));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2, -m_use));
+                if (e & 2) sum2 += p0 + p1; else sum += p0 + p1;  // two chains
+                pk[e >> 1] = pack2<BF16>(p0, p1);
+            }
+            l_run = l_run * alpha + (sum + sum2);
+            TC_ACC(c_exp);
             // the previous P V must be finished before P is overwritten and O rescaled
             if (j > 0) {
                 ok = mbar_wait_bounded(b_o_done, (j - 1) & 1) && !*failed;
@@ -329,48 +405,38 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 if (!ok) break;
                 tc_fence_after();
             }
-            // pass 2: probabilities -> P (keys along the row, K-major swizzled), row sum
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld32(tS + c * 32, v);
-                uint32_t pk[16];
+            TC_ACC(c_wo);
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float s0 = __uint_as_float(v[e]) * a.scale_log2, s1 = __uint_as_float(v[e + 1]) * a.scale_log2;
-                    if (need_mask) {
-                        const int kp = kbase + c * 32 + e;
-                        if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) s0 = -INFINITY;
-                        if (!(kp + 1 <= q_pos && (a.window <= 0 || kp + 1 + a.window > q_pos))) s1 = -INFINITY;
-                    }
-                    const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
-                    sum += p0 + p1;
-                    pk[e >> 1] = pack2<BF16>(p0, p1);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {  // four 16-byte pieces = 32 keys
-                    const int jj = (c & 1) * 4 + u;
-                    const uint32_t off = (c >> 1) * BLK + m * 128u + ((jj ^ (m & 7)) << 4);
-                    *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-                }
+            for (int u = 0; u < 16; u++) {  // sixteen 16-byte pieces = 128 keys, K-major swizzled
+                const uint32_t off = (u >> 3) * BLK + m * 128u + (((u & 7) ^ (m & 7)) << 4);
+                *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
             }
-            l_run = l_run * alpha + sum;
-            m_run = m_new;
-            // rescale O when some row of this warp moved its maximum
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld32(tO + lane_addr + c * 32, v);
+                if constexpr (D == 128) {
+                    uint32_t ov[128];
+                    tmem_ld128(tO + lane_addr, ov);
 #pragma unroll
-                    for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                    tmem_st32(tO + lane_addr + c * 32, v);
+                    for (int e = 0; e < 128; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+                    tmem_st128(tO + lane_addr, ov);
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; c++) {
+                        uint32_t v[32];
+                        tmem_ld32(tO + lane_addr + c * 32, v);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                        tmem_st32(tO + lane_addr + c * 32, v);
+                    }
                 }
             }
             fence_proxy_async();   // P for the async proxy
             tc_fence_before();     // the tensor-memory traffic above is ordered before the hand-over
             mbar_arrive(b_p_full);
+            TC_ACC(c_st);
+        }
+        if (a.dbg_buf && tid == 64) {
+            unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16;
+            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = clock64() - tstart;
         }
         // ---- epilogue: O / l -> out
         if (ok) ok = mbar_wait_bounded(b_o_done, (n_tiles - 1) & 1) && !*failed;
@@ -411,9 +477,9 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
 }
 
 template <int D, bool BF16>
-static cudaError_t launch_tc(const CUtensorMap& map, const ChunkArgs& a, cudaStream_t st) {
+static cudaError_t launch_tc(const CUtensorMap& map, const CUtensorMap& map32, const ChunkArgs& a, cudaStream_t st) {
     if (a.n_items <= 0) return cudaSuccess;
-    chunk_tc_kernel<D, BF16><<<a.n_items, kThreads, tc_smem_bytes<D>(), st>>>(map, a);
+    chunk_tc_kernel<D, BF16><<<a.n_items, kThreads, tc_smem_bytes<D>(), st>>>(map, map32, a);
     return cudaGetLastError();
 }
 
@@ -429,10 +495,10 @@ cudaError_t chunk_tc_init() {
 }
 
 // `map` must be the 16-row box view of the layer (one K or V tile of a page per box).
-cudaError_t launch_chunk_tc(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st) {
+cudaError_t launch_chunk_tc(const CUtensorMap& map, const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st) {
     switch (a.geo.d) {
-        case 64: return bf16 ? launch_tc<64, true>(map, a, st) : launch_tc<64, false>(map, a, st);
-        case 128: return bf16 ? launch_tc<128, true>(map, a, st) : launch_tc<128, false>(map, a, st);
+        case 64: return bf16 ? launch_tc<64, true>(map, map32, a, st) : launch_tc<64, false>(map, map32, a, st);
+        case 128: return bf16 ? launch_tc<128, true>(map, map32, a, st) : launch_tc<128, false>(map, map32, a, st);
         default: return cudaErrorInvalidValue;
     }
 }
