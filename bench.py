@@ -137,8 +137,7 @@ def time_cpu_port(n_seqs: int, n_layers: int, budget_s: float, lens: np.ndarray)
     oracle.build()
     from oracle import OracleArena
     rng = np.random.default_rng(SEED)
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    cores = oracle.set_threads(os.cpu_count() or 1)  # all host threads, whatever the launcher put in OMP_NUM_THREADS
     lens = lens[:n_seqs]
     pages = int(sum(-(-(int(n) + 64) // PAGE) for n in lens)) + 8
     arena = OracleArena(n_layers, N_KV, D, CTX_HI + 256, PAGE, pages, rolling=False, dtype="f16")

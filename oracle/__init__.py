@@ -80,6 +80,14 @@ def _lib(kind: str) -> C.CDLL:
     return lib
 
 
+def set_threads(n: int, kind: str = "f16") -> int:
+    """OpenMP threads used by the batch driver; returns the number in effect."""
+    lib = _lib(kind)
+    lib.orc_set_threads.argtypes = [C.c_int]
+    lib.orc_set_threads.restype = C.c_int
+    return lib.orc_set_threads(int(n))
+
+
 class OracleError(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(msg)

@@ -59,9 +59,22 @@ static inline elem_t st(float f) { return f; }
 #define ORC_ERR_EXHAUSTED -3 /* kv.rs:552-555 */
 #define ORC_ERR_ARG -4
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 static __thread char g_err[256];
 const char* orc_last_error(void) { return g_err; }
 int orc_elem_bytes(void) { return ORC_ELEM_BYTES; }
+/* Threads of the batch driver (the launcher may have pinned OMP_NUM_THREADS to 1). */
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
 
 /* ---------------------------------------------------------------- allocator
  * PageAllocator, kv.rs:417-446: a stack of page ids; `new` pushes n-1..0 so
