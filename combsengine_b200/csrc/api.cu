@@ -272,7 +272,7 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
 
 GeomDev geom(const Arena* a) {
     return GeomDev{a->cfg.n_q_heads, a->cfg.n_kv_heads, a->cfg.n_q_heads / a->cfg.n_kv_heads, a->cfg.head_dim,
-                   a->cfg.page_size, (int32_t)a->num_pages};
+                   a->cfg.page_size, (int32_t)a->num_pages, (a->dev && dev_of(const_cast<Arena*>(a))->fast) ? 1 : 0};
 }
 
 int32_t get_decode_plan(Arena* a, int64_t window, cudaStream_t st, DecodePlanDev** out) {
@@ -725,10 +725,15 @@ int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k
     std::vector<uint8_t> buf(tile * 2 * H);
     CU_TRY(cudaMemcpy(buf.data(), (uint8_t*)d->layers[(size_t)layer].base + (size_t)page * tile * 2 * H, buf.size(),
                       cudaMemcpyDeviceToHost));
-    for (int h = 0; h < H; h++) {  // [h][K|V][slot][d] -> K [h][slot][d], V [h][slot][d]
-        memcpy((uint8_t*)k_out_host + h * tile, buf.data() + (size_t)(2 * h) * tile, tile);
-        memcpy((uint8_t*)v_out_host + h * tile, buf.data() + (size_t)(2 * h + 1) * tile, tile);
-    }
+    const size_t rowb = (size_t)a->cfg.head_dim * 2;
+    const int P = a->cfg.page_size;
+    for (int h = 0; h < H; h++)  // the arena's row order (page_row) -> K [h][slot][d], V [h][slot][d]
+        for (int slot = 0; slot < P; slot++) {
+            memcpy((uint8_t*)k_out_host + ((size_t)h * P + slot) * rowb,
+                   buf.data() + ((size_t)h * 2 * P + page_row(0, slot, P, d->fast)) * rowb, rowb);
+            memcpy((uint8_t*)v_out_host + ((size_t)h * P + slot) * rowb,
+                   buf.data() + ((size_t)h * 2 * P + page_row(1, slot, P, d->fast)) * rowb, rowb);
+        }
     return CBKV_OK;
 }
 

@@ -9,8 +9,9 @@
 //                   (causal, bottom-right aligned, optional window; kv.rs:243-268)
 //   generic_kernel  any page size / head_dim; one warp per query row
 //
-// Layout of one layer in HBM: pages [num_pages][n_kv][2][16][d] (f16/bf16).  One
-// (page, kv head) is 32 consecutive rows of d elements: its K tile then its V tile.
+// Layout of one layer in HBM: pages [num_pages][n_kv][32 rows][d] (f16/bf16).  The 32
+// rows of one (page, kv head) are [K slots 0-7][V slots 0-7][K slots 8-15][V slots 8-15]
+// (page_row() in kernels.hpp).
 // A tile reaches shared memory through one TMA box per 64-element column block
 // (32 rows x 128 B, 128-byte swizzle), so ldmatrix reads are bank-conflict free.
 //
@@ -138,7 +139,7 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
     }
     // ---- S^T = K . Q^T  (two accumulator chains, summed at the end)
     {
-        const uint32_t row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row of this lane's ldmatrix address
+        const uint32_t row = (lane & 7) + ((lane >> 3) & 1) * 16;  // K slot (lane&7) + 8*((lane>>3)&1) -> its row
         const uint32_t jsel = lane >> 4;                           // which of the two 16-byte chunks
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
@@ -197,9 +198,9 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
         pb[nt][0] = movmatrix_trans(pack2<BF16>(s[nt][0], s[nt][1]));
         pb[nt][1] = movmatrix_trans(pack2<BF16>(s[nt][2], s[nt][3]));
     }
-    // ---- O^T += V^T . P^T   (V rows are 16..31 of the block)
+    // ---- O^T += V^T . P^T   (V slots 0-7 are rows 8-15 of the block, slots 8-15 rows 24-31)
     {
-        const uint32_t row = 16 + (lane & 7) + (lane >> 4) * 8;  // token row
+        const uint32_t row = 8 + (lane & 7) + (lane >> 4) * 16;  // V slot (lane&7) + 8*(lane>>4) -> its row
         const uint32_t jsel = (lane >> 3) & 1;                   // d chunk
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
@@ -242,7 +243,7 @@ __global__ void append_kernel(const AppendArgs a) {
         int slot = gpos % a.geo.page_size;             // kv.rs:726
         if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); continue; }
         const uint4* src = reinterpret_cast<const uint4*>(kv ? a.v : a.k) + row * D8 + c;
-        int64_t drow = (((int64_t)phys * a.geo.n_kv + h) * 2 + kv) * a.geo.page_size + slot;
+        int64_t drow = ((int64_t)phys * a.geo.n_kv + h) * 2 * a.geo.page_size + page_row(kv, slot, a.geo.page_size, a.geo.tiled != 0);
         reinterpret_cast<uint4*>(a.arena)[drow * D8 + c] = *src;
     }
 }
@@ -639,11 +640,11 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                         int kv = c / (D / 8), j = c - kv * (D / 8);
                         const uint4 val = *(reinterpret_cast<const uint4*>(kv ? a.v_new : a.k_new) +
                                             ((size_t)cur.tok_off * Hkv + cur.h) * (D / 8) + j);
-                        uint32_t row = kv * 16 + slot;
+                        uint32_t row = page_row(kv, slot, 16, true);
                         uint32_t addr = stage + (j >> 3) * 4096u + swz(row, j & 7);
                         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
                         if (phys >= 0 && phys < a.geo.num_pages) {
-                            size_t drow = (((size_t)phys * Hkv + cur.h) * 2 + kv) * 16 + slot;
+                            size_t drow = ((size_t)phys * Hkv + cur.h) * 32 + row;
                             reinterpret_cast<uint4*>(a.arena)[drow * (D / 8) + j] = val;
                         }
                     }

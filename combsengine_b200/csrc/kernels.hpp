@@ -17,8 +17,20 @@ enum : int32_t {
     ST_BAD_ARG = 8
 };
 
-// One layer's arena in HBM: pages [num_pages][n_kv][2 (K,V)][16 slots][d], so one
-// (page, kv head) holds its K tile and its V tile back to back (32 rows of d).
+// One layer's arena in HBM: one (page, kv head) is 32 consecutive rows of d elements.
+// Tiled arenas (16-token pages served by the TMA kernels) order them in groups of eight,
+// [K slots 0-7][V slots 0-7][K slots 8-15][V slots 8-15], so that one 32-row TMA box brings
+// K and V of a page and both still look like uniformly strided 8-row groups to the tensor
+// cores (stride 2048 bytes per 64-element column block).  Other arenas (any page size,
+// generic kernel) keep [K slots][V slots].
+#if defined(__CUDACC__)
+#define CBKV_HD __host__ __device__
+#else
+#define CBKV_HD
+#endif
+CBKV_HD inline int page_row(int kv, int slot, int page_size, bool tiled) {
+    return tiled ? ((slot >> 3) * 16 + kv * 8 + (slot & 7)) : (kv * page_size + slot);
+}
 struct LayerArena {
     void* base = nullptr;
     CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
@@ -35,6 +47,7 @@ struct StepDev {
 
 struct GeomDev {
     int32_t n_q, n_kv, n_rep, d, page_size, num_pages;
+    int32_t tiled;  // 1: rows of a (page, kv head) in the 8-row K/V interleave (see page_row)
 };
 
 struct DecodeArgs {

@@ -194,7 +194,7 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
     args.step.tables = block_tables;
     args.step.n_seqs = n_seqs;
     args.step.n_tokens = n_seqs;
-    args.geo = GeomDev{n_q_heads, n_kv_heads, n_rep, head_dim, 16, (int32_t)num_pages};
+    args.geo = GeomDev{n_q_heads, n_kv_heads, n_rep, head_dim, 16, (int32_t)num_pages, 1};
     args.seg_unit_begin = plan + o0; args.seg_page_lo = plan + o1; args.seg_first_cta = plan + o2; args.seg_nparts = plan + o3;
     args.seg_part_base = plan + o4; args.cta_unit_begin = plan + o5; args.cta_first_seg = plan + o6;
     args.n_segs = pl.n_segs;

@@ -9,14 +9,17 @@
 // the tile's i-th token (TPT = 128 / RS tokens, RS = n_rep rounded up to a power of
 // two), so the K/V tiles are shared by the whole q-head group.
 //
-//   warp 0        TMA producer: K and V boxes of 8 pages per tile, two stages
+//   warp 0        TMA producer: one 32-row box per (page, 64-column block) brings K and V of a
+//                 page in the arena's 8-row interleave; 8 pages per tile, two stages
 //   warp 1        one thread issues tcgen05.mma: S = Q K^T (two S buffers), O += P V
 //   warps 2..5    softmax: one TMEM lane (row) per thread, P written to shared memory
 //                 in the K-major swizzled layout, O rescaled in TMEM when a row max moves
 //
 // Tensor memory: S0 [0,128), S1 [128,256), O [256, 256 + D) -> 512 columns allocated.
-// Shared memory: Q, 2 x K, 2 x V, P tiles of 128 rows x D (or 128 keys), each stored as
-// D/64 blocks of 128 rows x 128 bytes with the 128-byte swizzle TMA produces.
+// Shared memory: Q and P tiles of 128 rows stored as 64-column blocks of 128 rows x 128 bytes
+// (128-byte swizzle); two K/V stages, each D/64 blocks of 8 pages x 32 rows x 128 bytes in
+// the arena's row order [K 0-7][V 0-7][K 8-15][V 8-15], so K and V are both 8-row groups
+// 2048 bytes apart (V starts 1024 bytes in).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -184,10 +187,11 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
     constexpr uint32_t BLK = 128u * 128u;      // one 64-element column block of a tile: 128 rows x 128 bytes
     constexpr int XB = D / 64;                 // column blocks per row
     extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr uint32_t BLKKV = 8u * 4096u;     // one 64-column block of a K/V stage: 8 pages x 32 rows x 128 bytes
+    constexpr uint32_t STAGE = 2u * TILE;      // K and V of 128 tokens
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + TILE;            // 2 stages
-    uint8_t* sV = sK + 2 * TILE;        // 2 stages
-    uint8_t* sP = sV + 2 * TILE;        // 128 x 128 keys
+    uint8_t* sKV = sQ + TILE;           // 2 stages
+    uint8_t* sP = sKV + 2 * STAGE;      // 128 x 128 keys
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 128 * 128 * 2);
     // barriers: kv_full[2], kv_empty[2], s_full[2], p_full, o_done
     const uint32_t b_kv_full = smem_u32(bars + 0), b_kv_empty = smem_u32(bars + 2), b_s_full = smem_u32(bars + 4);
@@ -268,19 +272,18 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 if (j >= 2 && !mbar_wait_bounded(b_kv_empty + st * 8, ((j >> 1) - 1) & 1)) ok = false;
                 TC_ACC(c_wait);
                 if (*failed) ok = false;
-                if (ok) mbar_expect_tx(b_kv_full + st * 8, 2 * TILE);
+                if (ok) mbar_expect_tx(b_kv_full + st * 8, STAGE);
                 else { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
-            for (int bx = lane; bx < 8 * 2 * XB; bx += 32) {
-                const int pg = bx / (2 * XB), rem = bx - pg * (2 * XB), x = rem >> 1, kv = rem & 1;
+            for (int bx = lane; bx < 8 * XB; bx += 32) {
+                const int pg = bx / XB, x = bx - pg * XB;
                 // pages past the last visible one repeat it: finite data that the causal mask hides
                 const int idx = min(j * 8 + pg, p_hi - p_lo);
                 int phys = idx < kPageCap ? s_pages[idx] : a.step.tables[sm.tbl_off + p_lo + idx];
                 if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-                const int row = (phys * Hkv + h) * 32 + kv * 16;
-                tma_load_2d(smem_u32((kv ? sV : sK) + st * TILE + x * BLK + pg * 2048), &tmap, x * 64, row, b_kv_full + st * 8);
+                tma_load_2d(smem_u32(sKV + st * STAGE + x * BLKKV + pg * 4096), &tmap32, x * 64, (phys * Hkv + h) * 32, b_kv_full + st * 8);
             }
             if (lane == 0) TC_ACC(c_issue);
         }
@@ -291,14 +294,17 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             const uint32_t id_qk = instr_desc(BF16, 128, 128, false);
             const uint32_t id_pv = instr_desc(BF16, 128, D, true);
             // descriptors differ only in the start address field (bits 0-13, address >> 4)
-            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sK), 16, 1024);
-            const uint64_t dp = smem_desc(smem_u32(sP), 16, 1024), dv = smem_desc(smem_u32(sV), BLK, 1024);
+            // K: 8-row groups 2048 bytes apart; V: the same groups 1024 bytes further, 64-wide d blocks BLKKV apart
+            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sKV), 16, 2048);
+            const uint64_t dp = smem_desc(smem_u32(sP), 16, 1024), dv = smem_desc(smem_u32(sKV) + 1024, BLKKV, 2048);
             auto issue_qk = [&](int j) {
-                const uint64_t kst = (uint64_t)(((j & 1) * TILE) >> 4);
+                const uint64_t kst = (uint64_t)(((j & 1) * STAGE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ks++) {
-                    const uint64_t off = (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4);  // 16 elements = 32 bytes inside the swizzled row
-                    umma(tS0 + (j & 1) * 128, dq + off, dk + kst + off, id_qk, ks > 0);
+                    // 16 elements = 32 bytes inside the swizzled row, four steps per 64-column block
+                    const uint64_t qoff = (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4);
+                    const uint64_t koff = (uint64_t)(((ks >> 2) * BLKKV + (ks & 3) * 32) >> 4);
+                    umma(tS0 + (j & 1) * 128, dq + qoff, dk + kst + koff, id_qk, ks > 0);
                 }
                 umma_commit(b_s_full + (j & 1) * 8);
             };
@@ -320,12 +326,11 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 if (!ok) break;
                 tc_fence_after();
                 const int st = j & 1;
-                const uint64_t vst = (uint64_t)((st * TILE) >> 4);
+                const uint64_t vst = (uint64_t)((st * STAGE) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {  // 16 keys per step
-                    // P: K-major, keys 16 ks.. inside key block ks / 4; V: MN-major, 64-wide d blocks BLK apart,
-                    // groups of 8 keys 1024 bytes apart, 16 keys = 2048 bytes per step
-                    umma(tO, dp + (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4), dv + vst + (uint64_t)((ks * 2048) >> 4), id_pv,
+                for (int ks = 0; ks < 8; ks++) {  // 16 keys per step = one page
+                    // P: K-major, keys 16 ks.. inside key block ks / 4; V: MN-major, one page (4096 bytes) per step
+                    umma(tO, dp + (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4), dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv,
                          (j > 0 || ks > 0));
                 }
                 umma_commit(b_kv_empty + st * 8);

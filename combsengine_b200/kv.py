@@ -321,7 +321,7 @@ def decode_attention_static(kv_pages: torch.Tensor, block_tables: torch.Tensor, 
     own pool, or the host process forbids late allocations): the kernel's working memory
     is a fixed array in the library, shared by every call on the device, so calls must
     not overlap on the GPU and sizes are capped (128 sequences, 1024 sequence x kv-head
-    pairs).  ``kv_pages`` is one layer ``[num_pages, n_kv, 2, 16, head_dim]``,
+    pairs).  ``kv_pages`` is one layer ``[num_pages, n_kv, 2, 2, 8, head_dim]`` (slot half, K/V, slot in half),
     ``block_tables`` int32 ``[n_seqs, stride]`` on the device, ``seq_lens`` host integers
     (cached tokens including the one being decoded), ``q``/``out`` ``[n_seqs, n_q, head_dim]``.
     Pass ``out`` to keep even the output allocation on the caller's side.

@@ -154,7 +154,7 @@ int32_t cbkv_host_free(void* p);
  * fixed ~4 MB array inside the library image.  Limits: at most 128 sequences and
  * 1024 sequence x kv-head pairs per call, head_dim 64/128/256, at most 8 q heads per
  * kv head, 16-token pages; larger problems return CBKV_ERR_ARG.
- *   kv_pages      device, one layer's pages [num_pages][n_kv][2 (K,V)][16][head_dim]
+ *   kv_pages      device, one layer's pages [num_pages][n_kv][2 (slots 0-7, 8-15)][2 (K,V)][8][head_dim]
  *   block_tables  device, [n_seqs][table_stride] physical page ids
  *   seq_lens_host HOST, [n_seqs]: cached tokens including the one being decoded
  *   q, out        device, [n_seqs][n_q][head_dim]

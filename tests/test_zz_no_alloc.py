@@ -44,13 +44,15 @@ def test_static_decode_matches_regular_entry_point_twice_in_a_row():
     lens = [s.seq_len() for s in seqs]
 
     # the caller-owned copy of the same pages, in the library's page layout
-    pages = torch.zeros(num_pages, n_kv, 2, 16, d, dtype=torch.float16)
+    # [page][kv head][slots 0-7 / 8-15][K, V][slot within the half][d]
+    pages = torch.zeros(num_pages, n_kv, 2, 2, 8, d, dtype=torch.float16)
     for b, tbl in enumerate(tables):
         kk = np.concatenate([kpre[b], knew[b]], axis=1)
         vv = np.concatenate([vpre[b], vnew[b]], axis=1)
         for t in range(lens[b]):
-            pages[int(tbl[t // 16]), :, 0, t % 16] = torch.from_numpy(kk[:, t])
-            pages[int(tbl[t // 16]), :, 1, t % 16] = torch.from_numpy(vv[:, t])
+            slot = t % 16
+            pages[int(tbl[t // 16]), :, slot // 8, 0, slot % 8] = torch.from_numpy(kk[:, t])
+            pages[int(tbl[t // 16]), :, slot // 8, 1, slot % 8] = torch.from_numpy(vv[:, t])
     pages = pages.cuda()
     stride = max(len(t) for t in tables)
     bt = torch.zeros(len(seqs), stride, dtype=torch.int32)
@@ -77,7 +79,7 @@ def test_static_decode_refuses_sizes_beyond_its_working_memory():
     from combsengine_b200 import CbkvError
     from combsengine_b200.kv import decode_attention_static
 
-    pages = torch.zeros(8, 4, 2, 16, 128, dtype=torch.float16, device="cuda")
+    pages = torch.zeros(8, 4, 2, 2, 8, 128, dtype=torch.float16, device="cuda")
     bt = torch.zeros(129, 2, dtype=torch.int32, device="cuda")
     q = torch.zeros(129 * 28 * 128, dtype=torch.float16, device="cuda")
     with pytest.raises(CbkvError, match="too large for the static working memory"):
