@@ -422,7 +422,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"cfg4 llama-3-8b geometry chunked prefill: {layers} layers, 32/8/128, 8 prompts x 8192 in 512-token "
                                "chunks, append + causal attention over paged prefix + chunk",
-                   "chunk_kernel": {0: "auto (tcgen05)", 1: "mma.sync", 2: "tcgen05"}[args.chunk_kernel]},
+                   "chunk_kernel": {0: "auto (tcgen05, two query tiles per CTA)", 1: "mma.sync", 2: "tcgen05, one query tile per CTA", 3: "tcgen05, two query tiles per CTA"}[args.chunk_kernel]},
         "roofline": {"bound": "tensor", "achieved": tfl, "peak": peak, "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None,
                      "algorithmic_flops_per_pass": flops},
     }), flush=True)
@@ -434,7 +434,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync kernel, 2 = tcgen05 kernel")
+    ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync, 2 = tcgen05 one tile per CTA, 3 = tcgen05 two tiles per CTA")
     ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload; cfg3 (windows, d=256) and cfg5 (shared prefix, long tails) on request")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")

@@ -79,6 +79,7 @@ struct DeviceState {
     bool tc_ok = false;       // the tcgen05 chunk kernel covers this geometry
     int chunk_mode = 0;       // 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel
     bool tile_plan_ok = false;
+    int tile_plan_tokens = 0;  // tokens per work item the tile plan was built for
     ChunkPlan tile_host;
     const int32_t* tile_item_begin = nullptr;
     float* part_o = nullptr;
@@ -338,10 +339,11 @@ int rep_slots_of(int n_rep) {
     return rs;
 }
 
-int32_t get_tile_plan(Arena* a, cudaStream_t st) {
+int32_t get_tile_plan(Arena* a, int tokens_per_item, cudaStream_t st) {
     DeviceState* d = dev_of(a);
-    if (d->tile_plan_ok) return CBKV_OK;
-    build_chunk_tile_plan(*a, 128 / rep_slots_of(a->n_rep()), &d->tile_host);
+    if (d->tile_plan_ok && d->tile_plan_tokens == tokens_per_item) return CBKV_OK;
+    build_chunk_tile_plan(*a, tokens_per_item, &d->tile_host);
+    d->tile_plan_tokens = tokens_per_item;
     const void* p = nullptr;
     int32_t rc = slot_upload(d, d->tile_host.item_begin.data(), d->tile_host.item_begin.size() * sizeof(int32_t), st, &p);
     if (rc) return rc;
@@ -423,21 +425,25 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
     }
-    // tensor-core chunk kernel: worth it once the step has enough new tokens to fill 128-row tiles
-    // (its softmax takes row maxima before scaling, which needs a positive scale)
-    const bool use_tc = d->fast && d->tc_ok && scale > 0 && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
-    if (use_tc) {
-        int32_t rc = get_tile_plan(a, st);
+    // tensor-core chunk kernels: worth it once the step has enough new tokens to fill 128-row tiles
+    // (their softmax takes row maxima before scaling, which needs a positive scale)
+    const bool tc_able = d->fast && d->tc_ok && scale > 0;
+    const bool use_tc2 = tc_able && chunk_tc2_supported(a->cfg.head_dim) &&
+                         (d->chunk_mode == 3 || (d->chunk_mode == 0 && a->step_tokens >= 128));
+    const bool use_tc = tc_able && !use_tc2 && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
+    if (use_tc || use_tc2) {
+        const int rs = rep_slots_of(a->n_rep());
+        int32_t rc = get_tile_plan(a, (use_tc2 ? 2 : 1) * (128 / rs), st);
         if (rc) return rc;
-        ChunkArgs args{d->step, geom(a), d->tile_item_begin, d->tile_host.n_items, q, out, d->status, (int32_t)w, scale_log2,
-                       rep_slots_of(a->n_rep()), nullptr};
+        ChunkArgs args{d->step, geom(a), d->tile_item_begin, d->tile_host.n_items, q, out, d->status, (int32_t)w, scale_log2, rs, nullptr};
         if (debug_flags() & 8) {  // measurement only: per-role cycle counters of the first 4096 CTAs
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
             CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
             if (d->tile_host.n_items <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
         }
         ProfScope ps(d, st);
-        CU_TRY(launch_chunk_tc(L.map_k16, L.map_kv, args, bf16, st));
+        if (use_tc2) CU_TRY(launch_chunk_tc2(L.map_kv, args, bf16, st));
+        else CU_TRY(launch_chunk_tc(L.map_k16, L.map_kv, args, bf16, st));
         g_launches++;
         d->last_kv_writer = -1;
         return CBKV_OK;
@@ -790,7 +796,7 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         std::vector<unsigned long long> h((size_t)n * 16);
         cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
         const char* names[11] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue", "softmax wait_s",
-                                 "softmax tmem_ld", "softmax max+exp", "softmax wait_o", "softmax store_p+rescale", "softmax total"};
+                                 "softmax ld+max", "softmax exp+store", "softmax wait_o", "softmax rescale+arrive", "softmax total"};
         double tiles = 0;
         for (int c = 0; c < n; c++) tiles += (double)h[(size_t)c * 16 + 15];
         for (int s2 = 0; s2 < 11; s2++) {
@@ -852,9 +858,12 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
 
 int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
     Arena* a = reinterpret_cast<Arena*>(arena);
-    if (!a || mode < 0 || mode > 2) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    if (!a || mode < 0 || mode > 3) { set_error("bad argument"); return CBKV_ERR_ARG; }
     int32_t rc = ensure_device(a);
     if (rc) return rc;
+    if (mode == 3 && !(dev_of(a)->tc_ok && chunk_tc2_supported(a->cfg.head_dim))) {
+        set_error("the two-tile tensor-core chunk kernel covers head_dim 128 with 16-token pages only"); return CBKV_ERR_ARG;
+    }
     if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64 and 128 with 16-token pages only"); return CBKV_ERR_ARG; }
     dev_of(a)->chunk_mode = mode;
     return CBKV_OK;

@@ -128,6 +128,9 @@ cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
 bool chunk_tc_supported(int d);
 cudaError_t chunk_tc_init();
 cudaError_t launch_chunk_tc(const CUtensorMap& map16, const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st);
+// two query tiles per CTA, P in tensor memory (head_dim 128)
+bool chunk_tc2_supported(int d);
+cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process
 
 }  // namespace cbkv

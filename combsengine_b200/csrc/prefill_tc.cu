@@ -488,6 +488,327 @@ static cudaError_t launch_tc(const CUtensorMap& map, const CUtensorMap& map32, c
     return cudaGetLastError();
 }
 
+
+// ------------------------------------------------------------------ two query tiles per CTA
+// The second-generation kernel: each CTA works on two 128-row query tiles (A and B) that
+// share every K/V tile, which halves the shared-memory fill per FLOP, and keeps P in tensor
+// memory (it overwrites the first 64 columns of its S tile as packed 16-bit pairs and is the
+// A operand of the P V product), so no shared memory is spent on P.
+//
+//   warp 0        TMA producer (as above)
+//   warp 1        MMA issuer:  QK_A, QK_B, then per K/V tile  PV_A, QK_A', PV_B, QK_B'
+//   warps 2..5    softmax of tile A        warps 6..9   softmax of tile B
+//
+// Tensor memory: S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512).
+constexpr int kThreads2 = 320;
+
+template <int D>
+constexpr int tc2_smem_bytes() {
+    return 2 * 128 * D * 2 /* Q_A, Q_B */ + 2 * 2 * 128 * D * 2 /* two K/V stages */ + 256 + kPageCap * 4;
+}
+
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_constant__ CUtensorMap tmap32, const ChunkArgs a) {
+    static_assert(D == 128, "two-tile kernel: head_dim 128");
+    constexpr uint32_t TILE = 128u * D * 2u;   // one Q tile
+    constexpr uint32_t BLK = 128u * 128u;      // 64-column block of a Q tile
+    constexpr int XB = D / 64;
+    constexpr uint32_t BLKKV = 8u * 4096u;     // 64-column block of a K/V stage
+    constexpr uint32_t STAGE = 2u * TILE;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;                 // Q_A then Q_B
+    uint8_t* sKV = sQ + 2 * TILE;       // 2 stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + 2 * STAGE);
+    // barriers: kv_full[2], kv_empty[2], s_full[A,B], p_full[A,B], o_done[A,B]
+    const uint32_t b_kv_full = smem_u32(bars + 0), b_kv_empty = smem_u32(bars + 2), b_s_full = smem_u32(bars + 4);
+    const uint32_t b_p_full = smem_u32(bars + 6), b_o_done = smem_u32(bars + 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* failed = reinterpret_cast<volatile int*>(bars + 11);
+    int* s_pages = reinterpret_cast<int*>(bars + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
+        return;
+    }
+    const int item = blockIdx.x;
+    int lo = 0, hi = a.step.n_seqs - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (a.item_begin[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    const SeqMeta sm = a.step.seq_meta[lo];
+    const int Hkv = a.geo.n_kv, n_rep = a.geo.n_rep, RS = a.rep_slots, TPT = 128 / RS;
+    const int n_qt = (sm.snew + 2 * TPT - 1) / (2 * TPT);        // pairs of tiles
+    const int local = item - a.item_begin[lo];
+    const int h = local / n_qt, qt = local - h * n_qt;
+    const int r0 = qt * 2 * TPT;                                  // first new token of tile A
+    const int q_first = sm.pos + r0, q_last = sm.pos + min(r0 + 2 * TPT, sm.snew) - 1;
+    const int lo_key = a.window > 0 ? max(0, q_first - a.window + 1) : 0;
+    const int p_lo = lo_key >> 4, p_hi = q_last >> 4;
+    const int n_tiles = (p_hi - p_lo + 1 + 7) >> 3;
+    const int k0 = p_lo * 16;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++) {
+            mbar_init(b_kv_full + i * 8, 1); mbar_init(b_kv_empty + i * 8, 1); mbar_init(b_s_full + i * 8, 1);
+            mbar_init(b_p_full + i * 8, 128); mbar_init(b_o_done + i * 8, 1);
+        }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap32) : "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i <= p_hi - p_lo && i < kPageCap; i += kThreads2) s_pages[i] = a.step.tables[sm.tbl_off + p_lo + i];
+    // ---- Q tiles: row m of tile X is q head (m / TPT) at token r0 + X TPT + m % TPT
+    {
+        const uint16_t* qbase = reinterpret_cast<const uint16_t*>(a.q) + (size_t)sm.tok_off * a.geo.n_q * D;
+        for (int c = tid; c < 256 * (D / 8); c += kThreads2) {
+            const int mm = c / (D / 8), j = c - mm * (D / 8);
+            const int X = mm >> 7, m = mm & 127;
+            const int rep = m / TPT, r = r0 + X * TPT + (m - rep * TPT);
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (rep < n_rep && r < sm.snew)
+                val = *reinterpret_cast<const uint4*>(qbase + ((size_t)(h * n_rep + rep) * sm.snew + r) * D + j * 8);
+            const uint32_t off = X * TILE + (j >> 3) * BLK + m * 128u + (((j & 7) ^ (m & 7)) << 4);
+            *reinterpret_cast<uint4*>(sQ + off) = val;
+        }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        bool ok = true;
+        long long tprev = clock64(), c_wait = 0, c_issue = 0;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles && ok; j++) {
+            const int st = j & 1;
+            if (lane == 0) {
+                if (j >= 2 && !mbar_wait_bounded(b_kv_empty + st * 8, ((j >> 1) - 1) & 1)) ok = false;
+                TC_ACC(c_wait);
+                if (*failed) ok = false;
+                if (ok) mbar_expect_tx(b_kv_full + st * 8, STAGE);
+                else { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            for (int bx = lane; bx < 8 * XB; bx += 32) {
+                const int pg = bx / XB, x = bx - pg * XB;
+                const int idx = min(j * 8 + pg, p_hi - p_lo);  // pages past the end repeat the last one (masked)
+                int phys = idx < kPageCap ? s_pages[idx] : a.step.tables[sm.tbl_off + p_lo + idx];
+                if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+                tma_load_2d(smem_u32(sKV + st * STAGE + x * BLKKV + pg * 4096), &tmap32, x * 64, (phys * Hkv + h) * 32, b_kv_full + st * 8);
+            }
+            if (lane == 0) TC_ACC(c_issue);
+        }
+        if (a.dbg_buf && lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t id_qk = instr_desc(BF16, 128, 128, false);
+            const uint32_t id_pv = instr_desc(BF16, 128, D, true);
+            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sKV), 16, 2048);
+            const uint64_t dv = smem_desc(smem_u32(sKV) + 1024, BLKKV, 2048);
+            auto issue_qk = [&](int X, int j) {
+                const uint64_t kst = (uint64_t)(((j & 1) * STAGE) >> 4), qst = (uint64_t)((X * TILE) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ks++) {
+                    const uint64_t qoff = (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4);
+                    const uint64_t koff = (uint64_t)(((ks >> 2) * BLKKV + (ks & 3) * 32) >> 4);
+                    umma(tmem + X * 128, dq + qst + qoff, dk + kst + koff, id_qk, ks > 0);
+                }
+                umma_commit(b_s_full + X * 8);
+            };
+            auto issue_pv = [&](int X, int j) {
+                const uint64_t vst = (uint64_t)(((j & 1) * STAGE) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)  // 16 keys = one page per step; P: 8 packed columns per step
+                    umma_ts(tmem + 256 + X * 128, tmem + X * 128 + ks * 8, dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv, (j > 0 || ks > 0));
+                umma_commit(b_o_done + X * 8);
+            };
+            long long tprev = clock64(), c_wkv = 0, c_wp = 0, c_iss = 0;
+            bool ok = mbar_wait_bounded(b_kv_full, 0);
+            if (ok) { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
+            for (int j = 0; ok && j < n_tiles; j++) {
+                TC_ACC(c_iss);
+                ok = mbar_wait_bounded(b_p_full, j & 1) && !*failed;
+                TC_ACC(c_wp);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(0, j);
+                if (j + 1 < n_tiles) {
+                    TC_ACC(c_iss);
+                    ok = mbar_wait_bounded(b_kv_full + ((j + 1) & 1) * 8, ((j + 1) >> 1) & 1);
+                    TC_ACC(c_wkv);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(0, j + 1);
+                }
+                TC_ACC(c_iss);
+                ok = mbar_wait_bounded(b_p_full + 8, j & 1) && !*failed;
+                TC_ACC(c_wp);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(1, j);
+                umma_commit(b_kv_empty + (j & 1) * 8);  // every read of this stage has been issued before
+                if (j + 1 < n_tiles) issue_qk(1, j + 1);
+            }
+            if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
+            if (a.dbg_buf) { a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss; }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue of tile X
+        const int X = (warp - 2) >> 2;
+        const int lane_base = (warp & 3) * 32;
+        const int m = lane_base + lane;
+        const int rep = m / TPT, r = r0 + X * TPT + (m - rep * TPT);
+        const bool row_ok = rep < n_rep && r < sm.snew;
+        const int q_pos = sm.pos + min(r, sm.snew - 1);
+        const int qx_min = sm.pos + min(r0 + X * TPT, sm.snew - 1), qx_max = sm.pos + min(r0 + (X + 1) * TPT, sm.snew) - 1;
+        const uint32_t lane_addr = (uint32_t)lane_base << 16;
+        const uint32_t tS = tmem + X * 128 + lane_addr, tO = tmem + 256 + X * 128 + lane_addr;
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        long long tprev = clock64(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
+        const long long tstart = tprev;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles; j++) {
+            ok = mbar_wait_bounded(b_s_full + X * 8, j & 1) && !*failed;
+            ok = __all_sync(0xffffffffu, ok);
+            TC_ACC(c_ws);
+            if (!ok) break;
+            tc_fence_after();
+            const int kbase = k0 + j * 128;
+            const bool need_mask = (kbase + 127 > qx_min) || (a.window > 0 && kbase + a.window <= max(qx_max, qx_min));
+            // the whole row of S in registers: maximum, exponentials, packed P back over the S columns
+            uint32_t sv[128];
+            tmem_ld128(tS, sv);
+            if (need_mask) {
+#pragma unroll
+                for (int e = 0; e < 128; e++) {
+                    const int kp = kbase + e;
+                    if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) sv[e] = 0xff800000u;  // -inf
+                }
+            }
+            float mx;
+            {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                for (int e = 0; e < 128; e += 4) {
+                    m0 = fmaxf(m0, __uint_as_float(sv[e])); m1 = fmaxf(m1, __uint_as_float(sv[e + 1]));
+                    m2 = fmaxf(m2, __uint_as_float(sv[e + 2])); m3 = fmaxf(m3, __uint_as_float(sv[e + 3]));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * a.scale_log2;
+            }
+            TC_ACC(c_ld);
+            float alpha = 1.f;
+            if (mx > m_ref + 8.f || m_ref == -INFINITY) {
+                alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+                m_ref = mx;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f, sum2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 128; e += 2) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), a.scale_log2, -m_use));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2, -m_use));
+                if (e & 2) sum2 += p0 + p1; else sum += p0 + p1;
+                sv[e >> 1] = pack2<BF16>(p0, p1);  // P pair e/2 reuses a register whose score is already consumed
+            }
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                    ::"r"(tS + c * 16), "r"(sv[c * 16 + 0]), "r"(sv[c * 16 + 1]), "r"(sv[c * 16 + 2]), "r"(sv[c * 16 + 3]), "r"(sv[c * 16 + 4]),
+                      "r"(sv[c * 16 + 5]), "r"(sv[c * 16 + 6]), "r"(sv[c * 16 + 7]), "r"(sv[c * 16 + 8]), "r"(sv[c * 16 + 9]), "r"(sv[c * 16 + 10]),
+                      "r"(sv[c * 16 + 11]), "r"(sv[c * 16 + 12]), "r"(sv[c * 16 + 13]), "r"(sv[c * 16 + 14]), "r"(sv[c * 16 + 15]) : "memory");
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            l_run = l_run * alpha + (sum + sum2);
+            TC_ACC(c_exp);
+            // S_X being full means P V_X of the previous tile has completed (the tensor pipe runs in
+            // order), so O_X may be rescaled now
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                uint32_t ov[128];
+                tmem_ld128(tO, ov);
+#pragma unroll
+                for (int e = 0; e < 128; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+                tmem_st128(tO, ov);
+            }
+            tc_fence_before();
+            mbar_arrive(b_p_full + X * 8);
+            TC_ACC(c_st);
+        }
+        if (a.dbg_buf && tid == 64) {
+            unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16;
+            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = clock64() - tstart;
+        }
+        if (ok) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / l_run;
+            uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) +
+                             ((size_t)sm.tok_off * a.geo.n_q + (size_t)(h * n_rep + (row_ok ? rep : 0)) * sm.snew + (row_ok ? r : 0)) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(tO + c * 32, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        uint4 w;
+                        w.x = pack2<BF16>(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+                        w.y = pack2<BF16>(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+                        w.z = pack2<BF16>(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+                        w.w = pack2<BF16>(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            *failed = 1;
+            atomicOr(a.status, ST_WAIT_TIMEOUT);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+template <bool BF16>
+static cudaError_t launch_tc2(const CUtensorMap& map32, const ChunkArgs& a, cudaStream_t st) {
+    if (a.n_items <= 0) return cudaSuccess;
+    chunk_tc2_kernel<128, BF16><<<a.n_items, kThreads2, tc2_smem_bytes<128>(), st>>>(map32, a);
+    return cudaGetLastError();
+}
+
+bool chunk_tc2_supported(int d) { return d == 128; }
+
+// Two query tiles per CTA (head_dim 128): the work list has one item per pair of tiles.
+cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st) {
+    if (a.geo.d != 128) return cudaErrorInvalidValue;
+    return bf16 ? launch_tc2<true>(map32, a, st) : launch_tc2<false>(map32, a, st);
+}
+
 bool chunk_tc_supported(int d) { return d == 64 || d == 128; }
 
 cudaError_t chunk_tc_init() {
@@ -496,6 +817,8 @@ cudaError_t chunk_tc_init() {
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<64>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<128>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
     return cudaSuccess;
 }
 

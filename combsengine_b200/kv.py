@@ -290,7 +290,8 @@ class KVArena:
                                                1 if overlap_launches else 0))
 
     def set_chunk_kernel(self, mode: int) -> None:
-        """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM chunk kernel."""
+        """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM kernel (one query tile per
+        CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128)."""
         check(self._lib.cbkv_set_chunk_kernel(self._h, mode))
 
     def debug_decode_plan(self, window: int, n_ctas: int) -> dict:

@@ -76,7 +76,7 @@ def test_cfg3_explicit_window_argument_on_global_layers():  # kv.rs:1001-1030, t
         p.step([s], [1], scale=0.9 / 16, window=5)
 
 
-@pytest.mark.parametrize("chunk_kernel", [1, 2])
+@pytest.mark.parametrize("chunk_kernel", [1, 2, 3])
 def test_cfg4_llama_chunked_prefill(chunk_kernel):
     p = Pair(2, 32, 8, 128, 2048, num_pages=256, shuffle_free_list=True, seed=0xC0B50004, chunk_kernel=chunk_kernel)
     seqs = [p.new_seq(), p.new_seq()]
@@ -87,12 +87,13 @@ def test_cfg4_llama_chunked_prefill(chunk_kernel):
     p.assert_state_equal(pages="used")
 
 
-@pytest.mark.parametrize("geom", [(28, 4, 128), (9, 3, 64), (8, 8, 128), (16, 2, 64)])
+@pytest.mark.parametrize("geom", [(28, 4, 128, 2), (9, 3, 64, 2), (8, 8, 128, 2), (16, 2, 64, 2),
+                                  (28, 4, 128, 3), (8, 8, 128, 3), (16, 2, 128, 3)])
 def test_tensor_core_chunk_kernel_shapes_windows_and_ragged_chunks(geom):
-    # tcgen05 kernel forced: q-head groups of 7, 3, 1 and 8; windows; chunks that do not fill a tile
-    n_q, n_kv, d = geom
+    # tcgen05 kernels forced: q-head groups of 7, 3, 1 and 8; windows; chunks that do not fill a tile
+    n_q, n_kv, d, kernel = geom
     p = Pair(2, n_q, n_kv, d, 4096, num_pages=300, shuffle_free_list=True, seed=n_q * 7 + d, windows=[None, 200],
-             chunk_kernel=2, popn_refuses=False)
+             chunk_kernel=kernel, popn_refuses=False)
     seqs = [p.new_seq(), p.new_seq(), p.new_seq()]
     p.step(seqs, [300, 17, 129])
     p.step(seqs, [130, 256, 1])
