@@ -556,9 +556,10 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
                     dbg_merges++; dbg_parts += nparts;
-                    // Merging is deferred to the end of the CTA, where the consumer warps are idle
-                    // and help (below); only a fifth segment in one CTA is merged here and now.
-                    if (n_deferred < 4) deferred[n_deferred++] = seg;
+                    // Near the end of the CTA the merge is deferred: the consumer warps are idle then
+                    // and help (below).  With plenty of tiles still to stream this warp merges alone,
+                    // off the consumers' path, so the end of the CTA is not burdened with it.
+                    if (u1 - pe < 24 && n_deferred < 4) deferred[n_deferred++] = seg;
                     else merge_parts<D, BF16>(a, a.seg_part_base[seg], nparts, out_row, n_rep, lane, 32);
                 }
             }
