@@ -330,7 +330,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         peak, peak_src = 6650.0, "fallback"
 
     traffic = None
-    tpath = os.path.join(ROOT, "profiles", f"decode_kernel_{args.config}_traffic.json")
+    tpath = os.path.join(ROOT, "profiles", f"decode_kernel_{args.config}_traffic.txt")
     if os.path.exists(tpath) and not args.layers:
         traffic = float(json.load(open(tpath))["traffic_bytes_per_launch"])  # from the committed ncu capture
 

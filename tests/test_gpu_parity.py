@@ -198,3 +198,48 @@ def test_host_buffer_entry_point_matches_device_one():
         refs.append(g.attention(0, qs[i].cuda(), k.cuda(), v.cuda(), 0.1).cpu())
     for o, r in zip(outs, refs):
         assert torch.equal(o, r)
+
+
+def test_one_long_sequence_is_cut_into_many_parts():
+    # a single 20 000-token sequence: every (kv head) segment is split over dozens of CTAs, so the
+    # ticket merge runs with far more than eight partials
+    from combsengine_b200 import KVArena
+    from oracle import OracleArena
+    n_q, n_kv, d, L = 28, 4, 128, 20000
+    rng = np.random.default_rng(77)
+    g = KVArena(1, n_q, n_kv, d, L + 64, num_pages=1300)
+    o = OracleArena(1, n_kv, d, L + 64, num_pages=1300, rolling=False, dtype="f16")
+    perm = rng.permutation(1300)
+    g.set_free_list(perm); o.set_free_list(perm)
+    gs, os_ = g.new_seq(), o.new_seq()
+    k = rng.standard_normal((n_kv, L, d)).astype(np.float16)
+    v = rng.standard_normal((n_kv, L, d)).astype(np.float16)
+    g.begin_step([gs], [L])
+    g.append(0, torch.from_numpy(k.reshape(-1)).cuda(), torch.from_numpy(v.reshape(-1)).cuda())
+    o.batch_begin([os_], [L])
+    os_.append_only(0, k, v, 0)
+    for step, window in enumerate([None, None, 4000]):
+        q, k1, v1 = (rng.standard_normal((h, 1, d)).astype(np.float16) for h in (n_q, n_kv, n_kv))
+        g.begin_step([gs], [1])
+        got = g.attention(0, *(torch.from_numpy(x.reshape(-1)).cuda() for x in (q, k1, v1)), d ** -0.5, window).cpu().numpy()
+        o.batch_begin([os_], [1])
+        ref = o.batch_layer([os_], [1], 0, q.reshape(-1), k1.reshape(-1), v1.reshape(-1), n_q, d ** -0.5, window)
+        assert_attention_close(got, ref, f"long sequence step {step}")
+    assert g.device_status() == 0
+
+
+def test_empty_step_smallest_window_and_exact_capacity():
+    from combsengine_b200 import CbkvError
+    p = Pair(1, 8, 2, 64, 48, seed=13)
+    p.g.begin_step([], [])                      # an empty step is legal and launches nothing
+    s = p.new_seq()
+    p.step([s], [30], window=2)                 # the smallest window: each query sees itself and one key before
+    for _ in range(17):
+        p.step([s], [1], window=2)
+    assert s[0].seq_len() == 47
+    p.step([s], [1])                            # exactly max_seq_len tokens
+    assert s[0].seq_len() == 48 and s[0].pages_used() == 3
+    with pytest.raises(CbkvError, match="capacity exceeded: 49 > 48"):
+        p.g.begin_step([s[0]], [1])
+    assert s[0].seq_len() == 48
+    p.assert_state_equal()
