@@ -257,6 +257,11 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->tile_plan_ok = false;
     d->tile_item_begin = nullptr;
     d->step = StepDev{};
+    d->last_kv_writer = -1;  // the upload is a full stream dependency
+    if (a->step_meta.empty()) {  // an empty step: nothing to upload, nothing will launch
+        d->uploaded_step = a->step_id;
+        return CBKV_OK;
+    }
     const void* p = nullptr;
     int32_t rc = slot_upload(d, a->step_meta.data(), a->step_meta.size() * sizeof(SeqMeta), st, &p);
     if (rc) return rc;
@@ -267,7 +272,6 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->step.n_seqs = (int32_t)a->step_meta.size();
     d->step.n_tokens = (int32_t)a->step_tokens;
     d->uploaded_step = a->step_id;
-    d->last_kv_writer = -1;  // the upload is a full stream dependency
     return CBKV_OK;
 }
 
@@ -544,6 +548,7 @@ int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void*
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
     if (!k || !v) { set_error("null k/v"); return CBKV_ERR_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CU_TRY(cudaSetDevice(dev_of(a)->device));
@@ -556,6 +561,7 @@ int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, vo
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
     if (!q || !out) { set_error("null q/out"); return CBKV_ERR_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CU_TRY(cudaSetDevice(dev_of(a)->device));
@@ -568,6 +574,7 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
     if (!q || !k || !v || !out) { set_error("null tensor"); return CBKV_ERR_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     DeviceState* d = dev_of(a);
@@ -583,6 +590,7 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
     if (!q_host || !k_host || !v_host || !out_host) { set_error("null tensor"); return CBKV_ERR_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     DeviceState* d = dev_of(a);
@@ -616,6 +624,7 @@ int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* 
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
     if (!q_host || !k_host || !v_host || !out_host) { set_error("null tensor"); return CBKV_ERR_ARG; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     DeviceState* d = dev_of(a);

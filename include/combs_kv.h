@@ -112,7 +112,8 @@ int32_t cbkv_seq_fork_prefix(cbkv_seq* parent, int64_t n_tokens, cbkv_seq** out)
  * (kv.rs:549-559) for every sequence of the step, in the order given:
  * requires pos[b] == seq_len (pass pos = NULL to skip the check), advances
  * seq_len by new_tokens[b], allocates pages, and uploads the step's block tables
- * and work partition to the device on `stream`. */
+ * and work partition to the device on `stream`.  n_seqs = 0 opens an empty step:
+ * the attention and append calls that follow return 0 and launch nothing. */
 int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
                         const int64_t* pos, int32_t n_seqs, void* stream);
 

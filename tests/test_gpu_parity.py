@@ -231,7 +231,12 @@ def test_one_long_sequence_is_cut_into_many_parts():
 def test_empty_step_smallest_window_and_exact_capacity():
     from combsengine_b200 import CbkvError
     p = Pair(1, 8, 2, 64, 48, seed=13)
+    from combsengine_b200.kv import launch_count
+    before = launch_count()
     p.g.begin_step([], [])                      # an empty step is legal and launches nothing
+    e = torch.empty(0, dtype=torch.float16, device="cuda")
+    assert p.g.attention(0, e, e, e, 0.125).numel() == 0
+    assert launch_count() == before
     s = p.new_seq()
     p.step([s], [30], window=2)                 # the smallest window: each query sees itself and one key before
     for _ in range(17):

@@ -264,3 +264,12 @@ def test_compute_fails_loudly_without_a_gpu():
     assert rc == -5 and b"no CPU path" in lib.cbkv_last_error()
     assert s.seq_len() == 0  # nothing advanced
     assert lib.cbkv_attention(a._h, 0, None, None, None, None, 1.0, 0, None) == -6  # no step begun
+
+
+def test_empty_step_changes_nothing():
+    a = KVArena(2, 8, 2, 64, 64, num_pages=8)
+    s = a.new_seq()
+    a.begin_step_host_only([s], [20])
+    free = a.num_free_pages()
+    a.begin_step_host_only([], [])
+    assert s.seq_len() == 20 and s.pages_used() == 2 and a.num_free_pages() == free
