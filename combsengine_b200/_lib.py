@@ -27,6 +27,19 @@ class cbkv_page_stats_t(C.Structure):
                                    "layers_materialized", "layers_total", "layers_sliding")]
 
 
+class cbkv_rope_config(C.Structure):
+    _fields_ = [
+        ("head_dim", I32), ("scaling", I32), ("theta", F64), ("max_position", I64), ("factor", F64),
+        ("low_freq_factor", F64), ("high_freq_factor", F64), ("beta_fast", F64), ("beta_slow", F64),
+        ("original_max_position", I64), ("has_attention_factor", I32), ("attention_factor", F64),
+        ("short_factor", C.POINTER(F64)), ("n_short_factor", I32),
+    ]
+
+
+class cbkv_qk_norm(C.Structure):
+    _fields_ = [("q_weight", P), ("k_weight", P), ("eps", F64), ("gemma", I32)]
+
+
 # name -> (restype, argtypes); every symbol include/combs_kv.h declares
 PROTOTYPES = {
     "cbkv_last_error": (C.c_char_p, []),
@@ -42,6 +55,12 @@ PROTOTYPES = {
     "cbkv_attention": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_attention_host": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_decode_attention_static": (I32, [P, I64, P, I32, C.POINTER(I32), I32, I32, I32, I32, I32, P, P, F64, I64, P]),
+    "cbkv_rope_tables_host": (I32, [C.POINTER(cbkv_rope_config), P, P]),
+    "cbkv_rope_inv_freq_host": (I32, [C.POINTER(cbkv_rope_config), P, C.POINTER(F64)]),
+    "cbkv_rope_create": (I32, [P, C.POINTER(cbkv_rope_config), C.POINTER(P)]),
+    "cbkv_rope_destroy": (I32, [P]),
+    "cbkv_rope_append": (I32, [P, I32, P, C.POINTER(cbkv_qk_norm), P, P, P, P, P]),
+    "cbkv_attention_rope": (I32, [P, I32, P, C.POINTER(cbkv_qk_norm), P, P, P, P, F64, I64, P]),
     "cbkv_attention_host_async": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_host_sync": (I32, [P]),
     "cbkv_host_alloc": (I32, [C.c_size_t, C.POINTER(P)]),

@@ -3,6 +3,8 @@
 // kernel selection and launch.  The host bookkeeping itself is manager.cpp.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <atomic>
 #include <algorithm>
@@ -94,6 +96,9 @@ struct DeviceState {
     // host-buffer entry point staging
     uint8_t* io = nullptr;
     size_t io_cap = 0;
+    // rotated q of the current layer (cbkv_attention_rope)
+    uint8_t* qrot = nullptr;
+    size_t qrot_cap = 0;
     // pipelined host-buffer entry point: copy streams, rotating staging slots
     struct IoSlot {
         uint8_t* dev = nullptr;
@@ -494,6 +499,7 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
         if (d->seg_counter) cudaFree(d->seg_counter);
         if (d->status) cudaFree(d->status);
         if (d->io) cudaFree(d->io);
+        if (d->qrot) cudaFree(d->qrot);
         for (auto& sl : d->io_slots) {
             if (sl.dev) cudaFree(sl.dev);
             if (sl.in_done) { cudaEventDestroy(sl.in_done); cudaEventDestroy(sl.k_done); cudaEventDestroy(sl.out_done); }
@@ -583,6 +589,155 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
     if (d->fast && a->step_is_decode) return run_attention(a, layer, q, k, v, out, scale, window, st);
     if ((rc = run_append(a, layer, k, v, st))) return rc;
     return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
+}
+
+// ---- rotary embedding + QK norm fused into the append (rope.cu) ----------------
+struct Rope {
+    Arena* arena;
+    int device;
+    int head_dim;
+    int64_t max_position;
+    void* table;  // [max_position][head_dim/2] (cos, sin) pairs in the arena's element type
+};
+
+static int32_t check_rope_cfg(const cbkv_rope_config* c) {
+    if (!c) { set_error("null rope config"); return CBKV_ERR_ARG; }
+    if (c->head_dim < 4 || c->head_dim % 4 != 0 || c->head_dim > 512) {
+        set_error("rope head_dim must be a multiple of 4 in [4, 512]"); return CBKV_ERR_ARG;
+    }
+    if (c->max_position < 1 || !(c->theta > 0.0)) { set_error("rope needs max_position >= 1 and theta > 0"); return CBKV_ERR_ARG; }
+    if (c->scaling < CBKV_ROPE_NONE || c->scaling > CBKV_ROPE_LONGROPE) { set_error("unknown rope scaling"); return CBKV_ERR_ARG; }
+    return CBKV_OK;
+}
+
+int32_t cbkv_rope_inv_freq_host(const cbkv_rope_config* cfg, double* inv_out, double* mscale_out) {
+    int32_t rc = check_rope_cfg(cfg);
+    if (rc) return rc;
+    if (!inv_out || !mscale_out) { set_error("null output"); return CBKV_ERR_ARG; }
+    std::vector<double> inv;
+    if ((rc = rope_inv_freq(*cfg, &inv, mscale_out))) return rc;
+    std::copy(inv.begin(), inv.end(), inv_out);
+    return CBKV_OK;
+}
+
+int32_t cbkv_rope_tables_host(const cbkv_rope_config* cfg, float* cos_out, float* sin_out) {
+    int32_t rc = check_rope_cfg(cfg);
+    if (rc) return rc;
+    if (!cos_out || !sin_out) { set_error("null output"); return CBKV_ERR_ARG; }
+    std::vector<double> inv;
+    double mscale = 1.0;
+    if ((rc = rope_inv_freq(*cfg, &inv, &mscale))) return rc;
+    rope_tables(*cfg, inv, mscale, cos_out, sin_out);
+    return CBKV_OK;
+}
+
+int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_rope** out) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
+    int32_t rc = check_rope_cfg(cfg);
+    if (rc) return rc;
+    if (cfg->head_dim != a->cfg.head_dim) { set_error("rope head_dim differs from the arena's"); return CBKV_ERR_ARG; }
+    if ((rc = ensure_device(a))) return rc;
+    const int64_t n = cfg->max_position * cfg->head_dim;
+    std::vector<float> cosv((size_t)n), sinv((size_t)n);
+    if ((rc = cbkv_rope_tables_host(cfg, cosv.data(), sinv.data()))) return rc;
+    // device layout: per position head_dim/2 (cos, sin) pairs, f32 -> element type (rope.rs:167-176)
+    const int half = cfg->head_dim / 2;
+    std::vector<uint16_t> packed((size_t)cfg->max_position * half * 2);
+    const bool bf16 = a->cfg.dtype == CBKV_BF16;
+    auto conv = [&](float f) -> uint16_t {
+        if (bf16) { __nv_bfloat16 h = __float2bfloat16_rn(f); uint16_t u; memcpy(&u, &h, 2); return u; }
+        __half h = __float2half_rn(f); uint16_t u; memcpy(&u, &h, 2); return u;
+    };
+    for (int64_t p = 0; p < cfg->max_position; p++)
+        for (int i = 0; i < half; i++) {
+            packed[(size_t)((p * half + i) * 2)] = conv(cosv[(size_t)(p * cfg->head_dim + i)]);
+            packed[(size_t)((p * half + i) * 2 + 1)] = conv(sinv[(size_t)(p * cfg->head_dim + i)]);
+        }
+    auto* r = new Rope{a, dev_of(a)->device, cfg->head_dim, cfg->max_position, nullptr};
+    cudaError_t e = cudaMalloc(&r->table, packed.size() * 2);
+    if (e == cudaSuccess) e = cudaMemcpy(r->table, packed.data(), packed.size() * 2, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (r->table) cudaFree(r->table);
+        delete r;
+        set_error(std::string("rope table upload: ") + cudaGetErrorString(e));
+        return CBKV_ERR_CUDA;
+    }
+    *out = reinterpret_cast<cbkv_rope*>(r);
+    return CBKV_OK;
+}
+
+int32_t cbkv_rope_destroy(cbkv_rope* rope) {
+    Rope* r = reinterpret_cast<Rope*>(rope);
+    if (!r) return CBKV_OK;
+    cudaSetDevice(r->device);
+    if (r->table) cudaFree(r->table);
+    delete r;
+    return CBKV_OK;
+}
+
+static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk_norm* norm, const void* q, const void* k,
+                               const void* v, void* q_out, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    if (r->arena != a) { set_error("rope tables belong to another arena"); return CBKV_ERR_ARG; }
+    for (const SeqMeta& m : a->step_meta)
+        if ((int64_t)m.pos + m.snew > r->max_position) {
+            set_error("rope table shorter than the step's positions: " + std::to_string((int64_t)m.pos + m.snew) + " > " +
+                      std::to_string(r->max_position));
+            return CBKV_ERR_ARG;
+        }
+    RopeArgs args{};
+    args.step = d->step; args.geo = geom(a);
+    args.q = q; args.k = k; args.v = v; args.q_out = q_out;
+    args.arena = d->layers[(size_t)layer].base;
+    args.table = r->table; args.max_position = r->max_position;
+    args.q_weight = norm ? norm->q_weight : nullptr;
+    args.k_weight = norm ? norm->k_weight : nullptr;
+    args.eps = norm ? (float)norm->eps : 0.f;
+    args.gemma = norm ? norm->gemma : 0;
+    args.status = d->status;
+    CU_TRY(launch_rope_append(args, a->cfg.dtype == CBKV_BF16, st));
+    g_launches++;
+    d->last_kv_writer = layer;
+    return CBKV_OK;
+}
+
+int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
+                         const void* q, const void* k, const void* v, void* q_out, void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
+    if (!rope || !q || !k || !v || !q_out) { set_error("null argument"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU_TRY(cudaSetDevice(dev_of(a)->device));
+    if ((rc = materialize(a, layer, st))) return rc;
+    return run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, q_out, st);
+}
+
+int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
+                            const void* q, const void* k, const void* v, void* out, double scale, int64_t window,
+                            void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    int32_t rc = check_step(a, layer);
+    if (rc) return rc;
+    if (a->step_tokens == 0) return CBKV_OK;  // empty step
+    if (!rope || !q || !k || !v || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    if ((rc = materialize(a, layer, st))) return rc;
+    const size_t qb = (size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2;
+    if (qb > d->qrot_cap) {
+        CU_TRY(cudaStreamSynchronize(st));  // an earlier layer may still read the old buffer
+        if (d->qrot) cudaFree(d->qrot);
+        d->qrot = nullptr;
+        d->qrot_cap = 0;
+        CU_TRY(cudaMalloc(&d->qrot, qb * 2));
+        d->qrot_cap = qb * 2;
+    }
+    if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, d->qrot, st))) return rc;
+    return run_attention(a, layer, d->qrot, nullptr, nullptr, out, scale, window, st);
 }
 
 int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,

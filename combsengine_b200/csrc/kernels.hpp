@@ -114,6 +114,25 @@ struct GenericArgs {
     float scale;
 };
 
+// Rotate-and-append (rope.cu).  `table` holds, per position, head_dim/2 (cos, sin) pairs in the
+// storage type; q_weight / k_weight (head_dim elements, storage type) are null without QK norm.
+struct RopeArgs {
+    StepDev step;
+    GeomDev geo;
+    const void* q;
+    const void* k;
+    const void* v;
+    void* q_out;
+    void* arena;
+    const void* table;
+    int64_t max_position;
+    const void* q_weight;
+    const void* k_weight;
+    float eps;
+    int32_t gemma;
+    int32_t* status;
+};
+
 // Decode kernel configuration for a head_dim (0 warps = not supported by the fast path).
 struct DecodeConfig { int consumers, stages, smem_bytes, ctas_per_sm, comb_cols, comb_bufs; };
 DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers);
@@ -124,6 +143,10 @@ cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st);
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, cudaStream_t st);
+// host side of the rotary tables (rope.cu): frequencies, then [max_position][head_dim] f32 tables
+int32_t rope_inv_freq(const cbkv_rope_config& c, std::vector<double>* inv, double* mscale);
+void rope_tables(const cbkv_rope_config& c, const std::vector<double>& inv, double mscale, float* cos_out, float* sin_out);
 // tcgen05 chunk kernel (prefill_tc.cu): head_dim 64 or 128; `map` is the 16-row box view
 bool chunk_tc_supported(int d);
 cudaError_t chunk_tc_init();

@@ -148,6 +148,62 @@ int32_t cbkv_host_sync(cbkv_arena* arena);
 int32_t cbkv_host_alloc(size_t bytes, void** out);
 int32_t cbkv_host_free(void* p);
 
+/* ---- the step right before the cache: rotary embedding and QK norm, fused into the append ----
+ *
+ * The model rotates q and k (RotaryEmbedding::apply, combs-models/src/rope.rs:180-204) after an
+ * optional per-head RMS norm (combs-models/src/llama.rs:275-281, norm.rs:11-39) and only then calls
+ * the cache (llama.rs:283-289).  These entry points take the UN-rotated q and k and do all of it in
+ * one launch that writes k and v into their page slots and the rotated q into a dense buffer. */
+enum { CBKV_ROPE_NONE = 0, CBKV_ROPE_LINEAR = 1, CBKV_ROPE_LLAMA3 = 2, CBKV_ROPE_YARN = 3, CBKV_ROPE_LONGROPE = 4 };
+
+/* RotaryEmbedding::new_scaled + combs_formats::RopeScaling (rope.rs:31-125,160-177). */
+typedef struct cbkv_rope_config {
+    int32_t head_dim;
+    int32_t scaling;                /* CBKV_ROPE_* */
+    double theta;
+    int64_t max_position;           /* rows of the tables */
+    double factor;                  /* linear, llama3, yarn, longrope */
+    double low_freq_factor;         /* llama3 */
+    double high_freq_factor;        /* llama3 */
+    double beta_fast, beta_slow;    /* yarn */
+    int64_t original_max_position;  /* llama3, yarn, longrope */
+    int32_t has_attention_factor;   /* yarn, longrope: 0 = derive it as the reference does */
+    double attention_factor;
+    const double* short_factor;     /* longrope: head_dim/2 divisors (missing entries = 1) */
+    int32_t n_short_factor;
+} cbkv_rope_config;
+
+typedef struct cbkv_rope cbkv_rope;
+
+/* build_tables_scaled (rope.rs:129-151) on the host: cos and sin [max_position][head_dim] f32.
+ * Needs no device. */
+int32_t cbkv_rope_tables_host(const cbkv_rope_config* cfg, float* cos_out, float* sin_out);
+/* scaled_inv_freq (rope.rs:31-125): head_dim/2 frequencies and the table multiplier. */
+int32_t cbkv_rope_inv_freq_host(const cbkv_rope_config* cfg, double* inv_freq_out, double* mscale_out);
+/* Tables on the arena's device in the arena's element type (rope.rs:160-177). */
+int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_rope** out);
+int32_t cbkv_rope_destroy(cbkv_rope* rope);
+
+/* Per-head norm of q and k over head_dim before the rotation: weights are device pointers to
+ * head_dim elements of the arena's type, either may be NULL; gemma != 0 scales by (1 + w)
+ * (norm.rs:33-39). */
+typedef struct cbkv_qk_norm {
+    const void* q_weight;
+    const void* k_weight;
+    double eps;
+    int32_t gemma;
+} cbkv_qk_norm;
+
+/* norm (optional, NULL = none) + rotate q -> q_out (may alias q), norm + rotate k -> pages,
+ * v -> pages, for the step opened by cbkv_begin_step.  Positions are the step's (pos + row). */
+int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
+                         const void* q, const void* k, const void* v, void* q_out, void* stream);
+/* cbkv_rope_append into an internal buffer followed by cbkv_paged_attention: the whole of
+ * llama.rs:275-289 for one layer. */
+int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
+                            const void* q, const void* k, const void* v, void* out, double scale, int64_t window,
+                            void* stream);
+
 /* No counterpart in the reference.  Decode attention over pages the CALLER owns, for
  * callers that must not allocate device memory while they run (a server that gave
  * the whole GPU to its own pool at start-up, a plugin inside a host that forbids

@@ -28,7 +28,7 @@ def build(force: bool = False) -> None:
     """Compile the oracle (gcc, a few seconds)."""
     out = os.path.join(_HERE, "_build")
     if not force and all(os.path.exists(os.path.join(out, f"liborc_{k}.so")) for k in ("f32", "f16")):
-        src = os.path.getmtime(os.path.join(_HERE, "kv_oracle.c"))
+        src = max(os.path.getmtime(os.path.join(_HERE, f)) for f in ("kv_oracle.c", "rope_oracle.c", "Makefile"))
         if all(os.path.getmtime(os.path.join(out, f"liborc_{k}.so")) >= src for k in ("f32", "f16")):
             return
     subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
@@ -305,3 +305,65 @@ class OracleContiguous:
 
     def popn(self, n):  # KVCache default, kv.rs:133-136
         return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# Rotary embedding and QK norm (rope_oracle.c): the step right before the cache.
+ROPE_KINDS = {"none": 0, "linear": 1, "llama3": 2, "yarn": 3, "longrope": 4}
+
+
+def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
+    """``scaled_inv_freq`` (rope.rs:31-125) -> (inv_freq f64[head_dim/2], mscale)."""
+    s = dict(scaling or {})
+    kind = ROPE_KINDS[s.get("kind", "none")]
+    lib = _lib("f32")
+    lib.orc_rope_inv_freq.argtypes = [C.c_int, C.c_double, C.c_int, C.c_double, C.c_double, C.c_double, C.c_double,
+                                      C.c_double, I64, C.c_double, P, C.c_int, P, P]
+    inv = np.zeros(head_dim // 2, dtype=np.float64)
+    ms = C.c_double(0.0)
+    short = np.ascontiguousarray(s.get("short_factor", []), dtype=np.float64)
+    af = s.get("attention_factor")
+    rc = lib.orc_rope_inv_freq(head_dim, float(theta), kind, float(s.get("factor", 1.0)),
+                               float(s.get("low_freq_factor", 1.0)), float(s.get("high_freq_factor", 1.0)),
+                               float(s.get("beta_fast", 32.0)), float(s.get("beta_slow", 1.0)),
+                               int(s.get("original_max_position_embeddings", 0)),
+                               float("nan") if af is None else float(af),
+                               _ptr(short) if len(short) else None, len(short), _ptr(inv), C.byref(ms))
+    if rc:
+        raise OracleError(rc, "unknown rope scaling kind")
+    return inv, ms.value
+
+
+def rope_tables(head_dim: int, theta: float, max_position: int, scaling: dict | None = None):
+    """``build_tables_scaled`` (rope.rs:129-151) -> (cos, sin) f32 [max_position, head_dim]."""
+    inv, ms = rope_inv_freq(head_dim, theta, scaling)
+    lib = _lib("f32")
+    lib.orc_rope_tables.argtypes = [C.c_int, I64, P, C.c_double, P, P]
+    cos = np.zeros((max_position, head_dim), dtype=np.float32)
+    sin = np.zeros_like(cos)
+    lib.orc_rope_tables(head_dim, max_position, _ptr(inv), ms, _ptr(cos), _ptr(sin))
+    return cos, sin
+
+
+def rope_apply(x: np.ndarray, pos: int, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """``RotaryEmbedding::apply`` (rope.rs:180-204) on x [heads, seq, d] (f16 or f32)."""
+    kind = "f16" if x.dtype == np.float16 else "f32"
+    lib = _lib(kind)
+    lib.orc_rope_apply.argtypes = [P, C.c_int, I64, C.c_int, I64, P, P]
+    out = np.ascontiguousarray(x).copy()
+    heads, seq, d = out.shape
+    assert cos.shape[1] == d and pos + seq <= cos.shape[0], "position outside the rope table"
+    lib.orc_rope_apply(_ptr(out), heads, seq, d, int(pos), _ptr(np.ascontiguousarray(cos)), _ptr(np.ascontiguousarray(sin)))
+    return out
+
+
+def rms_norm(x: np.ndarray, w: np.ndarray, eps: float, gemma: bool = False) -> np.ndarray:
+    """``rms_norm`` / ``gemma_rms_norm`` (norm.rs:11-39) over the last dim."""
+    kind = "f16" if x.dtype == np.float16 else "f32"
+    lib = _lib(kind)
+    lib.orc_rms_norm.argtypes = [P, I64, C.c_int, P, C.c_double, C.c_int]
+    out = np.ascontiguousarray(x).copy()
+    d = out.shape[-1]
+    w = np.ascontiguousarray(w, dtype=x.dtype)
+    lib.orc_rms_norm(_ptr(out), out.size // d, d, _ptr(w), float(eps), 1 if gemma else 0)
+    return out
