@@ -428,6 +428,79 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     }), flush=True)
 
 
+def run_rope(args, rank: int, world: int, local_rank: int) -> None:
+    """The step before the path, fused: per-head norm off, rotary embedding of q and k, k and v
+    written into page slots, one launch per layer.  Workload: one 512-token chunk of each of the
+    8 prompts of cfg4 (Llama-3-8B geometry 32/8/128, theta 500000), positions 4096..4607."""
+    import time
+    import torch
+    from combsengine_b200 import KVArena
+    from combsengine_b200 import rope as R
+
+    layers, n_q, n_kv, d, batch, prefix, chunk = 32, 32, 8, 128, 8, 4096, 512
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    arena = KVArena(layers, n_q, n_kv, d, prefix + chunk, 16, batch * ((prefix + chunk) // 16), device=local_rank)
+    arena.set_free_list(np.random.default_rng(0xC0B50004).permutation(arena.num_pages))
+    seqs = [arena.new_seq() for _ in range(batch)]
+    rope = R.RotaryEmbedding(arena, 500000.0, prefix + chunk)
+    gen = torch.Generator(device=dev).manual_seed(0xC0B50004)
+    ntok = batch * chunk
+    nbuf = 4  # rotate over 4 input sets (4 x 50 MB) so that reads come from HBM, not L2
+    q = [torch.randn(ntok * n_q * d, device=dev, generator=gen).half() for _ in range(nbuf)]
+    k = [torch.randn(ntok * n_kv * d, device=dev, generator=gen).half() for _ in range(nbuf)]
+    v = [torch.randn(ntok * n_kv * d, device=dev, generator=gen).half() for _ in range(nbuf)]
+    qo = [torch.empty_like(q[0]) for _ in range(nbuf)]
+    arena.begin_step(seqs, [prefix] * batch)       # the prefix's pages (contents irrelevant here)
+    arena.begin_step(seqs, [chunk] * batch)
+    stream = torch.cuda.current_stream()
+
+    def one_pass():
+        for layer in range(layers):
+            i = layer % nbuf
+            R.rope_append(arena, layer, rope, q[i], k[i], v[i], q_out=qo[i])
+
+    for _ in range(max(3, args.warmup // 4)):
+        one_pass()
+    torch.cuda.synchronize()
+    passes = max(2, args.steps // 4)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(passes):
+        one_pass()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (passes * layers)
+    assert arena.device_status() == 0
+    elems = ntok * d * 2
+    alg = 2 * elems * n_q + 4 * elems * n_kv + ntok * (d // 2) * 4   # q r+w, k r+w, v r+w, one table row per token
+    peaks = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks))["hbm_gbs"]) if os.path.exists(peaks) else 6650.0
+    gbs = alg / (us * 1e-6) / 1e9
+    cpu = None
+    if not args.no_cpu:
+        import oracle
+        oracle.build()
+        cos, sin = oracle.rope_tables(d, 500000.0, prefix + chunk)
+        xq = np.random.default_rng(1).standard_normal((n_q, chunk, d)).astype(np.float16)
+        xk = xq[:n_kv].copy()
+        t0 = time.perf_counter()
+        oracle.rope_apply(xq, prefix, cos, sin); oracle.rope_apply(xk, prefix, cos, sin)
+        dt = time.perf_counter() - t0
+        cpu = {"value": chunk / dt, "unit": "tokens/s", "cores": 1, "kind": "port",
+               "sample": f"rotation of q and k of one 512-token chunk of one prompt in {dt:.2f} s (scatter not included)"}
+    print(json.dumps({
+        "metric": "rope_append_tokens_per_s", "value": ntok / (us * 1e-6), "unit": "tokens/s", "n_gpus": 1,
+        "steps": passes * layers, "warmup": max(3, args.warmup // 4) * layers, "ms_per_step": us * 1e-3,
+        "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "rotary embedding of q,k + append of k,v for a 512-token chunk of 8 prompts, 32/8/128, one launch per layer",
+                   "l2": "four rotating input sets (200 MB) and 32 destination layers: larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "kernel": "rope_append_kernel<f16>", "us_per_launch": us, "algorithmic_bytes_per_launch": alg},
+        "gpu_launches": passes * layers, "cpu_baseline": cpu,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -435,7 +508,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync, 2 = tcgen05 one tile per CTA, 3 = tcgen05 two tiles per CTA")
-    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"],
+    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "rope"],
                     help="cfg2 is the headline workload; cfg3 (windows, d=256) and cfg5 (shared prefix, long tails) on request")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
@@ -446,6 +519,8 @@ def main():
     args = ap.parse_args()
     if args.config == "cfg4":
         return run_prefill(args, int(os.environ.get("RANK", "0")), 1, int(os.environ.get("LOCAL_RANK", "0")))
+    if args.config == "rope":
+        return run_rope(args, int(os.environ.get("RANK", "0")), 1, int(os.environ.get("LOCAL_RANK", "0")))
     select_config(args.config)
     if args.layers:
         global LAYERS, WINDOWS

@@ -597,7 +597,7 @@ struct Rope {
     int device;
     int head_dim;
     int64_t max_position;
-    void* table;  // [max_position][head_dim/2] (cos, sin) pairs in the arena's element type
+    void* table;  // [max_position][cos: head_dim/2 | sin: head_dim/2] in the arena's element type
 };
 
 static int32_t check_rope_cfg(const cbkv_rope_config* c) {
@@ -641,7 +641,8 @@ int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_ro
     const int64_t n = cfg->max_position * cfg->head_dim;
     std::vector<float> cosv((size_t)n), sinv((size_t)n);
     if ((rc = cbkv_rope_tables_host(cfg, cosv.data(), sinv.data()))) return rc;
-    // device layout: per position head_dim/2 (cos, sin) pairs, f32 -> element type (rope.rs:167-176)
+    // device layout: per position head_dim/2 cosines then head_dim/2 sines, f32 -> element type
+    // (rope.rs:167-176)
     const int half = cfg->head_dim / 2;
     std::vector<uint16_t> packed((size_t)cfg->max_position * half * 2);
     const bool bf16 = a->cfg.dtype == CBKV_BF16;
@@ -651,8 +652,8 @@ int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_ro
     };
     for (int64_t p = 0; p < cfg->max_position; p++)
         for (int i = 0; i < half; i++) {
-            packed[(size_t)((p * half + i) * 2)] = conv(cosv[(size_t)(p * cfg->head_dim + i)]);
-            packed[(size_t)((p * half + i) * 2 + 1)] = conv(sinv[(size_t)(p * cfg->head_dim + i)]);
+            packed[(size_t)(p * 2 * half + i)] = conv(cosv[(size_t)(p * cfg->head_dim + i)]);
+            packed[(size_t)(p * 2 * half + half + i)] = conv(sinv[(size_t)(p * cfg->head_dim + i)]);
         }
     auto* r = new Rope{a, dev_of(a)->device, cfg->head_dim, cfg->max_position, nullptr};
     cudaError_t e = cudaMalloc(&r->table, packed.size() * 2);

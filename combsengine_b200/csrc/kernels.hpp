@@ -114,8 +114,8 @@ struct GenericArgs {
     float scale;
 };
 
-// Rotate-and-append (rope.cu).  `table` holds, per position, head_dim/2 (cos, sin) pairs in the
-// storage type; q_weight / k_weight (head_dim elements, storage type) are null without QK norm.
+// Rotate-and-append (rope.cu).  `table` holds, per position, head_dim/2 cosines then head_dim/2 sines in
+// the storage type; q_weight / k_weight (head_dim elements, storage type) are null without QK norm.
 struct RopeArgs {
     StepDev step;
     GeomDev geo;
