@@ -61,6 +61,16 @@ PROTOTYPES = {
     "cbkv_rope_destroy": (I32, [P]),
     "cbkv_rope_append": (I32, [P, I32, P, C.POINTER(cbkv_qk_norm), P, P, P, P, P]),
     "cbkv_attention_rope": (I32, [P, I32, P, C.POINTER(cbkv_qk_norm), P, P, P, P, F64, I64, P]),
+    "cbkv_sessions_create": (I32, [P, I32, C.POINTER(P)]),
+    "cbkv_sessions_destroy": (I32, [P]),
+    "cbkv_sessions_acquire": (I32, [P, C.c_char_p, P, I64, I32, C.POINTER(P), C.POINTER(I64)]),
+    "cbkv_sessions_release": (I32, [P, C.c_char_p, P, P, I64, I32]),
+    "cbkv_sessions_clear": (I32, [P, C.POINTER(I64)]),
+    "cbkv_sessions_count": (I64, [P]),
+    "cbkv_sessions_evictions": (I64, [P]),
+    "cbkv_sessions_history_len": (I64, [P, C.c_char_p]),
+    "cbkv_spec_verify_rollback": (I32, [P, P, P, I32, C.POINTER(I32), C.POINTER(C.c_uint32)]),
+    "cbkv_sessions_stats_json": (I64, [P, C.c_char_p, I64]),
     "cbkv_attention_host_async": (I32, [P, I32, P, P, P, P, F64, I64, P]),
     "cbkv_host_sync": (I32, [P]),
     "cbkv_host_alloc": (I32, [C.c_size_t, C.POINTER(P)]),

@@ -204,6 +204,39 @@ int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* r
                             const void* q, const void* k, const void* v, void* out, double scale, int64_t window,
                             void* stream);
 
+/* ---- the callers that drive allocate / popn / reuse (host only, no device work) -------------
+ *
+ * Named rolling sessions over one arena: SessionSet with LRU eviction
+ * (combs-runtime/src/engine.rs:266-314, MAX_SESSIONS = 4 at :243).  The reference gives every
+ * session a private cache; here a session is a sequence of the shared arena. */
+typedef struct cbkv_sessions cbkv_sessions;
+int32_t cbkv_sessions_create(cbkv_arena* arena, int32_t max_sessions /* 0 = 4 */, cbkv_sessions** out);
+int32_t cbkv_sessions_destroy(cbkv_sessions* set);
+/* Start of a generation (engine.rs:1235-1287): takes the session `key` out of the table and rolls its
+ * cache back to the longest common prefix of its history with `prompt`, capped at n_prompt - 1; when
+ * nothing is shared, or the cache refuses the rollback, the old sequence is dropped and a fresh one
+ * returned.  *lcp_out = tokens already cached (prefill starts there).  reuse = 0: always fresh. */
+int32_t cbkv_sessions_acquire(cbkv_sessions* set, const char* key, const uint32_t* prompt, int64_t n_prompt,
+                              int32_t reuse, cbkv_seq** seq_out, int64_t* lcp_out);
+/* End of a generation (engine.rs:1541-1568, SessionSet::put :296-313): stores the sequence with its
+ * history (which must equal what the cache holds), evicting the least recently used session beyond
+ * max_sessions.  reuse = 0: the sequence is destroyed instead. */
+int32_t cbkv_sessions_release(cbkv_sessions* set, const char* key, cbkv_seq* seq, const uint32_t* history,
+                              int64_t n_history, int32_t reuse);
+int32_t cbkv_sessions_clear(cbkv_sessions* set, int64_t* removed);          /* clear_all, engine.rs:287-291 */
+int64_t cbkv_sessions_count(const cbkv_sessions* set);
+int64_t cbkv_sessions_evictions(const cbkv_sessions* set);
+int64_t cbkv_sessions_history_len(const cbkv_sessions* set, const char* key); /* -1: no such session */
+/* Speculative verification (engine.rs:1476-1493): `argmax` holds the model's k+1 row-wise choices after
+ * feeding [next, draft...]; accepts the longest matching prefix of the draft, pops the rejected tail
+ * from the cache (an incomplete pop is CBKV_ERR_STATE, as in the reference) and returns the correction
+ * token argmax[min(accepted, k)]. */
+int32_t cbkv_spec_verify_rollback(cbkv_seq* seq, const uint32_t* draft, const uint32_t* argmax, int32_t k,
+                                  int32_t* accepted_out, uint32_t* correction_out);
+/* The "kv" object of GET /v1/stats (combs-cli/src/serve.rs:146-166,197-208) as JSON text, sessions
+ * ordered by id.  Returns the length needed (excluding the terminator); writes at most cap bytes. */
+int64_t cbkv_sessions_stats_json(const cbkv_sessions* set, char* buf, int64_t cap);
+
 /* No counterpart in the reference.  Decode attention over pages the CALLER owns, for
  * callers that must not allocate device memory while they run (a server that gave
  * the whole GPU to its own pool at start-up, a plugin inside a host that forbids
