@@ -106,7 +106,7 @@ class OracleArena:
     """Arena + allocator shared by the sequences created from it."""
 
     def __init__(self, layers: int, n_kv: int, head_dim: int, max_seq_len: int, page_size: int = 16,
-                 num_pages: int = 0, windows=None, rolling: bool = True, dtype: str = "f16"):
+                 num_pages: int = 0, windows=None, rolling: bool = True, dtype: str = "f16", quantize_kv: bool = False):
         self.kind = dtype
         self.np_dtype = np.float16 if dtype == "f16" else np.float32
         self.lib = _lib(dtype)
@@ -121,6 +121,9 @@ class OracleArena:
             raise OracleError(-4, self.lib.orc_last_error().decode())
         self.num_pages = num_pages if num_pages > 0 else -(-max_seq_len // page_size)
         self._seqs = []
+        if quantize_kv:
+            self.lib.orc_arena_set_quantize.argtypes = [P, C.c_int]
+            self.lib.orc_arena_set_quantize(self.h, 1)
 
     def __del__(self):
         try:
@@ -148,6 +151,16 @@ class OracleArena:
         out = np.zeros(self.num_pages, dtype=np.int64)
         n = self.lib.orc_export_free_list(self.h, _ptr(out), len(out))
         return out[:n]
+
+    def page_quant(self, layer: int, page: int):
+        """Arena::Quant contents of one page (kv.rs:464-475): packed int32 [n_kv, P, d/4] and scales
+        [n_kv, P, d/32] for K and for V."""
+        kp = np.zeros((self.n_kv, self.page_size, self.d // 4), dtype=np.int32)
+        ks = np.zeros((self.n_kv, self.page_size, self.d // 32), dtype=self.np_dtype)
+        vp, vs = np.zeros_like(kp), np.zeros_like(ks)
+        self.lib.orc_export_page_quant.argtypes = [P, C.c_int, I64, P, P, P, P]
+        self.lib.orc_export_page_quant(self.h, layer, page, _ptr(kp), _ptr(ks), _ptr(vp), _ptr(vs))
+        return kp, ks, vp, vs
 
     def page(self, layer: int, page: int):
         k = np.zeros((self.n_kv, self.page_size, self.d), dtype=self.np_dtype)
@@ -366,4 +379,30 @@ def rms_norm(x: np.ndarray, w: np.ndarray, eps: float, gemma: bool = False) -> n
     d = out.shape[-1]
     w = np.ascontiguousarray(w, dtype=x.dtype)
     lib.orc_rms_norm(_ptr(out), out.size // d, d, _ptr(w), float(eps), 1 if gemma else 0)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# int8 KV pages (kv.rs:271-358)
+def kv_quantize(x: np.ndarray):
+    """``kv_quantize`` on x [..., d] (d % 32 == 0) -> (packed int32 [..., d/4], scales [..., d/32])."""
+    kind = "f16" if x.dtype == np.float16 else "f32"
+    lib = _lib(kind)
+    lib.orc_kv_quantize.argtypes = [P, I64, C.c_int, P, P]
+    x = np.ascontiguousarray(x)
+    d = x.shape[-1]
+    packed = np.zeros(x.shape[:-1] + (d // 4,), dtype=np.int32)
+    scales = np.zeros(x.shape[:-1] + (d // 32,), dtype=x.dtype)
+    lib.orc_kv_quantize(_ptr(x), x.size // d, d, _ptr(packed), _ptr(scales))
+    return packed, scales
+
+
+def kv_dequantize(packed: np.ndarray, scales: np.ndarray, d: int) -> np.ndarray:
+    """``kv_dequantize`` -> [..., d] in the dtype of ``scales``."""
+    kind = "f16" if scales.dtype == np.float16 else "f32"
+    lib = _lib(kind)
+    lib.orc_kv_dequantize.argtypes = [P, P, I64, C.c_int, P]
+    packed, scales = np.ascontiguousarray(packed), np.ascontiguousarray(scales)
+    out = np.zeros(packed.shape[:-1] + (d,), dtype=scales.dtype)
+    lib.orc_kv_dequantize(_ptr(packed), _ptr(scales), out.size // d, d, _ptr(out))
     return out

@@ -116,6 +116,12 @@ typedef struct {
     elem_t** v;
     int32_t* refcnt;     /* EXTENSION: holders per page (prefix sharing) */
     int live_seqs;
+    /* CacheConfig::quantize_kv (kv.rs:464-475,694-705): int8 pages for the layers without a
+       window of their own, when head_dim is a multiple of 32.  kp/vp hold the packed words
+       [num_pages, n_kv, page_size, d/4], ksc/vsc the group scales [.., d/32]; k/v then hold the
+       de-quantised values, which is what attention reads (kv.rs:771-780). */
+    int quantize;
+    int32_t** kp; int32_t** vp; elem_t** ksc; elem_t** vsc;
 } orc_arena;
 
 struct orc_seq {
@@ -147,13 +153,19 @@ orc_arena* orc_arena_new(int layers, int n_kv, int d, int64_t max_seq_len, int p
     a->k = (elem_t**)calloc((size_t)layers, sizeof(elem_t*));
     a->v = (elem_t**)calloc((size_t)layers, sizeof(elem_t*));
     a->refcnt = (int32_t*)calloc((size_t)a->num_pages, sizeof(int32_t));
+    a->kp = (int32_t**)calloc((size_t)layers, sizeof(int32_t*));
+    a->vp = (int32_t**)calloc((size_t)layers, sizeof(int32_t*));
+    a->ksc = (elem_t**)calloc((size_t)layers, sizeof(elem_t*));
+    a->vsc = (elem_t**)calloc((size_t)layers, sizeof(elem_t*));
     return a;
 }
 
+void orc_arena_set_quantize(orc_arena* a, int on) { a->quantize = on; }
+
 void orc_arena_free(orc_arena* a) {
     if (!a) return;
-    for (int i = 0; i < a->layers; i++) { free(a->k[i]); free(a->v[i]); }
-    free(a->k); free(a->v); free(a->windows); free(a->refcnt);
+    for (int i = 0; i < a->layers; i++) { free(a->k[i]); free(a->v[i]); free(a->kp[i]); free(a->vp[i]); free(a->ksc[i]); free(a->vsc[i]); }
+    free(a->k); free(a->v); free(a->kp); free(a->vp); free(a->ksc); free(a->vsc); free(a->windows); free(a->refcnt);
     free(a->alloc.free); free(a->alloc.initial); free(a);
 }
 
@@ -320,6 +332,83 @@ static void attend(const elem_t* q, const elem_t* k, const elem_t* v, elem_t* ou
     free(kr); free(vr);
 }
 
+/* ------------------------------------------------------------ int8 KV pages
+ * kv_quantize, kv.rs:284-313, for `rows` rows of d values (d % 32 == 0): per 32-value group
+ * scale = max(absmax / 127, 1e-8) in f32, q = clamp(round(x / scale), -127, 127), four values
+ * per word p = (q0+128) + (q1+128)*2^8 + (q2+128)*2^16 + q3*2^24; the scale is returned in the
+ * element type (kv.rs:312). */
+#define ORC_QGROUP 32
+void orc_kv_quantize(const elem_t* x, int64_t rows, int d, int32_t* packed, elem_t* scales) {
+    const int groups = d / ORC_QGROUP;
+    for (int64_t r = 0; r < rows; r++)
+        for (int g = 0; g < groups; g++) {
+            const elem_t* src = x + r * d + g * ORC_QGROUP;
+            float absmax = 0.f;
+            for (int j = 0; j < ORC_QGROUP; j++) { float v = fabsf(ld(src[j])); absmax = v > absmax ? v : absmax; }
+            float scale = absmax / 127.0f;
+            if (scale < 1e-8f) scale = 1e-8f;
+            int32_t q[ORC_QGROUP];
+            for (int j = 0; j < ORC_QGROUP; j++) {
+                float v = roundf(ld(src[j]) / scale);
+                v = v < -127.f ? -127.f : (v > 127.f ? 127.f : v);
+                q[j] = (int32_t)v;
+            }
+            for (int w = 0; w < ORC_QGROUP / 4; w++)
+                packed[r * (d / 4) + g * (ORC_QGROUP / 4) + w] =
+                    (q[4 * w] + 128) + (q[4 * w + 1] + 128) * 256 + (q[4 * w + 2] + 128) * 65536 + q[4 * w + 3] * 16777216;
+            scales[r * groups + g] = st(scale);
+        }
+}
+
+/* kv_dequantize, kv.rs:319-358: floor-division unpacking of the four lanes, then q * scale in
+ * the element type. */
+void orc_kv_dequantize(const int32_t* packed, const elem_t* scales, int64_t rows, int d, elem_t* out) {
+    const int groups = d / ORC_QGROUP;
+    for (int64_t r = 0; r < rows; r++)
+        for (int w = 0; w < d / 4; w++) {
+            int32_t p = packed[r * (d / 4) + w];
+            int32_t t = p / 16777216;                 /* truncating division, kv.rs:326 */
+            int32_t r3 = p - t * 16777216;
+            int32_t q3 = r3 < 0 ? t - 1 : t;          /* kv.rs:328-329 */
+            int32_t rem = r3 < 0 ? r3 + 16777216 : r3;
+            int32_t l2 = rem / 65536; rem -= l2 * 65536;
+            int32_t l1 = rem / 256;
+            int32_t l0 = rem - l1 * 256;
+            int32_t q[4] = {l0 - 128, l1 - 128, l2 - 128, q3};
+            float sc = ld(scales[r * groups + (4 * w) / ORC_QGROUP]);
+            for (int i = 0; i < 4; i++) out[r * d + 4 * w + i] = st(ld(st((float)q[i])) * sc);
+        }
+}
+
+static int layer_is_quantized(const orc_arena* a, int layer) {
+    return a->quantize && a->d % ORC_QGROUP == 0 && a->windows[layer] == 0; /* kv.rs:690-694 */
+}
+
+/* One run of new rows of one head into a page: plain copy, or quantise + keep the packed form
+ * and store what de-quantisation gives back (kv.rs:740-780). */
+static void store_rows(orc_arena* a, int layer, int is_v, size_t dst_row, const elem_t* src, int64_t run) {
+    const int d = a->d;
+    elem_t* dst = (is_v ? a->v[layer] : a->k[layer]) + dst_row * d;
+    if (!layer_is_quantized(a, layer)) { memcpy(dst, src, sizeof(elem_t) * (size_t)run * d); return; }
+    size_t n = (size_t)a->num_pages * a->n_kv * a->page_size;
+    int32_t** pk = is_v ? a->vp : a->kp;
+    elem_t** sc = is_v ? a->vsc : a->ksc;
+    if (!pk[layer]) {
+        pk[layer] = (int32_t*)calloc(n * (size_t)(d / 4), sizeof(int32_t));
+        sc[layer] = (elem_t*)calloc(n * (size_t)(d / ORC_QGROUP), sizeof(elem_t));
+    }
+    orc_kv_quantize(src, run, d, pk[layer] + dst_row * (d / 4), sc[layer] + dst_row * (d / ORC_QGROUP));
+    orc_kv_dequantize(pk[layer] + dst_row * (d / 4), sc[layer] + dst_row * (d / ORC_QGROUP), run, d, dst);
+}
+
+void orc_export_page_quant(const orc_arena* a, int layer, int64_t page, int32_t* kp, elem_t* ks, int32_t* vp, elem_t* vs) {
+    size_t rows = (size_t)a->n_kv * a->page_size, d4 = (size_t)a->d / 4, dg = (size_t)a->d / ORC_QGROUP;
+    if (a->kp[layer]) { memcpy(kp, a->kp[layer] + page * rows * d4, 4 * rows * d4); memcpy(ks, a->ksc[layer] + page * rows * dg, sizeof(elem_t) * rows * dg); }
+    else { memset(kp, 0, 4 * rows * d4); memset(ks, 0, sizeof(elem_t) * rows * dg); }
+    if (a->vp[layer]) { memcpy(vp, a->vp[layer] + page * rows * d4, 4 * rows * d4); memcpy(vs, a->vsc[layer] + page * rows * dg, sizeof(elem_t) * rows * dg); }
+    else { memset(vp, 0, 4 * rows * d4); memset(vs, 0, sizeof(elem_t) * rows * dg); }
+}
+
 /* gather_window, kv.rs:624-636: select pages, swap to head-major, trim to total */
 static elem_t* gather_window(const orc_seq* s, const elem_t* arena, int64_t pages, int64_t total) {
     const orc_arena* a = s->a;
@@ -419,8 +508,8 @@ int orc_layer(orc_seq* s, int layer, const elem_t* q, const elem_t* k, const ele
         int64_t run = (P - slot) < (seq - written) ? (P - slot) : (seq - written);
         int64_t phys = s->table[global / P];
         for (int h = 0; h < H; h++) {
-            memcpy(a->k[layer] + (((size_t)phys * H + h) * P + slot) * d, k + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
-            memcpy(a->v[layer] + (((size_t)phys * H + h) * P + slot) * d, v + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
+            store_rows(a, layer, 0, ((size_t)phys * H + h) * P + slot, k + ((size_t)h * seq + written) * d, run);
+            store_rows(a, layer, 1, ((size_t)phys * H + h) * P + slot, v + ((size_t)h * seq + written) * d, run);
         }
         written += run;
     }
@@ -448,8 +537,8 @@ int orc_append_only(orc_seq* s, int layer, const elem_t* k, const elem_t* v, int
         int64_t run = (P - slot) < (seq - written) ? (P - slot) : (seq - written);
         int64_t phys = s->table[global / P];
         for (int h = 0; h < H; h++) {
-            memcpy(a->k[layer] + (((size_t)phys * H + h) * P + slot) * d, k + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
-            memcpy(a->v[layer] + (((size_t)phys * H + h) * P + slot) * d, v + ((size_t)h * seq + written) * d, sizeof(elem_t) * (size_t)run * d);
+            store_rows(a, layer, 0, ((size_t)phys * H + h) * P + slot, k + ((size_t)h * seq + written) * d, run);
+            store_rows(a, layer, 1, ((size_t)phys * H + h) * P + slot, v + ((size_t)h * seq + written) * d, run);
         }
         written += run;
     }

@@ -7,6 +7,7 @@ oracle is pinned wherever the reference pins itself.
 import numpy as np
 import pytest
 
+import oracle
 from oracle import OracleArena, OracleContiguous, OracleError
 
 
@@ -317,3 +318,61 @@ def test_oracle_f16_build_matches_float64_within_storage_rounding():
     kk = np.concatenate([k, k1], axis=2)
     vv = np.concatenate([v, v1], axis=2)
     assert np.abs(o1.astype(np.float64) - attend_f64(q1, kk, vv, 300, 0.07, 64)).max() < 2e-3
+
+
+# ---- kv.rs:893-990: int8 KV pages ------------------------------------------
+def test_kv_quant_roundtrip_exact_on_grid_values():  # kv.rs:897-922
+    d = 64
+    data = np.array([(((i * 37) % 255) - 127) * 0.5 for i in range(2 * 3 * d)], dtype=np.float32)
+    data[::32] = 63.5                      # absmax 63.5 per group => scale 0.5
+    x = data.reshape(1, 2, 3, d)
+    packed, scales = oracle.kv_quantize(x)
+    assert packed.shape == (1, 2, 3, d // 4) and scales.shape == (1, 2, 3, d // 32)
+    assert np.all(scales == 0.5)
+    back = oracle.kv_dequantize(packed, scales, d)
+    assert np.all(np.abs(back - x) < 1e-6)
+    # the packing itself (kv.rs:276-283): lanes 0-2 offset binary, lane 3 signed
+    q = np.round(x / 0.5).astype(np.int64).reshape(-1, 4)
+    want = (q[:, 0] + 128) + (q[:, 1] + 128) * 256 + (q[:, 2] + 128) * 65536 + q[:, 3] * 16777216
+    assert np.array_equal(packed.reshape(-1).astype(np.int64), want)
+    assert want.max() <= 2 ** 31 - 1
+
+
+def test_kv_quant_extreme_corner_is_i32_max():       # kv.rs:279-281
+    x = np.full((1, 32), 127.0, dtype=np.float32)
+    packed, scales = oracle.kv_quantize(x)
+    assert scales[0, 0] == 1.0 and np.all(packed == 2 ** 31 - 1)
+    x[0, 3::4] = -127.0
+    packed, _ = oracle.kv_quantize(x)
+    assert np.all(packed == 255 + 255 * 256 + 255 * 65536 - 127 * 16777216)
+    assert np.array_equal(oracle.kv_dequantize(packed, np.ones((1, 1), np.float32), 32), x)
+
+
+def test_kv_quant_error_bounded_by_half_step():      # kv.rs:926-953
+    d = 64
+    data = np.array([((i * 7919) % 1000) / 250.0 - 2.0 for i in range(2 * 5 * d)], dtype=np.float32)
+    x = data.reshape(1, 2, 5, d)
+    back = oracle.kv_dequantize(*oracle.kv_quantize(x), d).reshape(-1, 32)
+    for g, chunk in enumerate(data.reshape(-1, 32)):
+        assert np.all(np.abs(chunk - back[g]) <= np.abs(chunk).max() / 254.0 + 1e-6)
+
+
+def test_quantized_paged_cache_matches_fp_within_tolerance():   # kv.rs:955-990
+    n_kv, n_q, d = 2, 4, 32
+    scale = 1.0 / np.sqrt(d) * 0.9
+    _, fp = paged(1, 64, 16, n_kv, d)
+    qa = OracleArena(1, n_kv, d, 64, 16, dtype="f32", quantize_kv=True)
+    qn = qa.new_seq()
+    k20, v20 = (np.concatenate([kv_tok(i, n_kv, d)[j] for i in range(20)], axis=2) for j in (0, 1))
+    q20 = cat_toks(q_tok, range(20), n_q, d)
+    a = fp.attention_opts(0, q20, k20, v20, 0, scale)
+    b = qn.attention_opts(0, q20, k20, v20, 0, scale)
+    assert np.all(np.abs(a - b) < 1e-2)
+    for i in range(20, 30):
+        k, v = kv_tok(i, n_kv, d)
+        q = q_tok(i, n_q, d)
+        a = fp.attention_opts(0, q, k, v, i, scale)
+        b = qn.attention_opts(0, q, k, v, i, scale)
+        assert np.all(np.abs(a - b) < 1e-2)
+    assert qn.seq_len() == 30 and qn.pages_used() == 2      # page semantics unchanged, kv.rs:984-989
+    assert qn.popn(14) == 14 and qn.pages_used() == 1
