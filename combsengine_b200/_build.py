@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcombskv.so")
-SOURCES = ["manager.cpp", "sessions.cpp", "kernels.cu", "prefill_tc.cu", "rope.cu", "api.cu", "noalloc.cu"]
+SOURCES = ["manager.cpp", "sessions.cpp", "kernels.cu", "prefill_tc.cu", "rope.cu", "kvquant.cu", "api.cu", "noalloc.cu"]
 HEADERS = ["manager.hpp", "kernels.hpp", os.path.join("..", "..", "include", "combs_kv.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

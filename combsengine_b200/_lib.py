@@ -19,6 +19,7 @@ class cbkv_config(C.Structure):
         ("num_layers", I32), ("n_q_heads", I32), ("n_kv_heads", I32), ("head_dim", I32),
         ("page_size", I32), ("dtype", I32), ("max_seq_len", I64), ("num_pages", I64),
         ("layer_windows", C.POINTER(I64)), ("sliding_popn_refuses", I32), ("device", I32),
+        ("quantize_kv", I32),
     ]
 
 
@@ -85,6 +86,8 @@ PROTOTYPES = {
     "cbkv_export_block_table": (I64, [P, C.POINTER(I64), I64]),
     "cbkv_export_free_list": (I64, [P, C.POINTER(I64), I64]),
     "cbkv_export_page": (I32, [P, I32, I64, P, P, P]),
+    "cbkv_export_page_quant": (I32, [P, I32, I64, P, P, P, P, P]),
+    "cbkv_layer_is_quantized": (I32, [P, I32]),
     "cbkv_page_refcount": (I32, [P, I64]),
     "cbkv_device_status": (I32, [P, P, C.POINTER(I32)]),
     "cbkv_launch_count": (I64, []),

@@ -187,6 +187,13 @@ int32_t materialize(Arena* a, int layer, cudaStream_t st) {
     DeviceState* d = dev_of(a);
     LayerArena& L = d->layers[(size_t)layer];
     if (L.base) return CBKV_OK;
+    if (a->layer_quant(layer)) {  // Arena::Quant, zero-filled (kv.rs:699-705)
+        const size_t bytes = (size_t)a->num_pages * a->cfg.n_kv_heads * qrec_bytes(a->cfg.page_size, a->cfg.head_dim);
+        CU_TRY(cudaMalloc(&L.base, bytes));
+        CU_TRY(cudaMemsetAsync(L.base, 0, bytes, st));
+        L.quant = true;
+        return CBKV_OK;
+    }
     CU_TRY(cudaMalloc(&L.base, d->layer_bytes));
     CU_TRY(cudaMemsetAsync(L.base, 0, d->layer_bytes, st));
     if (d->fast) {
@@ -391,7 +398,12 @@ int32_t check_step(Arena* a, int32_t layer) {
 int32_t run_append(Arena* a, int layer, const void* k, const void* v, cudaStream_t st) {
     DeviceState* d = dev_of(a);
     AppendArgs args{d->step, geom(a), k, v, d->layers[(size_t)layer].base, d->status};
-    CU_TRY(launch_append(args, a->cfg.dtype == CBKV_BF16, st));
+    if (d->layers[(size_t)layer].quant) {
+        args.geo.tiled = 0;
+        CU_TRY(launch_append_quant(args, a->cfg.dtype == CBKV_BF16, st));
+    } else {
+        CU_TRY(launch_append(args, a->cfg.dtype == CBKV_BF16, st));
+    }
     g_launches++;
     d->last_kv_writer = layer;
     return CBKV_OK;
@@ -406,6 +418,13 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     if (w != 0 && w < 2) { set_error("sliding window must be >= 2, got " + std::to_string(w)); return CBKV_ERR_ARG; }
     LayerArena& L = d->layers[(size_t)layer];
     const float scale_log2 = (float)(scale * 1.4426950408889634);
+    if (L.quant) {  // int8 pages: de-quantised on the fly
+        GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
+        ProfScope ps(d, st);
+        CU_TRY(launch_generic_quant(args, bf16, st));
+        g_launches++;
+        return CBKV_OK;
+    }
     if (d->fast && a->step_is_decode) {
         DecodePlanDev* pd = nullptr;
         int32_t rc = get_decode_plan(a, w, st, &pd);
@@ -586,7 +605,8 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
     DeviceState* d = dev_of(a);
     CU_TRY(cudaSetDevice(d->device));
     if ((rc = materialize(a, layer, st))) return rc;
-    if (d->fast && a->step_is_decode) return run_attention(a, layer, q, k, v, out, scale, window, st);
+    if (d->fast && a->step_is_decode && !d->layers[(size_t)layer].quant)
+        return run_attention(a, layer, q, k, v, out, scale, window, st);  // the append rides inside the decode kernel
     if ((rc = run_append(a, layer, k, v, st))) return rc;
     return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
 }
@@ -681,6 +701,7 @@ static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk
                                const void* v, void* q_out, cudaStream_t st) {
     DeviceState* d = dev_of(a);
     if (r->arena != a) { set_error("rope tables belong to another arena"); return CBKV_ERR_ARG; }
+    if (d->layers[(size_t)layer].quant) { set_error("the fused rotation does not write int8 pages: rotate, then cbkv_attention"); return CBKV_ERR_ARG; }
     for (const SeqMeta& m : a->step_meta)
         if ((int64_t)m.pos + m.snew > r->max_position) {
             set_error("rope table shorter than the step's positions: " + std::to_string((int64_t)m.pos + m.snew) + " > " +
@@ -864,7 +885,11 @@ int32_t cbkv_page_stats(const cbkv_seq* seq, cbkv_page_stats_t* out) {
 
 int64_t cbkv_page_bytes(const cbkv_arena* arena) {
     const Arena* a = reinterpret_cast<const Arena*>(arena);
-    return (int64_t)a->cfg.page_size * a->cfg.n_kv_heads * a->cfg.head_dim * 2 * 2 * a->cfg.num_layers;
+    int64_t total = 0;  // what one page id costs over all layers: float pages, or records with bytes + scales
+    for (int l = 0; l < a->cfg.num_layers; l++)
+        total += a->layer_quant(l) ? (int64_t)a->cfg.n_kv_heads * (int64_t)qrec_bytes(a->cfg.page_size, a->cfg.head_dim)
+                                   : (int64_t)a->cfg.page_size * a->cfg.n_kv_heads * a->cfg.head_dim * 2 * 2;
+    return total;
 }
 
 int64_t cbkv_export_block_table(const cbkv_seq* seq, int64_t* out, int64_t cap) {
@@ -891,6 +916,7 @@ int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k
         return CBKV_OK;
     }
     DeviceState* d = dev_of(a);
+    if (d->layers[(size_t)layer].quant) { set_error("layer holds int8 pages: use cbkv_export_page_quant"); return CBKV_ERR_STATE; }
     CU_TRY(cudaSetDevice(d->device));
     CU_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     std::vector<uint8_t> buf(tile * 2 * H);
@@ -905,6 +931,43 @@ int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k
             memcpy((uint8_t*)v_out_host + ((size_t)h * P + slot) * rowb,
                    buf.data() + ((size_t)h * 2 * P + page_row(1, slot, P, d->fast)) * rowb, rowb);
         }
+    return CBKV_OK;
+}
+
+int32_t cbkv_layer_is_quantized(const cbkv_arena* arena, int32_t layer) {
+    const Arena* a = reinterpret_cast<const Arena*>(arena);
+    if (!a || layer < 0 || layer >= a->cfg.num_layers) { set_error("layer out of range"); return CBKV_ERR_ARG; }
+    return a->layer_quant(layer) ? 1 : 0;
+}
+
+int32_t cbkv_export_page_quant(cbkv_arena* arena, int32_t layer, int64_t page, int32_t* kp, void* ks, int32_t* vp, void* vs,
+                               void* stream) {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || !kp || !ks || !vp || !vs) { set_error("null argument"); return CBKV_ERR_ARG; }
+    if (layer < 0 || layer >= a->cfg.num_layers || page < 0 || page >= a->num_pages) { set_error("layer or page out of range"); return CBKV_ERR_ARG; }
+    if (!a->layer_quant(layer)) { set_error("layer holds float pages: use cbkv_export_page"); return CBKV_ERR_STATE; }
+    const int H = a->cfg.n_kv_heads, P = a->cfg.page_size, D = a->cfg.head_dim, G = D / 32;
+    const size_t rows = (size_t)H * P;
+    if (!a->dev || !dev_of(a)->layers[(size_t)layer].base) {  // never written: zeros (kv.rs:699-705)
+        memset(kp, 0, rows * D); memset(vp, 0, rows * D);
+        memset(ks, 0, rows * G * 2); memset(vs, 0, rows * G * 2);
+        return CBKV_OK;
+    }
+    DeviceState* d = dev_of(a);
+    CU_TRY(cudaSetDevice(d->device));
+    CU_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    const size_t rec = qrec_bytes(P, D);
+    std::vector<uint8_t> buf(rec * H);
+    CU_TRY(cudaMemcpy(buf.data(), (uint8_t*)d->layers[(size_t)layer].base + (size_t)page * H * rec, buf.size(), cudaMemcpyDeviceToHost));
+    for (int h = 0; h < H; h++)
+        for (int slot = 0; slot < P; slot++)
+            for (int is_v = 0; is_v < 2; is_v++) {
+                uint8_t* pk = reinterpret_cast<uint8_t*>(is_v ? vp : kp) + ((size_t)h * P + slot) * D;
+                uint8_t* sc = reinterpret_cast<uint8_t*>(is_v ? vs : ks) + ((size_t)h * P + slot) * G * 2;
+                const uint8_t* r = buf.data() + (size_t)h * rec;
+                for (int j = 0; j < D; j++) pk[j] = r[qrec_value_off(is_v, slot, j, P, D)];
+                for (int g = 0; g < G; g++) memcpy(sc + 2 * g, r + qrec_scale_off(is_v, slot, g, P, D), 2);
+            }
     return CBKV_OK;
 }
 

@@ -31,8 +31,21 @@ enum : int32_t {
 CBKV_HD inline int page_row(int kv, int slot, int page_size, bool tiled) {
     return tiled ? ((slot >> 3) * 16 + kv * 8 + (slot & 7)) : (kv * page_size + slot);
 }
+// Quantised layers keep one record per (page, kv head):
+//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32 elems][V scales: P x d/32 elems]
+// a value byte is q+128 for d-indices 0-2 mod 4 and q (signed) for index 3 mod 4: the reference's packed
+// little-endian int32 words (kv.rs:276-283) laid out in d order.
+CBKV_HD inline size_t qrec_bytes(int page_size, int d) { return (size_t)2 * page_size * d + (size_t)2 * page_size * (d / 32) * 2; }
+CBKV_HD inline size_t qrec_value_off(int is_v, int slot, int j, int page_size, int d) {
+    return (size_t)is_v * page_size * d + (size_t)slot * d + j;
+}
+CBKV_HD inline size_t qrec_scale_off(int is_v, int slot, int group, int page_size, int d) {
+    return (size_t)2 * page_size * d + ((size_t)is_v * page_size * (d / 32) + (size_t)slot * (d / 32) + group) * 2;
+}
+
 struct LayerArena {
     void* base = nullptr;
+    bool quant = false;  // base holds quantised records, no tensor maps
     CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
     CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile)
     CUtensorMap map_lin; // measurement only: box 32 rows x d elems, no swizzle
@@ -143,6 +156,8 @@ cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st);
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_generic_quant(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, cudaStream_t st);
 // host side of the rotary tables (rope.cu): frequencies, then [max_position][head_dim] f32 tables
 int32_t rope_inv_freq(const cbkv_rope_config& c, std::vector<double>* inv, double* mscale);

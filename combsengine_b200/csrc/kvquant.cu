@@ -1,0 +1,194 @@
+// int8 KV pages: CacheConfig::quantize_kv of the reference (kv.rs:271-358, 464-475, 740-787).
+//
+//   append_quant_kernel    kv_quantize (kv.rs:284-313) fused with the page scatter
+//                          (kv.rs:746-768): per 32-value group scale = max(absmax/127, 1e-8)
+//                          in f32, q = clamp(round(x/scale), -127, 127), four values per 32-bit
+//                          word (lanes 0-2 offset binary, lane 3 signed), scale kept in the
+//                          element type
+//   generic_quant_kernel   attention over quantised pages for any shape: kv_dequantize
+//                          (kv.rs:319-358) happens on the fly, value = elem(q * scale), f32 math
+//
+// One record per (page, kv head), see qrec_* in kernels.hpp:
+//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32][V scales: P x d/32]
+// so a decode step reads d + d/16 bytes per cached token and head instead of 2d.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "kernels.hpp"
+
+namespace cbkv {
+
+namespace {
+
+template <bool BF16> __device__ __forceinline__ float q_up(uint16_t v) {
+    if (BF16) return __bfloat162float(__ushort_as_bfloat16(v));
+    return __half2float(__ushort_as_half(v));
+}
+template <bool BF16> __device__ __forceinline__ uint16_t q_down(float f) {
+    if (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    return __half_as_ushort(__float2half_rn(f));
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) append_quant_kernel(const AppendArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int d = a.geo.d, P = a.geo.page_size, Hkv = a.geo.n_kv;
+    const int words = d >> 2;                                  // 4 values per packed word
+    const int64_t kv_rows = (int64_t)a.step.n_tokens * Hkv;
+    uint8_t* arena = reinterpret_cast<uint8_t*>(a.arena);
+    const size_t rec = qrec_bytes(P, d);
+    for (int64_t R = warp0; R < 2 * kv_rows; R += nwarps) {
+        const int is_v = R >= kv_rows;
+        const int64_t row = is_v ? R - kv_rows : R;
+        int lo = 0, hi = a.step.n_seqs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if ((int64_t)a.step.seq_meta[mid].tok_off * Hkv <= row) lo = mid; else hi = mid - 1;
+        }
+        const SeqMeta sm = a.step.seq_meta[lo];
+        const int64_t local = row - (int64_t)sm.tok_off * Hkv;
+        const int h = (int)(local / sm.snew), r = (int)(local - (int64_t)h * sm.snew);
+        const int gpos = sm.pos + r;                            // kv.rs:749
+        int phys = a.step.tables[sm.tbl_off + gpos / P];        // kv.rs:752
+        if (phys < 0 || phys >= a.geo.num_pages) { if (lane == 0) atomicOr(a.status, ST_BAD_PAGE); continue; }
+        const int slot = gpos % P;                              // kv.rs:750
+        uint8_t* recp = arena + ((size_t)phys * Hkv + h) * rec;
+        const uint2* src = reinterpret_cast<const uint2*>(is_v ? a.v : a.k) + row * words;
+        // every lane runs every round (the shuffles below name the full warp)
+        for (int c0 = 0; c0 < words; c0 += 32) {
+            const int c = c0 + lane;
+            const bool live = c < words;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live) {
+                const uint2 raw = src[c];
+                x[0] = q_up<BF16>((uint16_t)(raw.x & 0xffff)); x[1] = q_up<BF16>((uint16_t)(raw.x >> 16));
+                x[2] = q_up<BF16>((uint16_t)(raw.y & 0xffff)); x[3] = q_up<BF16>((uint16_t)(raw.y >> 16));
+            }
+            float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+            // a group is 32 values = 8 consecutive lanes
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);   // kv.rs:296-301
+            if (live) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float q = roundf(__fdiv_rn(x[i], scale));             // kv.rs:302-305
+                    q = fminf(fmaxf(q, -127.f), 127.f);
+                    const int qi = (int)q;
+                    word |= (uint32_t)((i < 3 ? qi + 128 : qi) & 0xff) << (8 * i);   // kv.rs:308-311
+                }
+                *reinterpret_cast<uint32_t*>(recp + qrec_value_off(is_v, slot, 4 * c, P, d)) = word;
+                if ((c & 7) == 0)
+                    *reinterpret_cast<uint16_t*>(recp + qrec_scale_off(is_v, slot, c >> 3, P, d)) = q_down<BF16>(scale);
+            }
+        }
+    }
+}
+
+// One warp per query row, any page size and head_dim (multiple of 32, <= 512).
+template <bool BF16>
+__global__ void generic_quant_kernel(const GenericArgs a) {
+    __shared__ float qs[4][512];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t rid = (int64_t)blockIdx.x * 4 + w;
+    if (rid >= (int64_t)a.step.n_tokens * a.geo.n_q) return;
+    const int D = a.geo.d, P = a.geo.page_size, Hkv = a.geo.n_kv;
+    int lo = 0, hi = a.step.n_seqs - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if ((int64_t)a.step.seq_meta[mid].tok_off * a.geo.n_q <= rid) lo = mid; else hi = mid - 1;
+    }
+    const SeqMeta sm = a.step.seq_meta[lo];
+    const int64_t local = rid - (int64_t)sm.tok_off * a.geo.n_q;
+    const int hq = (int)(local / sm.snew), r = (int)(local % sm.snew);
+    const int h = hq / a.geo.n_rep;
+    const int q_pos = sm.pos + r;
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(a.q) + rid * D;
+    for (int j = lane; j < D; j += 32) qs[w][j] = q_up<BF16>(q[j]);
+    __syncwarp();
+    const uint8_t* arena = reinterpret_cast<const uint8_t*>(a.arena);
+    const size_t rec = qrec_bytes(P, D);
+    // kv_dequantize: lanes 0-2 are offset binary, lane 3 is signed (kv.rs:326-346); value = elem(q * scale)
+    auto value = [&](const uint8_t* recp, int is_v, int slot, int j) -> float {
+        const uint8_t b = recp[qrec_value_off(is_v, slot, j, P, D)];
+        const int qi = (j & 3) == 3 ? (int)(int8_t)b : (int)b - 128;
+        const float sc = q_up<BF16>(*reinterpret_cast<const uint16_t*>(recp + qrec_scale_off(is_v, slot, j >> 5, P, D)));
+        return q_up<BF16>(q_down<BF16>(__fmul_rn((float)qi, sc)));
+    };
+    const int t_lo = a.window > 0 ? max(0, q_pos - a.window + 1) : 0;
+    float m = -INFINITY, l = 0.f, acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc[i] = 0.f;
+    for (int t0 = t_lo; t0 <= q_pos; t0 += 32) {
+        const int tk = t0 + lane;
+        const bool ok = tk <= q_pos;
+        float s = -INFINITY;
+        if (ok) {
+            int phys = a.step.tables[sm.tbl_off + tk / P];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            const uint8_t* recp = arena + ((size_t)phys * Hkv + h) * rec;
+            float dot = 0.f;
+            for (int j = 0; j < D; j++) dot += qs[w][j] * value(recp, 0, tk % P, j);
+            s = dot * a.scale;
+        }
+        float mx = s;
+        for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float m_new = fmaxf(m, mx);
+        const float alpha = __expf(m - m_new);
+        const float p = ok ? __expf(s - m_new) : 0.f;
+        float ps = p;
+        for (int off = 16; off; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+        l = l * alpha + ps;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] *= alpha;
+        const int cnt = min(32, q_pos - t0 + 1);
+        for (int kk = 0; kk < cnt; kk++) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            const int tv = t0 + kk;
+            int phys = a.step.tables[sm.tbl_off + tv / P];
+            if (phys < 0 || phys >= a.geo.num_pages) phys = 0;
+            const uint8_t* recp = arena + ((size_t)phys * Hkv + h) * rec;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int j = lane + 32 * i;
+                if (j < D) acc[i] += pk * value(recp, 1, tv % P, j);
+            }
+        }
+    }
+    uint16_t* out = reinterpret_cast<uint16_t*>(a.out) + rid * D;
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int j = lane + 32 * i;
+        if (j < D) out[j] = q_down<BF16>(acc[i] * inv);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st) {
+    const int64_t rows = 2 * (int64_t)a.step.n_tokens * a.geo.n_kv;
+    if (rows <= 0) return cudaSuccess;
+    const int blocks = (int)std::min<int64_t>((rows + 7) / 8, 148 * 8);
+    if (bf16) append_quant_kernel<true><<<blocks, 256, 0, st>>>(a);
+    else append_quant_kernel<false><<<blocks, 256, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_generic_quant(const GenericArgs& a, bool bf16, cudaStream_t st) {
+    const int64_t rows = (int64_t)a.step.n_tokens * a.geo.n_q;
+    if (rows <= 0) return cudaSuccess;
+    const int blocks = (int)((rows + 3) / 4);
+    if (bf16) generic_quant_kernel<true><<<blocks, 128, 0, st>>>(a);
+    else generic_quant_kernel<false><<<blocks, 128, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace cbkv

@@ -94,6 +94,9 @@ struct Arena {
     void* dev = nullptr;  // device-side state (device.cu), created on first device use
 
     int n_rep() const { return cfg.n_q_heads / cfg.n_kv_heads; }
+    // int8 pages: asked for, head_dim a multiple of the 32-value group, and not a layer with a window of
+    // its own (those never reach the quantised branch in the reference, kv.rs:688-694)
+    bool layer_quant(int layer) const { return cfg.quantize_kv && cfg.head_dim % 32 == 0 && windows[(size_t)layer] == 0; }
     int64_t layer_window(int layer, int64_t arg) const {  // the cache's own window wins, kv.rs:688-693
         return windows[layer] > 0 ? windows[layer] : arg;
     }

@@ -197,7 +197,8 @@ int64_t cbkv_sessions_stats_json(const cbkv_sessions* set, char* buf, int64_t ca
     const int64_t page_bytes = cbkv_page_bytes(s->arena);
     std::string o = "{";
     auto num = [&](const char* k, long long v, bool comma = true) { o += '"'; o += k; o += "\":"; o += std::to_string(v); if (comma) o += ','; };
-    o += "\"kind\":\"paged\",\"quantized\":false,";
+    o += "\"kind\":\"paged\",\"quantized\":";
+    o += a->cfg.quantize_kv ? "true," : "false,";
     num("max_seq_len", a->cfg.max_seq_len);
     num("page_size", a->cfg.page_size);
     num("page_bytes", page_bytes);

@@ -123,7 +123,8 @@ class KVArena:
 
     def __init__(self, num_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, max_seq_len: int,
                  page_size: int = 16, num_pages: int = 0, windows: Optional[Sequence[Optional[int]]] = None,
-                 dtype: torch.dtype = torch.float16, device: int = 0, sliding_popn_refuses: bool = True):
+                 dtype: torch.dtype = torch.float16, device: int = 0, sliding_popn_refuses: bool = True,
+                 quantize_kv: bool = False):
         self._lib = _lib.load()
         if windows is not None and len(windows) != num_layers:
             raise CbkvError(-4, "one window entry per layer")  # kv.rs:513
@@ -138,6 +139,7 @@ class KVArena:
             cfg.layer_windows = C.cast(self._wbuf, C.POINTER(C.c_int64))
         cfg.sliding_popn_refuses = 1 if sliding_popn_refuses else 0
         cfg.device = device
+        cfg.quantize_kv = 1 if quantize_kv else 0   # CacheConfig::quantize_kv, kv.rs:464-475
         h = P()
         check(self._lib.cbkv_arena_create(C.byref(cfg), C.byref(h)))
         self._h = h.value
@@ -260,6 +262,22 @@ class KVArena:
     def refcount(self, page: int) -> int:
         return self._lib.cbkv_page_refcount(self._h, page)
 
+    def layer_is_quantized(self, layer: int) -> bool:
+        rc = self._lib.cbkv_layer_is_quantized(self._h, layer)
+        check(min(rc, 0))
+        return rc == 1
+
+    def export_page_quant(self, layer: int, page: int, stream=None):
+        """One int8 page as the reference's Arena::Quant holds it: packed int32 [n_kv, P, d/4] and scale bit
+        patterns uint16 [n_kv, P, d/32], for K and for V."""
+        kp = np.zeros((self.n_kv_heads, self.page_size, self.head_dim // 4), dtype=np.int32)
+        ks = np.zeros((self.n_kv_heads, self.page_size, self.head_dim // 32), dtype=np.uint16)
+        vp, vs = np.zeros_like(kp), np.zeros_like(ks)
+        sp = _stream_ptr(stream) if torch.cuda.is_available() else 0
+        check(self._lib.cbkv_export_page_quant(self._h, layer, page, kp.ctypes.data_as(P), ks.ctypes.data_as(P),
+                                               vp.ctypes.data_as(P), vs.ctypes.data_as(P), sp))
+        return kp, ks, vp, vs
+
     def export_page(self, layer: int, page: int, stream=None):
         """One page as the reference lays it out: K and V as [n_kv, page_size, d] uint16 bit patterns."""
         shape = (self.n_kv_heads, self.page_size, self.head_dim)
@@ -361,11 +379,9 @@ class PagedKVCache:
                  device: int = 0):
         if config.kind is not CacheKind.Paged:
             raise NotImplementedError("only CacheKind.Paged exists on this path (the cat-per-step baseline is the oracle's)")
-        if config.quantize_kv:
-            raise NotImplementedError("int8 KV pages are not built yet")
         self.config = config
         self.arena = KVArena(num_layers, n_q_heads, n_kv_heads, head_dim, config.max_seq_len, config.page_size,
-                             0, windows, dtype, device)
+                             0, windows, dtype, device, quantize_kv=config.quantize_kv)
         self.seq = self.arena.new_seq()
 
     @classmethod

@@ -65,6 +65,9 @@ typedef struct {
     int32_t sliding_popn_refuses; /* 1 = popn refuses once a sliding layer would have
                                      evicted (kv.rs:812-816); 0 = windows are pure masks */
     int32_t device;               /* CUDA device ordinal */
+    int32_t quantize_kv;          /* CacheConfig::quantize_kv (kv.rs:464-475,694): int8 pages with one scale
+                                     per 32 values for every layer without a window of its own, when
+                                     head_dim is a multiple of 32; other layers keep float pages */
 } cbkv_config;
 
 /* PageStats (kv.rs:153-175), same eight counters in the same order. */
@@ -282,6 +285,13 @@ int64_t cbkv_export_free_list(const cbkv_arena* arena, int64_t* out, int64_t cap
  * materialised.  Synchronises `stream`. */
 int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k_out_host,
                          void* v_out_host, void* stream);
+/* One page of a quantised layer as the reference's Arena::Quant holds it (kv.rs:464-475): packed
+ * int32 words [n_kv][page_size][head_dim/4] (kv.rs:276-283) and scales [n_kv][page_size][head_dim/32]
+ * in the arena's element type, for K and for V.  Host buffers; synchronises. */
+int32_t cbkv_export_page_quant(cbkv_arena* arena, int32_t layer, int64_t page, int32_t* k_packed_host, void* k_scales_host,
+                               int32_t* v_packed_host, void* v_scales_host, void* stream);
+/* 1 if the layer stores int8 pages, 0 if float pages, negative on a bad argument. */
+int32_t cbkv_layer_is_quantized(const cbkv_arena* arena, int32_t layer);
 int32_t cbkv_page_refcount(const cbkv_arena* arena, int64_t page);
 
 /* ---- diagnostics ----------------------------------------------------------- */

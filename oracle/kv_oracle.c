@@ -384,19 +384,24 @@ static int layer_is_quantized(const orc_arena* a, int layer) {
     return a->quantize && a->d % ORC_QGROUP == 0 && a->windows[layer] == 0; /* kv.rs:690-694 */
 }
 
+/* Packed words and scales of a quantised layer appear with the layer's arenas (kv.rs:699-705). */
+static void ensure_quant_arrays(orc_arena* a, int layer) {
+    if (!layer_is_quantized(a, layer) || a->kp[layer]) return;
+    size_t n = (size_t)a->num_pages * a->n_kv * a->page_size;
+    a->kp[layer] = (int32_t*)calloc(n * (size_t)(a->d / 4), sizeof(int32_t));
+    a->vp[layer] = (int32_t*)calloc(n * (size_t)(a->d / 4), sizeof(int32_t));
+    a->ksc[layer] = (elem_t*)calloc(n * (size_t)(a->d / ORC_QGROUP), sizeof(elem_t));
+    a->vsc[layer] = (elem_t*)calloc(n * (size_t)(a->d / ORC_QGROUP), sizeof(elem_t));
+}
+
 /* One run of new rows of one head into a page: plain copy, or quantise + keep the packed form
  * and store what de-quantisation gives back (kv.rs:740-780). */
 static void store_rows(orc_arena* a, int layer, int is_v, size_t dst_row, const elem_t* src, int64_t run) {
     const int d = a->d;
     elem_t* dst = (is_v ? a->v[layer] : a->k[layer]) + dst_row * d;
     if (!layer_is_quantized(a, layer)) { memcpy(dst, src, sizeof(elem_t) * (size_t)run * d); return; }
-    size_t n = (size_t)a->num_pages * a->n_kv * a->page_size;
     int32_t** pk = is_v ? a->vp : a->kp;
     elem_t** sc = is_v ? a->vsc : a->ksc;
-    if (!pk[layer]) {
-        pk[layer] = (int32_t*)calloc(n * (size_t)(d / 4), sizeof(int32_t));
-        sc[layer] = (elem_t*)calloc(n * (size_t)(d / ORC_QGROUP), sizeof(elem_t));
-    }
     orc_kv_quantize(src, run, d, pk[layer] + dst_row * (d / 4), sc[layer] + dst_row * (d / ORC_QGROUP));
     orc_kv_dequantize(pk[layer] + dst_row * (d / 4), sc[layer] + dst_row * (d / ORC_QGROUP), run, d, dst);
 }
@@ -499,6 +504,7 @@ int orc_layer(orc_seq* s, int layer, const elem_t* q, const elem_t* k, const ele
         a->k[layer] = (elem_t*)calloc(n, sizeof(elem_t));
         a->v[layer] = (elem_t*)calloc(n, sizeof(elem_t));
     }
+    ensure_quant_arrays(a, layer);
     int64_t pages = (total + P - 1) / P;
     /* append loop, kv.rs:723-734 */
     int64_t written = 0;
@@ -531,6 +537,7 @@ int orc_append_only(orc_seq* s, int layer, const elem_t* k, const elem_t* v, int
         a->k[layer] = (elem_t*)calloc(n, sizeof(elem_t));
         a->v[layer] = (elem_t*)calloc(n, sizeof(elem_t));
     }
+    ensure_quant_arrays(a, layer);
     int64_t written = 0;
     while (written < seq) {
         int64_t global = pos + written, slot = global % P;
@@ -698,6 +705,7 @@ int orc_batch_layer(orc_seq** seqs, const int64_t* new_tokens, int n, int layer,
         a->k[layer] = (elem_t*)calloc(cnt, sizeof(elem_t));
         a->v[layer] = (elem_t*)calloc(cnt, sizeof(elem_t));
     }
+    ensure_quant_arrays(a, layer);
     int rc_all = ORC_OK;
 #pragma omp parallel for schedule(dynamic)
     for (int b = 0; b < n; b++) {

@@ -27,12 +27,13 @@ class Pair:
     """A CUDA arena and an oracle arena kept in lock-step."""
 
     def __init__(self, layers, n_q, n_kv, d, max_seq_len, num_pages=0, page_size=16, windows=None, seed=0,
-                 shuffle_free_list=False, popn_refuses=True, tuning=None, chunk_kernel=None):
+                 shuffle_free_list=False, popn_refuses=True, tuning=None, chunk_kernel=None, quantize_kv=False):
         self.layers, self.n_q, self.n_kv, self.d = layers, n_q, n_kv, d
         self.g = KVArena(layers, n_q, n_kv, d, max_seq_len, page_size, num_pages, windows,
-                         sliding_popn_refuses=popn_refuses)
+                         sliding_popn_refuses=popn_refuses, quantize_kv=quantize_kv)
         # sliding layers live in pages on both sides so that page contents can be compared
-        self.o = OracleArena(layers, n_kv, d, max_seq_len, page_size, num_pages, windows=windows, rolling=False, dtype="f16")
+        self.o = OracleArena(layers, n_kv, d, max_seq_len, page_size, num_pages, windows=windows, rolling=False, dtype="f16",
+                             quantize_kv=quantize_kv)
         self.windows = windows
         if tuning:
             self.g.set_decode_tuning(**tuning)
@@ -103,6 +104,12 @@ class Pair:
         check = range(self.g.num_pages) if pages == "all" else sorted(used)
         for layer in range(self.layers):
             for pg in check:
+                if self.g.layer_is_quantized(layer):  # packed words and scales, bit for bit
+                    got, want = self.g.export_page_quant(layer, pg), self.o.page_quant(layer, pg)
+                    for name, x, y in zip(("K words", "K scales", "V words", "V scales"), got, want):
+                        y = y if y.dtype == np.int32 else y.view(np.uint16)
+                        assert np.array_equal(x, y), f"{name} of page {pg} layer {layer}"
+                    continue
                 gk, gv = self.g.export_page(layer, pg)
                 ok, ov = self.o.page(layer, pg)
                 assert np.array_equal(gk, ok.view(np.uint16)), f"K page {pg} layer {layer}"
