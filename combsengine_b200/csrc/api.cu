@@ -418,7 +418,9 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     if (w != 0 && w < 2) { set_error("sliding window must be >= 2, got " + std::to_string(w)); return CBKV_ERR_ARG; }
     LayerArena& L = d->layers[(size_t)layer];
     const float scale_log2 = (float)(scale * 1.4426950408889634);
-    if (L.quant) {  // int8 pages: de-quantised on the fly
+    // int8 pages: decode steps stream the records through the decode kernel; everything else (chunks,
+    // shapes outside the fast path) de-quantises on the fly in the generic kernel
+    if (L.quant && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
         GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
         ProfScope ps(d, st);
         CU_TRY(launch_generic_quant(args, bf16, st));
@@ -437,7 +439,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.q = q; args.out = out; args.k_new = k_fused; args.v_new = v_fused; args.arena = L.base;
         args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
         args.window = (int32_t)w; args.scale_log2 = scale_log2;
-        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
+        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers, L.quant);
         args.n_stages = dc.stages; args.comb_cols = dc.comb_cols; args.comb_bufs = dc.comb_bufs;
         args.kv_dep = d->last_kv_writer == layer ? 1 : 0;
         args.debug = debug_flags();
@@ -448,7 +450,8 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
             d->dbg_ctas = pd->host.n_ctas;
         }
         ProfScope ps(d, st);
-        CU_TRY(launch_decode((args.debug & 2) ? L.map_lin : L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st));
+        if (L.quant) args.debug &= ~2;
+        CU_TRY(launch_decode((args.debug & 2) ? L.map_lin : L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st, L.quant));
         g_launches++;
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;

@@ -212,6 +212,159 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
     }
 }
 
+// ------------------------------------------------------------------ int8 pages (kv.rs:271-358)
+// A quantised record (kernels.hpp, qrec_*) reaches shared memory by one bulk copy.  Values are
+// converted in registers by a byte permute that puts a constant exponent byte over each value byte
+// and one exact subtraction (q8_pair).  The group scales never touch the values: K's multiply the f32 score partial sums of their 32-wide group, V's multiply the
+// probabilities of their token before the P.V product of that group's rows.
+//
+// The contraction index of an MMA may be permuted freely if both operands agree, and so may the
+// output rows of O^T if the store undoes it; that is how a thread gets whole 4- and 8-byte words:
+//   K (A operand, row = token): per group a thread takes bytes 8t..8t+7 of rows g and g+8; k-step s
+//     contracts d = 32*grp + 8t + 4s + {0,1,2,3} against the Q fragment loaded in the same order.
+//   V (A operand of O^T, row = d): per group a thread takes bytes 4g..4g+3 of tokens 2t, 2t+1, 2t+8,
+//     2t+9; m-tile 2*grp has rows d = 32*grp + 4g + {0 (row g), 1 (row g+8)}, m-tile 2*grp+1 the
+//     other two.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.b16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+// Byte -> number.  f16: all four bytes of a word are made offset binary (b = q + 128); a byte under
+// the exponent byte 0x64 reads as 1024 + b, and subtracting 1152 leaves q.  bf16 has one mantissa bit
+// less than a byte is wide, so there the bytes are made two's complement instead: the low seven bits
+// under 0x43 read as 128 + (b & 127), the sign bit under 0x43 reads as 128 or 256, and their
+// difference is q.  Both subtractions are exact.
+template <bool BF16> __device__ __forceinline__ uint32_t q8_fix(uint32_t w) { return w ^ (BF16 ? 0x00808080u : 0x80000000u); }
+// two bytes of `src` (selected by `sel`, which also places the exponent bytes) -> two numbers q
+template <bool BF16>
+__device__ __forceinline__ uint32_t q8_pair(uint32_t src, uint32_t sel) {
+    uint32_t v = __byte_perm(src, BF16 ? 0x43434343u : 0x64646464u, sel);
+    if constexpr (BF16) {
+        uint32_t lo = v & 0xff7fff7fu, hi = v & 0xff80ff80u;
+        __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&lo), *reinterpret_cast<__nv_bfloat162*>(&hi));
+        return *reinterpret_cast<uint32_t*>(&r);
+    } else {
+        const uint32_t bias = 0x64806480u;  // 1152, 1152
+        __half2 r = __hsub2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&bias));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    } else {
+        __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+}
+constexpr uint32_t SEL_LO = 0x5140u;  // bytes 0 and 1 of the source, each under an exponent byte
+constexpr uint32_t SEL_HI = 0x7362u;  // bytes 2 and 3
+
+// One 16-token quantised tile against the 8 query columns of the kv group (decode).
+template <int D, bool BF16>
+__device__ __forceinline__ void attend_tile_q8(uint32_t stage, const uint32_t (&qf)[1][D / 16][2], float (&o)[1][D / 16][4],
+                                               float (&m)[1][2], float (&l)[1][2], int kpos0, const int (&qpos)[1][2],
+                                               int window, float scale_log2, bool need_mask, int lane) {
+    constexpr int G = D / 32;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t kbase = stage, vbase = stage + 16u * D, ksc = stage + 32u * D, vsc = ksc + 16u * G * 2u;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- S^T = sum over groups of scale_K[token][grp] * (Kq . Q^T)
+    {
+        const int swz = qrec_swz(0, g, D);  // rows g and g+8 share it
+        const uint32_t r0 = kbase + (uint32_t)g * D + 8u * t, r1 = r0 + 8u * D;
+#pragma unroll
+        for (int grp = 0; grp < G; grp++) {
+            const uint32_t off = (uint32_t)((grp ^ swz) << 5);
+            uint2 x = lds64(r0 + off), y = lds64(r1 + off);
+            x.x = q8_fix<BF16>(x.x); x.y = q8_fix<BF16>(x.y); y.x = q8_fix<BF16>(y.x); y.y = q8_fix<BF16>(y.y);
+            float sg[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t a[4];
+            a[0] = q8_pair<BF16>(x.x, SEL_LO); a[1] = q8_pair<BF16>(y.x, SEL_LO);
+            a[2] = q8_pair<BF16>(x.x, SEL_HI); a[3] = q8_pair<BF16>(y.x, SEL_HI);
+            mma_16816<BF16>(sg, a, qf[0][2 * grp][0], qf[0][2 * grp][1]);
+            a[0] = q8_pair<BF16>(x.y, SEL_LO); a[1] = q8_pair<BF16>(y.y, SEL_LO);
+            a[2] = q8_pair<BF16>(x.y, SEL_HI); a[3] = q8_pair<BF16>(y.y, SEL_HI);
+            mma_16816<BF16>(sg, a, qf[0][2 * grp + 1][0], qf[0][2 * grp + 1][1]);
+            const float k0 = from_elem<BF16>((uint16_t)lds16(ksc + (uint32_t)(g * G + grp) * 2u));
+            const float k1 = from_elem<BF16>((uint16_t)lds16(ksc + (uint32_t)((g + 8) * G + grp) * 2u));
+            s[0] += sg[0] * k0; s[1] += sg[1] * k0; s[2] += sg[2] * k1; s[3] += sg[3] * k1;
+        }
+    }
+    // ---- online softmax over the tile's 16 tokens (rows g and g+8 of the fragment)
+#pragma unroll
+    for (int i = 0; i < 4; i++) s[i] *= scale_log2;
+    if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int kp = kpos0 + g + (i >> 1) * 8, qp = qpos[0][i & 1];
+            const bool ok = kp <= qp && (window <= 0 || kp + window > qp);
+            if (!ok) s[i] = -INFINITY;
+        }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        float mx = fmaxf(s[j], s[j + 2]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m[0][j], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[j] = exp2f(m[0][j] - m_use);
+        m[0][j] = m_new;
+        const float p0 = exp2f(s[j] - m_use), p1 = exp2f(s[j + 2] - m_use);
+        s[j] = p0; s[j + 2] = p1;
+        l[0][j] = l[0][j] * alpha[j] + p0 + p1;
+    }
+#pragma unroll
+    for (int mt = 0; mt < D / 16; mt++) {
+        o[0][mt][0] *= alpha[0]; o[0][mt][1] *= alpha[1];
+        o[0][mt][2] *= alpha[0]; o[0][mt][3] *= alpha[1];
+    }
+    const uint32_t pb0 = movmatrix_trans(pack2<BF16>(s[0], s[1]));  // tokens 2t, 2t+1 of column g
+    const uint32_t pb1 = movmatrix_trans(pack2<BF16>(s[2], s[3]));  // tokens 2t+8, 2t+9
+    // ---- O^T += sum over groups of Vq^T . (P^T * scale_V[token][grp])
+    {
+        const int swz = qrec_swz(1, 2 * t, D);  // tokens 2t, 2t+1, 2t+8, 2t+9 share it
+        const uint32_t c0 = vbase + (uint32_t)(2 * t) * D + 4u * g;
+#pragma unroll
+        for (int grp = 0; grp < G; grp++) {
+            const uint32_t off = (uint32_t)((grp ^ swz) << 5);
+            uint32_t w0 = lds32(c0 + off), w1 = lds32(c0 + D + off), w2 = lds32(c0 + 8u * D + off), w3 = lds32(c0 + 9u * D + off);
+            w0 = q8_fix<BF16>(w0); w1 = q8_fix<BF16>(w1); w2 = q8_fix<BF16>(w2); w3 = q8_fix<BF16>(w3);
+            const uint32_t b0 = mul2<BF16>(pb0, lds32(vsc + (uint32_t)(grp * 16 + 2 * t) * 2u));
+            const uint32_t b1 = mul2<BF16>(pb1, lds32(vsc + (uint32_t)(grp * 16 + 2 * t + 8) * 2u));
+            const uint32_t t01 = __byte_perm(w0, w1, SEL_LO), t23 = __byte_perm(w0, w1, SEL_HI);  // (w0.b, w1.b) pairs
+            const uint32_t u01 = __byte_perm(w2, w3, SEL_LO), u23 = __byte_perm(w2, w3, SEL_HI);
+            uint32_t a[4];
+            a[0] = q8_pair<BF16>(t01, SEL_LO); a[1] = q8_pair<BF16>(t01, SEL_HI);
+            a[2] = q8_pair<BF16>(u01, SEL_LO); a[3] = q8_pair<BF16>(u01, SEL_HI);
+            mma_16816<BF16>(o[0][2 * grp], a, b0, b1);
+            a[0] = q8_pair<BF16>(t23, SEL_LO); a[1] = q8_pair<BF16>(t23, SEL_HI);
+            a[2] = q8_pair<BF16>(u23, SEL_LO); a[3] = q8_pair<BF16>(u23, SEL_HI);
+            mma_16816<BF16>(o[0][2 * grp + 1], a, b0, b1);
+        }
+    }
+}
+
 // Issue the TMA copies for one (page, kv head) tile: D/64 boxes of 32 rows x 64 elems.
 template <int D>
 __device__ __forceinline__ void issue_tile(const CUtensorMap* map, uint32_t stage, uint32_t bar, int row0) {
@@ -299,6 +452,21 @@ __device__ __forceinline__ void load_q_frags(const DecodeArgs& a, const Piece& p
     }
 }
 
+// The same fragments in the contraction order of the quantised K tiles (see attend_tile_q8).
+template <int D>
+__device__ __forceinline__ void load_q_frags_q8(const DecodeArgs& a, const Piece& p, int g, int t, uint32_t (&qf)[1][D / 16][2]) {
+    const int n_rep = a.geo.n_rep;
+    const uint2* qrow = reinterpret_cast<const uint2*>(
+        reinterpret_cast<const uint16_t*>(a.q) + ((size_t)p.tok_off * a.geo.n_q + (size_t)p.h * n_rep + (g < n_rep ? g : 0)) * D);
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks++) {
+        // k-step ks = 2*grp + s contracts d = 32*grp + 8t + 4s + {0..3}: one 8-byte word
+        const uint2 v = g < n_rep ? __ldg(qrow + (ks >> 1) * 8 + 2 * t + (ks & 1)) : make_uint2(0u, 0u);
+        qf[0][ks][0] = v.x;
+        qf[0][ks][1] = v.y;
+    }
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -361,9 +529,10 @@ __device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int n
 }
 
 // Warp roles: 0 = producer, 1..C = consumers, C+1 = merger.
-template <int D, int C, bool BF16>
+// Q8: the layer holds int8 records; a tile is one record fetched by a bulk copy, no fused append.
+template <int D, int C, bool BF16, bool Q8>
 __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
-    constexpr uint32_t UNIT = 32u * D * 2u;
+    constexpr uint32_t UNIT = Q8 ? (uint32_t)(2 * 16 * D + 2 * 16 * (D / 32) * 2) : 32u * D * 2u;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int NS = a.n_stages;            // multiple of C (checked by the host)
     const int R = NS < 8 ? 4 : 8;         // producer lanes per round; R <= NS keeps a round free of self-dependencies
@@ -395,7 +564,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     const int Hkv = a.geo.n_kv;
     const int first_seg = a.cta_first_seg[cta];
     if (tid == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+        if (!Q8) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
         for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
         for (int i = 0; i < 2; i++) { mbar_init(cfull0 + i * 8, C); mbar_init(cempty0 + i * 8, 1); }
         flag[0] = 0; flag[1] = 0; flag[2] = 0;
@@ -432,7 +601,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             const int h = sg % Hkv;
             int phys = a.step.tables[toff + plo + (u - sub)];
             if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-            rows[n % ROWS_CAP] = (phys * Hkv + h) * 32;
+            rows[n % ROWS_CAP] = Q8 ? (phys * Hkv + h) : (phys * Hkv + h) * 32;  // record index, or first arena row
         }
     };
     resolve_rows(0, min(ntiles, ROWS_CAP), tid, (C + 2) * 32);
@@ -458,7 +627,10 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 const int st = n % NS;
                 const int row0 = rows[n % ROWS_CAP];
                 if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, ((n / NS) - 1) & 1)) failed = true;
-                if (!failed) {
+                if (!failed && Q8) {
+                    mbar_expect_tx(full0 + st * 8, UNIT);
+                    bulk_load(ring + st * UNIT, reinterpret_cast<const uint8_t*>(a.arena) + (size_t)row0 * UNIT, UNIT, full0 + st * 8);
+                } else if (!failed) {
                     if (a.debug & 2) {  // measurement only: one unswizzled box per tile (math would be wrong)
                         mbar_expect_tx(full0 + st * 8, UNIT);
                         tma_load_2d(ring + st * UNIT, &tmap, 0, row0, full0 + st * 8);
@@ -601,7 +773,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     Piece cur = load_piece(a, first_seg);  // plan and block tables were uploaded by a copy: always visible
     pdl_wait();  // q, k_new and v_new come from earlier work in the stream
     uint32_t qf[1][D / 16][2];
-    load_q_frags<D>(a, cur, g, t, qf);
+    if constexpr (Q8) load_q_frags_q8<D>(a, cur, g, t, qf);
+    else load_q_frags<D>(a, cur, g, t, qf);
     if (tid == 32) stamp(a, 3);
     bool failed = false;
     int seg = first_seg, pb = u0, k = 0;
@@ -614,7 +787,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         const bool more = pe < u1;
         if (more) {  // next piece's metadata and queries arrive while this one is processed
             nxt = load_piece(a, seg + 1);
-            load_q_frags<D>(a, nxt, g, t, qf_next);
+            if constexpr (Q8) load_q_frags_q8<D>(a, nxt, g, t, qf_next);
+            else load_q_frags<D>(a, nxt, g, t, qf_next);
         }
         float o[1][D / 16][4], m[1][2] = {{-INFINITY, -INFINITY}}, l[1][2] = {{0.f, 0.f}};
 #pragma unroll
@@ -633,7 +807,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             if (first_tile && tid == 32) { stamp(a, 4); first_tile = false; }
             const int lp = cur.page_lo + (u - cur.sb);
             if (!failed && !(a.debug & 1)) {
-                if (a.k_new != nullptr && lp == cur.page_last) {
+                if (!Q8 && a.k_new != nullptr && lp == cur.page_last) {
                     // fused append: put the new K/V row into the tile just fetched and into its page
                     const int slot = cur.q_pos & 15;
                     const int phys = a.step.tables[cur.tbl_off + lp];
@@ -653,7 +827,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     __syncwarp();
                 }
                 const bool need_mask = (lp * 16 + 15 > cur.q_pos) || (a.window > 0 && lp * 16 + a.window <= cur.q_pos);
-                attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+                if constexpr (Q8) attend_tile_q8<D, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+                else attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + st * 8);  // the stage may be refilled
@@ -676,13 +851,16 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         float* cml = comb_ml + (buf * C + cw) * 16;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
+            // the d-values behind rows g and g+8 of m-tile mt (permuted for quantised tiles, see attend_tile_q8)
+            const int d0 = Q8 ? 32 * (mt >> 1) + 4 * g + 2 * (mt & 1) : mt * 16 + g;
+            const int d1 = Q8 ? d0 + 1 : d0 + 8;
             if (2 * t < ccols) {
-                co[(2 * t) * D + mt * 16 + g] = o[0][mt][0];
-                co[(2 * t) * D + mt * 16 + g + 8] = o[0][mt][2];
+                co[(2 * t) * D + d0] = o[0][mt][0];
+                co[(2 * t) * D + d1] = o[0][mt][2];
             }
             if (2 * t + 1 < ccols) {
-                co[(2 * t + 1) * D + mt * 16 + g] = o[0][mt][1];
-                co[(2 * t + 1) * D + mt * 16 + g + 8] = o[0][mt][3];
+                co[(2 * t + 1) * D + d0] = o[0][mt][1];
+                co[(2 * t + 1) * D + d1] = o[0][mt][3];
             }
         }
         if (g == 0) {
@@ -920,8 +1098,9 @@ template <> struct DecodeCfg<64>  { static constexpr int C = 6, CTAS = 1; };
 template <> struct DecodeCfg<128> { static constexpr int C = 6, CTAS = 1; };
 template <> struct DecodeCfg<256> { static constexpr int C = 6, CTAS = 1; };
 
-static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols, int comb_bufs) {
-    return stages * 32 * d * 2 + comb_bufs * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 32 +
+static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols, int comb_bufs, bool q8 = false) {
+    const int unit = q8 ? (int)qrec_bytes(16, d) : 32 * d * 2;
+    return stages * unit + comb_bufs * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 32 +
            ROWS_CAP * 4 + SEG_CAP * 12;
 }
 
@@ -937,7 +1116,7 @@ template <int D> constexpr int chunk_smem() { return ChunkCfg<D>::W * ChunkCfg<D
 // reserved by the system), at most 8 stages per consumer.  Bytes in flight matter
 // more than a second merge buffer: the merge area is double-buffered only when that
 // costs no stage.
-DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers) {
+DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers, bool q8) {
     int c, ctas;
     switch (d) {
         case 64: c = DecodeCfg<64>::C; ctas = DecodeCfg<64>::CTAS; break;
@@ -951,11 +1130,11 @@ DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int co
     const int budget = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
     if (stages <= 0) {
         stages = 8 * c;
-        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols, 1) > budget) stages -= c;
+        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols, 1, q8) > budget) stages -= c;
     }
     stages = std::max(c, (stages / c) * c);
-    const int bufs = decode_smem_bytes(d, c, stages, comb_cols, 2) <= budget ? 2 : 1;
-    return {c, stages, decode_smem_bytes(d, c, stages, comb_cols, bufs), ctas, comb_cols, bufs};
+    const int bufs = decode_smem_bytes(d, c, stages, comb_cols, 2, q8) <= budget ? 2 : 1;
+    return {c, stages, decode_smem_bytes(d, c, stages, comb_cols, bufs, q8), ctas, comb_cols, bufs};
 }
 ChunkConfig chunk_config(int d) {
     switch (d) {
@@ -968,11 +1147,17 @@ ChunkConfig chunk_config(int d) {
 
 template <int D, bool BF16> static cudaError_t set_attrs() {
     cudaError_t e;
-    e = cudaFuncSetAttribute(decode_kernel<D, 4, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(decode_kernel<D, 4, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(decode_kernel<D, 6, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(decode_kernel<D, 6, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(decode_kernel<D, 8, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(decode_kernel<D, 8, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 4, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 6, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 8, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(chunk_kernel<D, ChunkCfg<D>::NT, ChunkCfg<D>::W, ChunkCfg<D>::S, BF16>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_smem<D>());
@@ -998,7 +1183,7 @@ cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-template <int D, int C, bool BF16>
+template <int D, int C, bool BF16, bool Q8>
 static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int smem, bool pdl, cudaStream_t st) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)n_ctas);
@@ -1010,25 +1195,31 @@ static cudaError_t launch_decode_t(const CUtensorMap& map, const DecodeArgs& a, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, decode_kernel<D, C, BF16>, map, a);
+    return cudaLaunchKernelEx(&cfg, decode_kernel<D, C, BF16, Q8>, map, a);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool Q8>
 static cudaError_t launch_decode_c(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, cudaStream_t st) {
     switch (consumers) {
-        case 4: return launch_decode_t<D, 4, BF16>(map, a, n_ctas, smem, pdl, st);
-        case 6: return launch_decode_t<D, 6, BF16>(map, a, n_ctas, smem, pdl, st);
-        case 8: return launch_decode_t<D, 8, BF16>(map, a, n_ctas, smem, pdl, st);
+        case 4: return launch_decode_t<D, 4, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
+        case 6: return launch_decode_t<D, 6, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
+        case 8: return launch_decode_t<D, 8, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
         default: return cudaErrorInvalidValue;
     }
 }
+template <int D>
+static cudaError_t launch_decode_d(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, bool bf16, bool q8, cudaStream_t st) {
+    if (q8) return bf16 ? launch_decode_c<D, true, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<D, false, true>(map, a, n_ctas, consumers, smem, pdl, st);
+    return bf16 ? launch_decode_c<D, true, false>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<D, false, false>(map, a, n_ctas, consumers, smem, pdl, st);
+}
 
-cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, bool bf16, cudaStream_t st) {
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, bool bf16, cudaStream_t st, bool q8) {
     if (a.n_stages < consumers || a.n_stages % consumers != 0) return cudaErrorInvalidValue;
+    if (q8 && a.k_new != nullptr) return cudaErrorInvalidValue;  // no fused append into int8 records
     switch (a.geo.d) {
-        case 64: return bf16 ? launch_decode_c<64, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<64, false>(map, a, n_ctas, consumers, smem, pdl, st);
-        case 128: return bf16 ? launch_decode_c<128, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<128, false>(map, a, n_ctas, consumers, smem, pdl, st);
-        case 256: return bf16 ? launch_decode_c<256, true>(map, a, n_ctas, consumers, smem, pdl, st) : launch_decode_c<256, false>(map, a, n_ctas, consumers, smem, pdl, st);
+        case 64: return launch_decode_d<64>(map, a, n_ctas, consumers, smem, pdl, bf16, q8, st);
+        case 128: return launch_decode_d<128>(map, a, n_ctas, consumers, smem, pdl, bf16, q8, st);
+        case 256: return launch_decode_d<256>(map, a, n_ctas, consumers, smem, pdl, bf16, q8, st);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -32,15 +32,25 @@ CBKV_HD inline int page_row(int kv, int slot, int page_size, bool tiled) {
     return tiled ? ((slot >> 3) * 16 + kv * 8 + (slot & 7)) : (kv * page_size + slot);
 }
 // Quantised layers keep one record per (page, kv head):
-//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32 elems][V scales: P x d/32 elems]
-// a value byte is q+128 for d-indices 0-2 mod 4 and q (signed) for index 3 mod 4: the reference's packed
-// little-endian int32 words (kv.rs:276-283) laid out in d order.
+//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32 elems][V scales: d/32 x P elems]
+// A value byte is q+128 for d-indices 0-2 mod 4 and q (signed) for index 3 mod 4: the reference's packed
+// little-endian int32 words (kv.rs:276-283) laid out in d order.  Inside a row the 32-byte groups are
+// permuted (group g sits at position g ^ qrec_swz) so that the decode kernel, which copies a record to
+// shared memory as it is, reads it without bank conflicts; V scales are stored group-major so that the
+// scales of two neighbouring tokens are one 32-bit word.
 CBKV_HD inline size_t qrec_bytes(int page_size, int d) { return (size_t)2 * page_size * d + (size_t)2 * page_size * (d / 32) * 2; }
+CBKV_HD inline int qrec_swz(int is_v, int slot, int d) {
+    if (d == 64) return (slot >> 1) & 1;
+    if (d == 128 || d == 256 || d == 512) return (is_v ? (slot >> 1) : slot) & 3;
+    return 0;
+}
 CBKV_HD inline size_t qrec_value_off(int is_v, int slot, int j, int page_size, int d) {
-    return (size_t)is_v * page_size * d + (size_t)slot * d + j;
+    return (size_t)is_v * page_size * d + (size_t)slot * d + (size_t)((((j >> 5) ^ qrec_swz(is_v, slot, d)) << 5) + (j & 31));
 }
 CBKV_HD inline size_t qrec_scale_off(int is_v, int slot, int group, int page_size, int d) {
-    return (size_t)2 * page_size * d + ((size_t)is_v * page_size * (d / 32) + (size_t)slot * (d / 32) + group) * 2;
+    const size_t base = (size_t)2 * page_size * d;
+    return is_v ? base + ((size_t)page_size * (d / 32) + (size_t)group * page_size + slot) * 2
+                : base + ((size_t)slot * (d / 32) + group) * 2;
 }
 
 struct LayerArena {
@@ -148,12 +158,13 @@ struct RopeArgs {
 
 // Decode kernel configuration for a head_dim (0 warps = not supported by the fast path).
 struct DecodeConfig { int consumers, stages, smem_bytes, ctas_per_sm, comb_cols, comb_bufs; };
-DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers);
+DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int consumers, bool q8 = false);
 struct ChunkConfig { int warps, stages, smem_bytes, cols_per_item; };
 ChunkConfig chunk_config(int d);
 
 cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
-cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st);
+cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st,
+                          bool q8 = false);  // q8: `a.arena` holds int8 records, `map` is unused
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);

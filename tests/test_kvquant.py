@@ -104,3 +104,75 @@ def test_quantized_cache_tracks_the_float_cache():
             outs.append(arena.attention(0, dev(q_tok(i)), dev(kv_tok(i, 0)), dev(kv_tok(i, 5)), scale).float().cpu().numpy())
         assert np.all(np.isfinite(outs[1])) and np.all(np.abs(outs[0] - outs[1]) < 5e-2)
     assert sq.seq_len() == 30 and sq.pages_used() == 2
+
+
+@pytest.mark.gpu
+def test_quantized_decode_streams_many_pages_and_reuses_the_ring():
+    # long contexts, ragged lengths, a window: every CTA wraps its ring many times and segments are cut
+    # across CTAs; decode runs on the record-streaming kernel, the fill on the generic one
+    from oracle import OracleArena
+    n_q, n_kv, d = 28, 4, 128
+    rng = np.random.default_rng(31)
+    lens = [3000, 1500, 777, 16, 1]
+    pages = sum((L + 40) // 16 + 1 for L in lens)
+    g = KVArena(1, n_q, n_kv, d, 3100, num_pages=pages, quantize_kv=True)
+    o = OracleArena(1, n_kv, d, 3100, num_pages=pages, rolling=False, dtype="f16", quantize_kv=True)
+    perm = rng.permutation(pages)
+    g.set_free_list(perm); o.set_free_list(perm)
+    gs, os_ = [g.new_seq() for _ in lens], [o.new_seq() for _ in lens]
+    k = [rng.standard_normal((n_kv, L, d)).astype(np.float16) for L in lens]
+    v = [rng.standard_normal((n_kv, L, d)).astype(np.float16) for L in lens]
+    cat = lambda xs: torch.from_numpy(np.concatenate([x.reshape(-1) for x in xs])).cuda()
+    g.begin_step(gs, lens)
+    g.append(0, cat(k), cat(v))
+    o.batch_begin(os_, lens)
+    for b, s in enumerate(os_):
+        s.append_only(0, k[b], v[b], 0)
+    for step, window in enumerate([None, None, 1000, None]):
+        one = [1] * len(lens)
+        q, k1, v1 = ([rng.standard_normal((h, 1, d)).astype(np.float16) for _ in lens] for h in (n_q, n_kv, n_kv))
+        g.begin_step(gs, one)
+        got = g.attention(0, cat(q), cat(k1), cat(v1), d ** -0.5, window).cpu().numpy()
+        o.batch_begin(os_, one)
+        flat = lambda xs: np.concatenate([x.reshape(-1) for x in xs])
+        ref = o.batch_layer(os_, one, 0, flat(q), flat(k1), flat(v1), n_q, d ** -0.5, window)
+        from kvcase import assert_attention_close
+        assert_attention_close(got, ref, f"decode step {step}")
+    assert g.device_status() == 0
+    for b in (0, 4):
+        for pg in gs[b].block_table()[-2:]:
+            for x, y in zip(g.export_page_quant(0, int(pg)), o.page_quant(0, int(pg))):
+                assert np.array_equal(x, y if y.dtype == np.int32 else y.view(np.uint16))
+
+
+@pytest.mark.gpu
+def test_bf16_quantized_decode_against_a_float32_reading_of_its_own_pages():
+    n_q, n_kv, d, L = 8, 2, 128, 333
+    rng = np.random.default_rng(8)
+    g = KVArena(1, n_q, n_kv, d, 512, quantize_kv=True, dtype=torch.bfloat16)
+    s = g.new_seq()
+    t = lambda x: torch.from_numpy(x).cuda().to(torch.bfloat16)
+    k, v = rng.standard_normal((n_kv, L, d)).astype(np.float32), rng.standard_normal((n_kv, L, d)).astype(np.float32)
+    g.begin_step([s], [L])
+    g.append(0, t(k.reshape(-1)), t(v.reshape(-1)))
+    q, k1, v1 = (rng.standard_normal((h, 1, d)).astype(np.float32) for h in (n_q, n_kv, n_kv))
+    g.begin_step([s], [1])
+    got = g.attention(0, t(q.reshape(-1)), t(k1.reshape(-1)), t(v1.reshape(-1)), d ** -0.5).float().cpu().numpy().reshape(n_q, d)
+    # read the pages back and de-quantise them by the reference's rule (kv.rs:319-358) in float32
+    K, V = np.zeros((n_kv, L + 1, d), np.float32), np.zeros((n_kv, L + 1, d), np.float32)
+    for lp, pg in enumerate(s.block_table()):
+        kp, ks, vp, vs = g.export_page_quant(0, int(pg))
+        n = min(16, L + 1 - lp * 16)
+        for packed, scales, dst in ((kp, ks, K), (vp, vs, V)):
+            by = packed.view(np.uint8).reshape(n_kv, 16, d).astype(np.int32)
+            qv = np.where(np.arange(d) % 4 == 3, by.astype(np.int8).astype(np.int32), by - 128)
+            sc = torch.from_numpy(scales.astype(np.int16)).view(torch.bfloat16).float().numpy()      # [n_kv, 16, d/32]
+            dq = torch.from_numpy(qv.astype(np.float32) * np.repeat(sc, 32, axis=-1)).to(torch.bfloat16).float().numpy()
+            dst[:, lp * 16:lp * 16 + n] = dq[:, :n]
+    qb = torch.from_numpy(q).to(torch.bfloat16).float().numpy().reshape(n_q, d)
+    ref = np.zeros((n_q, d), np.float32)
+    for h in range(n_q):
+        sc = (K[h // (n_q // n_kv)] @ qb[h]) * d ** -0.5
+        p = np.exp(sc - sc.max()); p /= p.sum()
+        ref[h] = p @ V[h // (n_q // n_kv)]
+    assert np.abs(got - ref).max() < 2e-2, np.abs(got - ref).max()
