@@ -62,6 +62,9 @@ def select_config(name: str) -> None:
     SCALE = D ** -0.5
 
 
+QUANT = False  # --quantize-kv: int8 KV pages (CacheConfig::quantize_kv)
+
+
 def context_lengths(rank: int) -> np.ndarray:
     """Cached tokens per sequence before the first decode step (suffix lengths when a prefix is shared)."""
     rng = np.random.default_rng(SEED + 1000 * rank)
@@ -76,7 +79,10 @@ def algorithmic_bytes_per_layer(lens_after: np.ndarray, window=None) -> float:
     L = lens_after.astype(np.float64)
     if window:
         L = np.minimum(L, float(window))
-    per = 4 * N_KV * D * L + 4 * N_Q * D + 8 * N_KV * D + 4 * np.ceil(L / PAGE)
+    if QUANT and not window:  # int8 pages: one byte per value plus one 2-byte scale per 32 values, K and V
+        per = 2 * N_KV * (D + D // 16) * L + 4 * N_Q * D + 4 * N_KV * D + 2 * N_KV * (D + D // 16) + 4 * np.ceil(L / PAGE)
+    else:
+        per = 4 * N_KV * D * L + 4 * N_Q * D + 8 * N_KV * D + 4 * np.ceil(L / PAGE)
     return float(per.sum())
 
 
@@ -203,7 +209,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     lens = context_lengths(rank)
     total_steps = 3 * (args.steps + args.warmup) + 16
     arena = KVArena(LAYERS, N_Q, N_KV, D, PREFIX + CTX_HI + total_steps + 64, PAGE, ARENA_PAGES, windows=WINDOWS,
-                    device=local_rank, sliding_popn_refuses=False)
+                    device=local_rank, sliding_popn_refuses=False, quantize_kv=QUANT)
     arena.set_free_list(np.random.default_rng(SEED + 7 + rank).permutation(ARENA_PAGES))
     if args.ctas_per_sm or args.stages or args.consumers or args.no_overlap:
         arena.set_decode_tuning(args.ctas_per_sm, args.stages, args.consumers, 0, not args.no_overlap)
@@ -331,7 +337,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     traffic = None
     tpath = os.path.join(ROOT, "profiles", f"decode_kernel_{args.config}_traffic.txt")
-    if os.path.exists(tpath) and not args.layers:
+    if os.path.exists(tpath) and not args.layers and not QUANT:
         traffic = float(json.load(open(tpath))["traffic_bytes_per_launch"])  # from the committed ncu capture
 
     cpu = None
@@ -347,13 +353,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD,
+        "config": {"workload": WORKLOAD + (", int8 KV pages (quantize_kv): append quantises, decode reads records" if QUANT else ""),
                    "l2": f"inputs larger than L2 (about {bytes_step / 1e9:.1f} GB of KV read per step)",
                    "sharding": "by sequence, no collective"},
         "hbm_gbs": bytes_step * world / (ms / args.steps * 1e-3) / 1e9,
         "hbm_frac_of_8tbs": bytes_step / (ms / args.steps * 1e-3) / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "kernel": f"decode_kernel<d={D},f16>", "us_per_launch": kms / kn * 1e3,
+                     "traffic": traffic, "kernel": f"decode_kernel<d={D},f16{',int8 pages' if QUANT else ''}>", "us_per_launch": kms / kn * 1e3,
                      "algorithmic_bytes_per_launch": bytes_launch, "peak_source": peak_src},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ems / args.steps},
@@ -515,6 +521,7 @@ def main():
     ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8)")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quantize-kv", action="store_true", help="int8 KV pages (the reference's CacheConfig::quantize_kv)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer than the 28 layers (small ncu case)")
     args = ap.parse_args()
     if args.config == "cfg4":
@@ -522,6 +529,8 @@ def main():
     if args.config == "rope":
         return run_rope(args, int(os.environ.get("RANK", "0")), 1, int(os.environ.get("LOCAL_RANK", "0")))
     select_config(args.config)
+    global QUANT
+    QUANT = bool(args.quantize_kv)
     if args.layers:
         global LAYERS, WINDOWS
         LAYERS = args.layers

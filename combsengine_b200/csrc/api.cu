@@ -190,8 +190,22 @@ int32_t materialize(Arena* a, int layer, cudaStream_t st) {
     if (a->layer_quant(layer)) {  // Arena::Quant, zero-filled (kv.rs:699-705)
         const size_t bytes = (size_t)a->num_pages * a->cfg.n_kv_heads * qrec_bytes(a->cfg.page_size, a->cfg.head_dim);
         CU_TRY(cudaMalloc(&L.base, bytes));
-        CU_TRY(cudaMemsetAsync(L.base, 0, bytes, st));
+        CU_TRY(launch_init_quant(L.base, (size_t)a->num_pages * a->cfg.n_kv_heads, a->cfg.page_size, a->cfg.head_dim, st));
         L.quant = true;
+        if (d->fast) {
+            // the decode kernel fetches one record per copy: a byte tensor of 128-byte rows, one box = one record
+            const uint64_t rec_rows = qrec_bytes(16, a->cfg.head_dim) / 128;
+            const uint64_t rows = (uint64_t)a->num_pages * a->cfg.n_kv_heads * rec_rows;
+            if (rows >= (1ull << 31)) { set_error("arena too large for one tensor map"); return CBKV_ERR_ARG; }
+            cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+            cuuint64_t strides[1] = {128};
+            cuuint32_t box[2] = {128, (cuuint32_t)rec_rows};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = encode_fn()(&L.map_kv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, L.base, dims, strides, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 records) failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
+        }
         return CBKV_OK;
     }
     CU_TRY(cudaMalloc(&L.base, d->layer_bytes));
@@ -968,7 +982,8 @@ int32_t cbkv_export_page_quant(cbkv_arena* arena, int32_t layer, int64_t page, i
                 uint8_t* pk = reinterpret_cast<uint8_t*>(is_v ? vp : kp) + ((size_t)h * P + slot) * D;
                 uint8_t* sc = reinterpret_cast<uint8_t*>(is_v ? vs : ks) + ((size_t)h * P + slot) * G * 2;
                 const uint8_t* r = buf.data() + (size_t)h * rec;
-                for (int j = 0; j < D; j++) pk[j] = r[qrec_value_off(is_v, slot, j, P, D)];
+                // records hold q + 128 in every byte; the reference's words keep lane 3 signed (kv.rs:276-283)
+                for (int j = 0; j < D; j++) pk[j] = r[qrec_value_off(is_v, slot, j, P, D)] ^ ((j & 3) == 3 ? 0x80 : 0x00);
                 for (int g = 0; g < G; g++) memcpy(sc + 2 * g, r + qrec_scale_off(is_v, slot, g, P, D), 2);
             }
     return CBKV_OK;

@@ -213,7 +213,7 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
 }
 
 // ------------------------------------------------------------------ int8 pages (kv.rs:271-358)
-// A quantised record (kernels.hpp, qrec_*) reaches shared memory by one bulk copy.  Values are
+// A quantised record (kernels.hpp, qrec_*) reaches shared memory as it lies in HBM, by one TMA box.  Values are
 // converted in registers by a byte permute that puts a constant exponent byte over each value byte
 // and one exact subtraction (q8_pair).  The group scales never touch the values: K's multiply the f32 score partial sums of their 32-wide group, V's multiply the
 // probabilities of their token before the P.V product of that group's rows.
@@ -222,13 +222,9 @@ __device__ __forceinline__ void attend_tile(uint32_t stage, const uint32_t (&qf)
 // output rows of O^T if the store undoes it; that is how a thread gets whole 4- and 8-byte words:
 //   K (A operand, row = token): per group a thread takes bytes 8t..8t+7 of rows g and g+8; k-step s
 //     contracts d = 32*grp + 8t + 4s + {0,1,2,3} against the Q fragment loaded in the same order.
-//   V (A operand of O^T, row = d): per group a thread takes bytes 4g..4g+3 of tokens 2t, 2t+1, 2t+8,
-//     2t+9; m-tile 2*grp has rows d = 32*grp + 4g + {0 (row g), 1 (row g+8)}, m-tile 2*grp+1 the
-//     other two.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
+//   V (A operand of O^T, row = d): per group a thread takes d = 4g..4g+3 of token pairs (2t, 2t+1)
+//     and (2t+8, 2t+9), stored pair-interleaved so that one register is one 16-bit pick; m-tile
+//     2*grp has rows d = 32*grp + 4g + {0 (row g), 1 (row g+8)}, m-tile 2*grp+1 the other two.
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -244,12 +240,12 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     asm volatile("ld.shared.b16 %0, [%1];" : "=h"(v) : "r"(addr));
     return v;
 }
-// Byte -> number.  f16: all four bytes of a word are made offset binary (b = q + 128); a byte under
-// the exponent byte 0x64 reads as 1024 + b, and subtracting 1152 leaves q.  bf16 has one mantissa bit
-// less than a byte is wide, so there the bytes are made two's complement instead: the low seven bits
+// Byte -> number.  Every byte of a record is b = q + 128.  f16: a byte under the exponent byte 0x64
+// reads as 1024 + b, and subtracting 1152 leaves q.  bf16 has one mantissa bit less than a byte is
+// wide, so there the bytes are first made two's complement (one XOR per word): the low seven bits
 // under 0x43 read as 128 + (b & 127), the sign bit under 0x43 reads as 128 or 256, and their
 // difference is q.  Both subtractions are exact.
-template <bool BF16> __device__ __forceinline__ uint32_t q8_fix(uint32_t w) { return w ^ (BF16 ? 0x00808080u : 0x80000000u); }
+template <bool BF16> __device__ __forceinline__ uint32_t q8_fix(uint32_t w) { return BF16 ? (w ^ 0x80808080u) : w; }
 // two bytes of `src` (selected by `sel`, which also places the exponent bytes) -> two numbers q
 template <bool BF16>
 __device__ __forceinline__ uint32_t q8_pair(uint32_t src, uint32_t sel) {
@@ -274,39 +270,77 @@ __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
         return *reinterpret_cast<uint32_t*>(&r);
     }
 }
+template <bool BF16>
+__device__ __forceinline__ float2 up2(uint32_t v) {
+    if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+    else return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 constexpr uint32_t SEL_LO = 0x5140u;  // bytes 0 and 1 of the source, each under an exponent byte
 constexpr uint32_t SEL_HI = 0x7362u;  // bytes 2 and 3
 
-// One 16-token quantised tile against the 8 query columns of the kv group (decode).
+// One 16-token quantised tile against the 8 query columns of the kv group (decode).  All
+// shared-memory reads of the tile are issued first.  The running maximum of a column moves only
+// when the new one exceeds it by 2^8 (the exponentials stay far inside the f16 range), so most
+// tiles skip the rescaling of the output accumulators.
 template <int D, bool BF16>
 __device__ __forceinline__ void attend_tile_q8(uint32_t stage, const uint32_t (&qf)[1][D / 16][2], float (&o)[1][D / 16][4],
                                                float (&m)[1][2], float (&l)[1][2], int kpos0, const int (&qpos)[1][2],
-                                               int window, float scale_log2, bool need_mask, int lane) {
+                                               int window, float scale_log2, bool need_mask, int lane, int dbg = 0) {
     constexpr int G = D / 32;
+    static_assert(G % 2 == 0, "scales are read two at a time");
     const int g = lane >> 2, t = lane & 3;
     const uint32_t kbase = stage, vbase = stage + 16u * D, ksc = stage + 32u * D, vsc = ksc + 16u * G * 2u;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-    // ---- S^T = sum over groups of scale_K[token][grp] * (Kq . Q^T)
+    // ---- loads: K bytes of rows g, g+8; V bytes of token pairs t, t+4; their scales
+    uint2 kx[G], ky[G], va[G], vb[G];
+    uint32_t ks0[G / 2], ks1[G / 2], vs0[G], vs1[G];
     {
-        const int swz = qrec_swz(0, g, D);  // rows g and g+8 share it
+        const int swz = qrec_swz(g, D);  // rows g and g+8 share it
         const uint32_t r0 = kbase + (uint32_t)g * D + 8u * t, r1 = r0 + 8u * D;
 #pragma unroll
         for (int grp = 0; grp < G; grp++) {
             const uint32_t off = (uint32_t)((grp ^ swz) << 5);
-            uint2 x = lds64(r0 + off), y = lds64(r1 + off);
-            x.x = q8_fix<BF16>(x.x); x.y = q8_fix<BF16>(x.y); y.x = q8_fix<BF16>(y.x); y.y = q8_fix<BF16>(y.y);
-            float sg[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t a[4];
-            a[0] = q8_pair<BF16>(x.x, SEL_LO); a[1] = q8_pair<BF16>(y.x, SEL_LO);
-            a[2] = q8_pair<BF16>(x.x, SEL_HI); a[3] = q8_pair<BF16>(y.x, SEL_HI);
-            mma_16816<BF16>(sg, a, qf[0][2 * grp][0], qf[0][2 * grp][1]);
-            a[0] = q8_pair<BF16>(x.y, SEL_LO); a[1] = q8_pair<BF16>(y.y, SEL_LO);
-            a[2] = q8_pair<BF16>(x.y, SEL_HI); a[3] = q8_pair<BF16>(y.y, SEL_HI);
-            mma_16816<BF16>(sg, a, qf[0][2 * grp + 1][0], qf[0][2 * grp + 1][1]);
-            const float k0 = from_elem<BF16>((uint16_t)lds16(ksc + (uint32_t)(g * G + grp) * 2u));
-            const float k1 = from_elem<BF16>((uint16_t)lds16(ksc + (uint32_t)((g + 8) * G + grp) * 2u));
-            s[0] += sg[0] * k0; s[1] += sg[1] * k0; s[2] += sg[2] * k1; s[3] += sg[3] * k1;
+            kx[grp] = lds64(r0 + off);
+            ky[grp] = lds64(r1 + off);
         }
+#pragma unroll
+        for (int i = 0; i < G / 2; i++) {
+            ks0[i] = lds32(ksc + (uint32_t)(g * G + 2 * i) * 2u);
+            ks1[i] = lds32(ksc + (uint32_t)((g + 8) * G + 2 * i) * 2u);
+        }
+        // pair t and pair t+4 share the unit and chunk permutation (qrec_value_off)
+        const uint32_t c0 = vbase + (uint32_t)t * 2u * D + (uint32_t)((g ^ (4 * ((t >> 1) & 1))) * 8);
+#pragma unroll
+        for (int grp = 0; grp < G; grp++) {
+            const uint32_t off = (uint32_t)((grp ^ (t & 1)) * 64);
+            va[grp] = lds64(c0 + off);
+            vb[grp] = lds64(c0 + 8u * D + off);
+            vs0[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t) * 2u);
+            vs1[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t + 8) * 2u);
+        }
+    }
+    // ---- S^T = sum over groups of scale_K[token][grp] * (Kq . Q^T)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!(dbg & 32))  // measurement only: skip the score phase
+#pragma unroll
+    for (int grp = 0; grp < G; grp++) {
+        const uint32_t x0 = q8_fix<BF16>(kx[grp].x), x1 = q8_fix<BF16>(kx[grp].y);
+        const uint32_t y0 = q8_fix<BF16>(ky[grp].x), y1 = q8_fix<BF16>(ky[grp].y);
+        float sg[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t a[4];
+        a[0] = q8_pair<BF16>(x0, SEL_LO); a[1] = q8_pair<BF16>(y0, SEL_LO);
+        a[2] = q8_pair<BF16>(x0, SEL_HI); a[3] = q8_pair<BF16>(y0, SEL_HI);
+        mma_16816<BF16>(sg, a, qf[0][2 * grp][0], qf[0][2 * grp][1]);
+        a[0] = q8_pair<BF16>(x1, SEL_LO); a[1] = q8_pair<BF16>(y1, SEL_LO);
+        a[2] = q8_pair<BF16>(x1, SEL_HI); a[3] = q8_pair<BF16>(y1, SEL_HI);
+        mma_16816<BF16>(sg, a, qf[0][2 * grp + 1][0], qf[0][2 * grp + 1][1]);
+        const float2 f0 = up2<BF16>(ks0[grp >> 1]), f1 = up2<BF16>(ks1[grp >> 1]);
+        const float k0 = (grp & 1) ? f0.y : f0.x, k1 = (grp & 1) ? f1.y : f1.x;
+        s[0] += sg[0] * k0; s[1] += sg[1] * k0; s[2] += sg[2] * k1; s[3] += sg[3] * k1;
     }
     // ---- online softmax over the tile's 16 tokens (rows g and g+8 of the fragment)
 #pragma unroll
@@ -319,49 +353,48 @@ __device__ __forceinline__ void attend_tile_q8(uint32_t stage, const uint32_t (&
             if (!ok) s[i] = -INFINITY;
         }
     }
-    float alpha[2];
+    float alpha[2] = {1.f, 1.f};
+    bool moved = false;
+    if (!(dbg & 64))  // measurement only: skip the softmax
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         float mx = fmaxf(s[j], s[j + 2]);
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-        const float m_new = fmaxf(m[0][j], mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[j] = exp2f(m[0][j] - m_use);
-        m[0][j] = m_new;
-        const float p0 = exp2f(s[j] - m_use), p1 = exp2f(s[j + 2] - m_use);
+        if (mx > m[0][j] + 8.f) {  // also the first finite maximum (m starts at -inf)
+            alpha[j] = fast_ex2(m[0][j] - mx);
+            m[0][j] = mx;
+            moved = true;
+        }
+        const float m_use = (m[0][j] == -INFINITY) ? 0.f : m[0][j];
+        const float p0 = fast_ex2(s[j] - m_use), p1 = fast_ex2(s[j + 2] - m_use);
         s[j] = p0; s[j + 2] = p1;
         l[0][j] = l[0][j] * alpha[j] + p0 + p1;
     }
+    if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-    for (int mt = 0; mt < D / 16; mt++) {
-        o[0][mt][0] *= alpha[0]; o[0][mt][1] *= alpha[1];
-        o[0][mt][2] *= alpha[0]; o[0][mt][3] *= alpha[1];
+        for (int mt = 0; mt < D / 16; mt++) {
+            o[0][mt][0] *= alpha[0]; o[0][mt][1] *= alpha[1];
+            o[0][mt][2] *= alpha[0]; o[0][mt][3] *= alpha[1];
+        }
     }
     const uint32_t pb0 = movmatrix_trans(pack2<BF16>(s[0], s[1]));  // tokens 2t, 2t+1 of column g
     const uint32_t pb1 = movmatrix_trans(pack2<BF16>(s[2], s[3]));  // tokens 2t+8, 2t+9
     // ---- O^T += sum over groups of Vq^T . (P^T * scale_V[token][grp])
-    {
-        const int swz = qrec_swz(1, 2 * t, D);  // tokens 2t, 2t+1, 2t+8, 2t+9 share it
-        const uint32_t c0 = vbase + (uint32_t)(2 * t) * D + 4u * g;
+    if (!(dbg & 128))  // measurement only: skip the output phase
 #pragma unroll
-        for (int grp = 0; grp < G; grp++) {
-            const uint32_t off = (uint32_t)((grp ^ swz) << 5);
-            uint32_t w0 = lds32(c0 + off), w1 = lds32(c0 + D + off), w2 = lds32(c0 + 8u * D + off), w3 = lds32(c0 + 9u * D + off);
-            w0 = q8_fix<BF16>(w0); w1 = q8_fix<BF16>(w1); w2 = q8_fix<BF16>(w2); w3 = q8_fix<BF16>(w3);
-            const uint32_t b0 = mul2<BF16>(pb0, lds32(vsc + (uint32_t)(grp * 16 + 2 * t) * 2u));
-            const uint32_t b1 = mul2<BF16>(pb1, lds32(vsc + (uint32_t)(grp * 16 + 2 * t + 8) * 2u));
-            const uint32_t t01 = __byte_perm(w0, w1, SEL_LO), t23 = __byte_perm(w0, w1, SEL_HI);  // (w0.b, w1.b) pairs
-            const uint32_t u01 = __byte_perm(w2, w3, SEL_LO), u23 = __byte_perm(w2, w3, SEL_HI);
-            uint32_t a[4];
-            a[0] = q8_pair<BF16>(t01, SEL_LO); a[1] = q8_pair<BF16>(t01, SEL_HI);
-            a[2] = q8_pair<BF16>(u01, SEL_LO); a[3] = q8_pair<BF16>(u01, SEL_HI);
-            mma_16816<BF16>(o[0][2 * grp], a, b0, b1);
-            a[0] = q8_pair<BF16>(t23, SEL_LO); a[1] = q8_pair<BF16>(t23, SEL_HI);
-            a[2] = q8_pair<BF16>(u23, SEL_LO); a[3] = q8_pair<BF16>(u23, SEL_HI);
-            mma_16816<BF16>(o[0][2 * grp + 1], a, b0, b1);
-        }
+    for (int grp = 0; grp < G; grp++) {
+        const uint32_t a0 = q8_fix<BF16>(va[grp].x), a1 = q8_fix<BF16>(va[grp].y);  // d 4g, 4g+1 | 4g+2, 4g+3 of tokens 2t, 2t+1
+        const uint32_t c0 = q8_fix<BF16>(vb[grp].x), c1 = q8_fix<BF16>(vb[grp].y);  // the same of tokens 2t+8, 2t+9
+        const uint32_t b0 = mul2<BF16>(pb0, vs0[grp]), b1 = mul2<BF16>(pb1, vs1[grp]);
+        uint32_t a[4];
+        a[0] = q8_pair<BF16>(a0, SEL_LO); a[1] = q8_pair<BF16>(a0, SEL_HI);
+        a[2] = q8_pair<BF16>(c0, SEL_LO); a[3] = q8_pair<BF16>(c0, SEL_HI);
+        mma_16816<BF16>(o[0][2 * grp], a, b0, b1);
+        a[0] = q8_pair<BF16>(a1, SEL_LO); a[1] = q8_pair<BF16>(a1, SEL_HI);
+        a[2] = q8_pair<BF16>(c1, SEL_LO); a[3] = q8_pair<BF16>(c1, SEL_HI);
+        mma_16816<BF16>(o[0][2 * grp + 1], a, b0, b1);
     }
 }
 
@@ -529,7 +562,7 @@ __device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int n
 }
 
 // Warp roles: 0 = producer, 1..C = consumers, C+1 = merger.
-// Q8: the layer holds int8 records; a tile is one record fetched by a bulk copy, no fused append.
+// Q8: the layer holds int8 records; a tile is one record fetched as one box of a byte tensor map, no fused append.
 template <int D, int C, bool BF16, bool Q8>
 __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
     constexpr uint32_t UNIT = Q8 ? (uint32_t)(2 * 16 * D + 2 * 16 * (D / 32) * 2) : 32u * D * 2u;
@@ -564,7 +597,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     const int Hkv = a.geo.n_kv;
     const int first_seg = a.cta_first_seg[cta];
     if (tid == 0) {
-        if (!Q8) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
         for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
         for (int i = 0; i < 2; i++) { mbar_init(cfull0 + i * 8, C); mbar_init(cempty0 + i * 8, 1); }
         flag[0] = 0; flag[1] = 0; flag[2] = 0;
@@ -628,8 +661,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 const int row0 = rows[n % ROWS_CAP];
                 if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, ((n / NS) - 1) & 1)) failed = true;
                 if (!failed && Q8) {
-                    mbar_expect_tx(full0 + st * 8, UNIT);
-                    bulk_load(ring + st * UNIT, reinterpret_cast<const uint8_t*>(a.arena) + (size_t)row0 * UNIT, UNIT, full0 + st * 8);
+                    mbar_expect_tx(full0 + st * 8, UNIT);  // one box of UNIT/128 rows x 128 bytes = one record
+                    tma_load_2d(ring + st * UNIT, &tmap, 0, row0 * (int)(UNIT / 128u), full0 + st * 8);
                 } else if (!failed) {
                     if (a.debug & 2) {  // measurement only: one unswizzled box per tile (math would be wrong)
                         mbar_expect_tx(full0 + st * 8, UNIT);
@@ -827,7 +860,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     __syncwarp();
                 }
                 const bool need_mask = (lp * 16 + 15 > cur.q_pos) || (a.window > 0 && lp * 16 + a.window <= cur.q_pos);
-                if constexpr (Q8) attend_tile_q8<D, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+                if constexpr (Q8) attend_tile_q8<D, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane, a.debug);
                 else attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
             }
             __syncwarp();

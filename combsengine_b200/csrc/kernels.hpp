@@ -32,20 +32,26 @@ CBKV_HD inline int page_row(int kv, int slot, int page_size, bool tiled) {
     return tiled ? ((slot >> 3) * 16 + kv * 8 + (slot & 7)) : (kv * page_size + slot);
 }
 // Quantised layers keep one record per (page, kv head):
-//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32 elems][V scales: d/32 x P elems]
-// A value byte is q+128 for d-indices 0-2 mod 4 and q (signed) for index 3 mod 4: the reference's packed
-// little-endian int32 words (kv.rs:276-283) laid out in d order.  Inside a row the 32-byte groups are
-// permuted (group g sits at position g ^ qrec_swz) so that the decode kernel, which copies a record to
-// shared memory as it is, reads it without bank conflicts; V scales are stored group-major so that the
-// scales of two neighbouring tokens are one 32-bit word.
+//   [K bytes: P rows x d][V bytes: P/2 token pairs x d x 2][K scales: P x d/32 elems][V scales: d/32 x P elems]
+// Every value byte is q + 128 (the reference's packed words, kv.rs:276-283, keep their fourth lane
+// signed; the export flips that byte's top bit back).  The layout inside a record is the decode
+// kernel's, which copies a record to shared memory as it lies and reads it with 8-byte loads:
+//   K: row = token, d order, the 32-byte groups of a row permuted (group g at position g ^ swizzle);
+//   V: the two tokens of a pair interleaved per d (so the two numbers an MMA register needs are
+//      neighbours), 64-byte units = one group of a pair, units and their halves permuted;
+//   V scales group-major, so the scales of two neighbouring tokens are one 32-bit word.
 CBKV_HD inline size_t qrec_bytes(int page_size, int d) { return (size_t)2 * page_size * d + (size_t)2 * page_size * (d / 32) * 2; }
-CBKV_HD inline int qrec_swz(int is_v, int slot, int d) {
+CBKV_HD inline bool qrec_swizzled(int d) { return d == 64 || d == 128 || d == 256 || d == 512; }
+CBKV_HD inline int qrec_swz(int slot, int d) {  // K rows
     if (d == 64) return (slot >> 1) & 1;
-    if (d == 128 || d == 256 || d == 512) return (is_v ? (slot >> 1) : slot) & 3;
-    return 0;
+    return qrec_swizzled(d) ? (slot & 3) : 0;
 }
 CBKV_HD inline size_t qrec_value_off(int is_v, int slot, int j, int page_size, int d) {
-    return (size_t)is_v * page_size * d + (size_t)slot * d + (size_t)((((j >> 5) ^ qrec_swz(is_v, slot, d)) << 5) + (j & 31));
+    if (!is_v) return (size_t)slot * d + (size_t)((((j >> 5) ^ qrec_swz(slot, d)) << 5) + (j & 31));
+    const int pair = slot >> 1, sw = qrec_swizzled(d) ? 1 : 0;
+    const int unit = (j >> 5) ^ (sw * (pair & 1));               // 64-byte unit: one group of the pair
+    const int chunk = ((j & 31) >> 2) ^ (sw * 4 * ((pair >> 1) & 1));  // 8-byte chunk: 4 d-values x 2 tokens
+    return (size_t)page_size * d + (size_t)pair * 2 * d + (size_t)unit * 64 + (size_t)chunk * 8 + (size_t)(j & 3) * 2 + (slot & 1);
 }
 CBKV_HD inline size_t qrec_scale_off(int is_v, int slot, int group, int page_size, int d) {
     const size_t base = (size_t)2 * page_size * d;
@@ -164,9 +170,10 @@ ChunkConfig chunk_config(int d);
 
 cudaError_t launch_append(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem_bytes, bool pdl, bool bf16, cudaStream_t st,
-                          bool q8 = false);  // q8: `a.arena` holds int8 records, `map` is unused
+                          bool q8 = false);  // q8: the layer holds int8 records, `map` is the byte view with one record per box
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_init_quant(void* arena, size_t n_records, int page_size, int d, cudaStream_t st);
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic_quant(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, cudaStream_t st);

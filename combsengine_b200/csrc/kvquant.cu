@@ -2,14 +2,12 @@
 //
 //   append_quant_kernel    kv_quantize (kv.rs:284-313) fused with the page scatter
 //                          (kv.rs:746-768): per 32-value group scale = max(absmax/127, 1e-8)
-//                          in f32, q = clamp(round(x/scale), -127, 127), four values per 32-bit
-//                          word (lanes 0-2 offset binary, lane 3 signed), scale kept in the
-//                          element type
+//                          in f32, q = clamp(round(x/scale), -127, 127), one byte q + 128 per
+//                          value, scale kept in the element type
 //   generic_quant_kernel   attention over quantised pages for any shape: kv_dequantize
 //                          (kv.rs:319-358) happens on the fly, value = elem(q * scale), f32 math
 //
-// One record per (page, kv head), see qrec_* in kernels.hpp:
-//   [K bytes: P rows x d][V bytes: P rows x d][K scales: P x d/32][V scales: P x d/32]
+// One record per (page, kv head), laid out for the decode kernel (qrec_* in kernels.hpp),
 // so a decode step reads d + d/16 bytes per cached token and head instead of 2d.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -75,19 +73,37 @@ __global__ void __launch_bounds__(256) append_quant_kernel(const AppendArgs a) {
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
             const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);   // kv.rs:296-301
             if (live) {
-                uint32_t word = 0;
+                uint32_t word = 0;  // four bytes q + 128
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     float q = roundf(__fdiv_rn(x[i], scale));             // kv.rs:302-305
                     q = fminf(fmaxf(q, -127.f), 127.f);
-                    const int qi = (int)q;
-                    word |= (uint32_t)((i < 3 ? qi + 128 : qi) & 0xff) << (8 * i);   // kv.rs:308-311
+                    word |= (uint32_t)((int)q + 128) << (8 * i);
                 }
-                *reinterpret_cast<uint32_t*>(recp + qrec_value_off(is_v, slot, 4 * c, P, d)) = word;
+                if (!is_v) {
+                    *reinterpret_cast<uint32_t*>(recp + qrec_value_off(0, slot, 4 * c, P, d)) = word;
+                } else {  // the pair's other token sits between these bytes
+#pragma unroll
+                    for (int i = 0; i < 4; i++) recp[qrec_value_off(1, slot, 4 * c + i, P, d)] = (uint8_t)(word >> (8 * i));
+                }
                 if ((c & 7) == 0)
                     *reinterpret_cast<uint16_t*>(recp + qrec_scale_off(is_v, slot, c >> 3, P, d)) = q_down<BF16>(scale);
             }
         }
+    }
+}
+
+// A fresh quantised arena reads as the reference's zero-filled one (kv.rs:699-705): packed words 0
+// mean q = -128 in lanes 0-2 and q = 0 in lane 3, i.e. record bytes 0, 0, 0, 0x80; scales 0.
+__global__ void init_quant_kernel(uint8_t* arena, size_t n_records, int P, int d) {
+    const size_t rec = qrec_bytes(P, d), values = (size_t)2 * P * d;
+    const size_t words = n_records * (rec / 4);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (rec / 4), w = i - r * (rec / 4), off = w * 4;
+        uint32_t v = 0;
+        if (off < (size_t)P * d) v = 0x80000000u;                  // K: lane 3 is the top byte of each word
+        else if (off < values) v = (w & 1) ? 0x80800000u : 0u;      // V: lane 3 of both tokens = bytes 6, 7 of each 8
+        reinterpret_cast<uint32_t*>(arena)[i] = v;
     }
 }
 
@@ -114,10 +130,10 @@ __global__ void generic_quant_kernel(const GenericArgs a) {
     __syncwarp();
     const uint8_t* arena = reinterpret_cast<const uint8_t*>(a.arena);
     const size_t rec = qrec_bytes(P, D);
-    // kv_dequantize: lanes 0-2 are offset binary, lane 3 is signed (kv.rs:326-346); value = elem(q * scale)
+    // kv_dequantize (kv.rs:319-358): value = elem(q * scale); every byte of a record is q + 128
     auto value = [&](const uint8_t* recp, int is_v, int slot, int j) -> float {
         const uint8_t b = recp[qrec_value_off(is_v, slot, j, P, D)];
-        const int qi = (j & 3) == 3 ? (int)(int8_t)b : (int)b - 128;
+        const int qi = (int)b - 128;
         const float sc = q_up<BF16>(*reinterpret_cast<const uint16_t*>(recp + qrec_scale_off(is_v, slot, j >> 5, P, D)));
         return q_up<BF16>(q_down<BF16>(__fmul_rn((float)qi, sc)));
     };
@@ -172,6 +188,11 @@ __global__ void generic_quant_kernel(const GenericArgs a) {
 }
 
 }  // namespace
+
+cudaError_t launch_init_quant(void* arena, size_t n_records, int page_size, int d, cudaStream_t st) {
+    init_quant_kernel<<<148 * 8, 256, 0, st>>>(reinterpret_cast<uint8_t*>(arena), n_records, page_size, d);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st) {
     const int64_t rows = 2 * (int64_t)a.step.n_tokens * a.geo.n_kv;
