@@ -1062,6 +1062,11 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
             for (int c = 0; c < d->dbg_ctas; c++) { unsigned long long v = h[(size_t)c * 16 + s2]; if (!v) continue; double x = (double)(v - t0) * 1e-3; mn = std::min(mn, x); mx = std::max(mx, x); av += x; cnt++; }
             if (cnt) fprintf(stderr, "[cbkv timeline] %-22s min %7.2f avg %7.2f max %7.2f us (%d CTAs)\n", names[s2], mn, av / cnt, mx, cnt);
         }
+        {
+            double w = 0, tot = 0, n = 0;
+            for (int c = 0; c < d->dbg_ctas; c++) { w += (double)h[(size_t)c * 16 + 13]; tot += (double)h[(size_t)c * 16 + 14]; n += (double)h[(size_t)c * 16 + 15]; }
+            if (n > 0) fprintf(stderr, "[cbkv consumer0] per tile: %.0f cycles waiting for the tile, %.0f cycles in all (%.1f tiles per CTA)\n", w / n, tot / n, n / d->dbg_ctas);
+        }
         std::vector<int> order(d->dbg_ctas);
         for (int c = 0; c < d->dbg_ctas; c++) order[c] = c;
         std::sort(order.begin(), order.end(), [&](int x, int y) { return h[(size_t)x * 16 + 6] > h[(size_t)y * 16 + 6]; });

@@ -283,46 +283,58 @@ __device__ __forceinline__ float fast_ex2(float x) {
 constexpr uint32_t SEL_LO = 0x5140u;  // bytes 0 and 1 of the source, each under an exponent byte
 constexpr uint32_t SEL_HI = 0x7362u;  // bytes 2 and 3
 
-// One 16-token quantised tile against the 8 query columns of the kv group (decode).  All
-// shared-memory reads of the tile are issued first.  The running maximum of a column moves only
-// when the new one exceeds it by 2^8 (the exponentials stay far inside the f16 range), so most
-// tiles skip the rescaling of the output accumulators.
-template <int D, bool BF16>
-__device__ __forceinline__ void attend_tile_q8(uint32_t stage, const uint32_t (&qf)[1][D / 16][2], float (&o)[1][D / 16][4],
-                                               float (&m)[1][2], float (&l)[1][2], int kpos0, const int (&qpos)[1][2],
-                                               int window, float scale_log2, bool need_mask, int lane, int dbg = 0) {
+// One 16-token quantised tile against the 8 query columns of the kv group (decode), in two steps:
+// q8_load copies this thread's share of the record from shared memory to registers, after which the
+// ring stage can go back to the producer; q8_attend does the math from registers.  The running
+// maximum of a column moves only when the new one exceeds it by 2^8 (the exponentials stay far inside
+// the f16 range), so most tiles skip the rescaling of the output accumulators.
+template <int D>
+struct Q8Tile {
+    static constexpr int G = D / 32;
+    uint2 kx[G], ky[G], va[G], vb[G];            // K bytes of rows g, g+8; V bytes of token pairs t, t+4
+    uint32_t ks0[G / 2], ks1[G / 2], vs0[G], vs1[G];  // their scales
+};
+
+template <int D>
+__device__ __forceinline__ void q8_load(uint32_t stage, int lane, Q8Tile<D>& r) {
     constexpr int G = D / 32;
     static_assert(G % 2 == 0, "scales are read two at a time");
     const int g = lane >> 2, t = lane & 3;
     const uint32_t kbase = stage, vbase = stage + 16u * D, ksc = stage + 32u * D, vsc = ksc + 16u * G * 2u;
-    // ---- loads: K bytes of rows g, g+8; V bytes of token pairs t, t+4; their scales
-    uint2 kx[G], ky[G], va[G], vb[G];
-    uint32_t ks0[G / 2], ks1[G / 2], vs0[G], vs1[G];
-    {
-        const int swz = qrec_swz(g, D);  // rows g and g+8 share it
-        const uint32_t r0 = kbase + (uint32_t)g * D + 8u * t, r1 = r0 + 8u * D;
+    const int swz = qrec_swz(g, D);  // rows g and g+8 share it
+    const uint32_t r0 = kbase + (uint32_t)g * D + 8u * t, r1 = r0 + 8u * D;
 #pragma unroll
-        for (int grp = 0; grp < G; grp++) {
-            const uint32_t off = (uint32_t)((grp ^ swz) << 5);
-            kx[grp] = lds64(r0 + off);
-            ky[grp] = lds64(r1 + off);
-        }
-#pragma unroll
-        for (int i = 0; i < G / 2; i++) {
-            ks0[i] = lds32(ksc + (uint32_t)(g * G + 2 * i) * 2u);
-            ks1[i] = lds32(ksc + (uint32_t)((g + 8) * G + 2 * i) * 2u);
-        }
-        // pair t and pair t+4 share the unit and chunk permutation (qrec_value_off)
-        const uint32_t c0 = vbase + (uint32_t)t * 2u * D + (uint32_t)((g ^ (4 * ((t >> 1) & 1))) * 8);
-#pragma unroll
-        for (int grp = 0; grp < G; grp++) {
-            const uint32_t off = (uint32_t)((grp ^ (t & 1)) * 64);
-            va[grp] = lds64(c0 + off);
-            vb[grp] = lds64(c0 + 8u * D + off);
-            vs0[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t) * 2u);
-            vs1[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t + 8) * 2u);
-        }
+    for (int grp = 0; grp < G; grp++) {
+        const uint32_t off = (uint32_t)((grp ^ swz) << 5);
+        r.kx[grp] = lds64(r0 + off);
+        r.ky[grp] = lds64(r1 + off);
     }
+#pragma unroll
+    for (int i = 0; i < G / 2; i++) {
+        r.ks0[i] = lds32(ksc + (uint32_t)(g * G + 2 * i) * 2u);
+        r.ks1[i] = lds32(ksc + (uint32_t)((g + 8) * G + 2 * i) * 2u);
+    }
+    // pair t and pair t+4 share the unit and chunk permutation (qrec_value_off)
+    const uint32_t c0 = vbase + (uint32_t)t * 2u * D + (uint32_t)((g ^ (4 * ((t >> 1) & 1))) * 8);
+#pragma unroll
+    for (int grp = 0; grp < G; grp++) {
+        const uint32_t off = (uint32_t)((grp ^ (t & 1)) * 64);
+        r.va[grp] = lds64(c0 + off);
+        r.vb[grp] = lds64(c0 + 8u * D + off);
+        r.vs0[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t) * 2u);
+        r.vs1[grp] = lds32(vsc + (uint32_t)(grp * 16 + 2 * t + 8) * 2u);
+    }
+}
+
+template <int D, bool BF16>
+__device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&qf)[1][D / 16][2], float (&o)[1][D / 16][4],
+                                          float (&m)[1][2], float (&l)[1][2], int kpos0, const int (&qpos)[1][2],
+                                          int window, float scale_log2, bool need_mask, int lane, int dbg = 0) {
+    constexpr int G = D / 32;
+    const int g = lane >> 2;
+    const uint2 (&kx)[G] = r.kx; const uint2 (&ky)[G] = r.ky; const uint2 (&va)[G] = r.va; const uint2 (&vb)[G] = r.vb;
+    const uint32_t (&ks0)[G / 2] = r.ks0; const uint32_t (&ks1)[G / 2] = r.ks1;
+    const uint32_t (&vs0)[G] = r.vs0; const uint32_t (&vs1)[G] = r.vs1;
     // ---- S^T = sum over groups of scale_K[token][grp] * (Kq . Q^T)
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     if (!(dbg & 32))  // measurement only: skip the score phase
@@ -812,6 +824,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     bool failed = false;
     int seg = first_seg, pb = u0, k = 0;
     bool first_tile = true;
+    long long dbg_wait = 0, dbg_t0 = (a.debug & 4) ? clock64() : 0;  // measurement only
+    int dbg_tiles = 0;
 #pragma unroll 1
     while (pb < u1) {
         const int pe = min(u1, cur.se);
@@ -833,10 +847,12 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         for (int u = pb + (cw - n0 % C + C) % C; u < pe; u += C) {
             const int n = u - u0, st = n % NS;  // n % C == cw
             const uint32_t stage = ring + st * UNIT;
+            const long long tw0 = (a.debug & 4) ? clock64() : 0;
             if (!failed && !mbar_wait_bounded(full0 + st * 8, (n / NS) & 1)) {
                 failed = true;
                 if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             }
+            if (a.debug & 4) { dbg_wait += clock64() - tw0; dbg_tiles++; }
             if (first_tile && tid == 32) { stamp(a, 4); first_tile = false; }
             const int lp = cur.page_lo + (u - cur.sb);
             if (!failed && !(a.debug & 1)) {
@@ -860,8 +876,15 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     __syncwarp();
                 }
                 const bool need_mask = (lp * 16 + 15 > cur.q_pos) || (a.window > 0 && lp * 16 + a.window <= cur.q_pos);
-                if constexpr (Q8) attend_tile_q8<D, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane, a.debug);
-                else attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+                if constexpr (Q8) {
+                    Q8Tile<D> regs;
+                    q8_load<D>(stage, lane, regs);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + st * 8);  // the tile is in registers: the stage may be refilled
+                    q8_attend<D, BF16>(regs, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane, a.debug);
+                    continue;
+                }
+                attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + st * 8);  // the stage may be refilled
@@ -910,6 +933,11 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
 #pragma unroll
             for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
         }
+    }
+    if ((a.debug & 4) && a.dbg_buf && tid == 32) {  // measurement only: consumer 0's cycles waiting for tiles / in total / tiles
+        a.dbg_buf[(size_t)blockIdx.x * 16 + 13] = (unsigned long long)dbg_wait;
+        a.dbg_buf[(size_t)blockIdx.x * 16 + 14] = (unsigned long long)(clock64() - dbg_t0);
+        a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = (unsigned long long)dbg_tiles;
     }
     // idle now: help merge the segments whose last ticket this CTA drew
     consumer_sync((C + 1) * 32);
