@@ -518,7 +518,7 @@ def main():
                     help="cfg2 is the headline workload; cfg3 (windows, d=256) and cfg5 (shared prefix, long tails) on request")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")
     ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
-    ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8)")
+    ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8, 12)")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quantize-kv", action="store_true", help="int8 KV pages (the reference's CacheConfig::quantize_kv)")

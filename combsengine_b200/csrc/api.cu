@@ -1088,7 +1088,7 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
                                int32_t max_ctas, int32_t overlap_launches) {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || ctas_per_sm < 0 || ctas_per_sm > 8 || stages < 0 || stages > 64 || max_ctas < 0 ||
-        !(consumers == 0 || consumers == 4 || consumers == 6 || consumers == 8)) {
+        !(consumers == 0 || consumers == 4 || consumers == 6 || consumers == 8 || consumers == 12)) {
         set_error("bad argument"); return CBKV_ERR_ARG;
     }
     int32_t rc = ensure_device(a);

@@ -391,8 +391,9 @@ __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&q
             o[0][mt][2] *= alpha[0]; o[0][mt][3] *= alpha[1];
         }
     }
-    const uint32_t pb0 = movmatrix_trans(pack2<BF16>(s[0], s[1]));  // tokens 2t, 2t+1 of column g
-    const uint32_t pb1 = movmatrix_trans(pack2<BF16>(s[2], s[3]));  // tokens 2t+8, 2t+9
+    uint32_t pb0 = pack2<BF16>(s[0], s[1]), pb1 = pack2<BF16>(s[2], s[3]);
+    pb0 = movmatrix_trans(pb0);  // tokens 2t, 2t+1 of column g
+    pb1 = movmatrix_trans(pb1);  // tokens 2t+8, 2t+9
     // ---- O^T += sum over groups of Vq^T . (P^T * scale_V[token][grp])
     if (!(dbg & 128))  // measurement only: skip the output phase
 #pragma unroll
@@ -660,6 +661,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         if (a.kv_dep) pdl_wait();
         bool failed = false;
         int issued_end = 0;
+        // this lane's stage and ring revolution, advanced by R per round (no division in the loop)
+        int p_st = lane % NS, p_rev = lane / NS;
 #pragma unroll 1
         for (int base = 0; base < ntiles && !failed; base += R) {
             if (base > 0 && base % ROWS_CAP == 0) {  // long ranges: next batch of rows (all tiles before `base` are issued)
@@ -669,9 +672,9 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             }
             const int n = base + lane;
             if (lane < R && n < ntiles) {
-                const int st = n % NS;
+                const int st = p_st;
                 const int row0 = rows[n % ROWS_CAP];
-                if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, ((n / NS) - 1) & 1)) failed = true;
+                if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, (p_rev - 1) & 1)) failed = true;
                 if (!failed && Q8) {
                     mbar_expect_tx(full0 + st * 8, UNIT);  // one box of UNIT/128 rows x 128 bytes = one record
                     tma_load_2d(ring + st * UNIT, &tmap, 0, row0 * (int)(UNIT / 128u), full0 + st * 8);
@@ -684,6 +687,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     }
                 }
             }
+            p_st += R;
+            if (p_st >= NS) { p_st -= NS; p_rev++; }  // R <= NS
             failed = __any_sync(0xffffffffu, failed);
             if (!failed) issued_end = min(ntiles, base + R);
             if (base == 0 && lane == 0) stamp(a, 2);
@@ -843,12 +848,15 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         const int qpos[1][2] = {{cur.q_pos, cur.q_pos}};
 
         const int n0 = pb - u0;
+        const int u_first = pb + (cw - n0 % C + C) % C;
+        // stage and revolution parity of this warp's tiles, advanced by C per tile (NS is a multiple of C)
+        int st = (u_first - u0) % NS, par = ((u_first - u0) / NS) & 1;
 #pragma unroll 1
-        for (int u = pb + (cw - n0 % C + C) % C; u < pe; u += C) {
-            const int n = u - u0, st = n % NS;  // n % C == cw
+        for (int u = u_first; u < pe; u += C, st += C) {
+            if (st >= NS) { st -= NS; par ^= 1; }
             const uint32_t stage = ring + st * UNIT;
             const long long tw0 = (a.debug & 4) ? clock64() : 0;
-            if (!failed && !mbar_wait_bounded(full0 + st * 8, (n / NS) & 1)) {
+            if (!failed && !mbar_wait_bounded(full0 + st * 8, par)) {
                 failed = true;
                 if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             }
@@ -1185,7 +1193,8 @@ DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int co
         case 256: c = DecodeCfg<256>::C; ctas = DecodeCfg<256>::CTAS; break;
         default: return {0, 0, 0, 0, 0, 0};
     }
-    if (consumers == 4 || consumers == 6 || consumers == 8) c = consumers;
+    if (q8 && d <= 128) c = 8;  // int8 tiles cost more instructions per byte: two consumer warps per scheduler
+    if (consumers == 4 || consumers == 6 || consumers == 8 || (consumers == 12 && d <= 128)) c = consumers;  // 12 warps of head_dim 256 spill
     if (ctas_per_sm > 0) ctas = ctas_per_sm;
     const int comb_cols = std::min(8, (n_rep + 1) & ~1);
     const int budget = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
@@ -1219,6 +1228,10 @@ template <int D, bool BF16> static cudaError_t set_attrs() {
     e = cudaFuncSetAttribute(decode_kernel<D, 6, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(decode_kernel<D, 8, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 12, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_kernel<D, 12, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(chunk_kernel<D, ChunkCfg<D>::NT, ChunkCfg<D>::W, ChunkCfg<D>::S, BF16>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_smem<D>());
@@ -1265,6 +1278,7 @@ static cudaError_t launch_decode_c(const CUtensorMap& map, const DecodeArgs& a, 
         case 4: return launch_decode_t<D, 4, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
         case 6: return launch_decode_t<D, 6, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
         case 8: return launch_decode_t<D, 8, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
+        case 12: return launch_decode_t<D, 12, BF16, Q8>(map, a, n_ctas, smem, pdl, st);
         default: return cudaErrorInvalidValue;
     }
 }

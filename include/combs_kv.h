@@ -307,7 +307,7 @@ int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on);
 int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches);
 /* Tuning knobs for measurements and tests (0 = built-in default): CTAs per SM of the
  * decode kernel, stages of its TMA ring (rounded down to a multiple of the consumer
- * count), consumer warps per CTA (4, 6 or 8), an upper bound on the CTAs launched,
+ * count), consumer warps per CTA (4, 6, 8 or 12), an upper bound on the CTAs launched,
  * and whether consecutive decode launches may overlap (programmatic dependent
  * launch; 1 = default). */
 int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
