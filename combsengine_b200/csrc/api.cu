@@ -622,7 +622,7 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
     DeviceState* d = dev_of(a);
     CU_TRY(cudaSetDevice(d->device));
     if ((rc = materialize(a, layer, st))) return rc;
-    if (d->fast && a->step_is_decode && !d->layers[(size_t)layer].quant)
+    if (d->fast && a->step_is_decode && !(d->layers[(size_t)layer].quant && (debug_flags() & 16)))
         return run_attention(a, layer, q, k, v, out, scale, window, st);  // the append rides inside the decode kernel
     if ((rc = run_append(a, layer, k, v, st))) return rc;
     return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);

@@ -411,6 +411,62 @@ __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&q
     }
 }
 
+// Fused append for int8 pages: kv_quantize (kv.rs:284-313) of the step's new K and V rows of one
+// (sequence, kv head), written into the tile that was just fetched and into its record in HBM.
+// Lane c owns values 4c..4c+3 (a 32-value group = 8 lanes); head_dim <= 128 per round.
+template <int D, bool BF16>
+__device__ __forceinline__ void q8_append_row(uint32_t stage, uint8_t* recp, const uint16_t* krow, const uint16_t* vrow,
+                                              int slot, int lane) {
+#pragma unroll
+    for (int is_v = 0; is_v < 2; is_v++) {
+        const uint2* src = reinterpret_cast<const uint2*>(is_v ? vrow : krow);
+#pragma unroll
+        for (int c0 = 0; c0 < D / 4; c0 += 32) {
+            const int c = c0 + lane;
+            const bool live = c < D / 4;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live) {
+                const uint2 raw = src[c];
+                x[0] = from_elem<BF16>((uint16_t)(raw.x & 0xffff)); x[1] = from_elem<BF16>((uint16_t)(raw.x >> 16));
+                x[2] = from_elem<BF16>((uint16_t)(raw.y & 0xffff)); x[3] = from_elem<BF16>((uint16_t)(raw.y >> 16));
+            }
+            float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);
+            if (live) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float q = roundf(__fdiv_rn(x[i], scale));
+                    q = fminf(fmaxf(q, -127.f), 127.f);
+                    word |= (uint32_t)((int)q + 128) << (8 * i);
+                }
+                if (!is_v) {
+                    const uint32_t off = (uint32_t)qrec_value_off(0, slot, 4 * c, 16, D);
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(stage + off), "r"(word) : "memory");
+                    *reinterpret_cast<uint32_t*>(recp + off) = word;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t off = (uint32_t)qrec_value_off(1, slot, 4 * c + i, 16, D);
+                        const uint32_t b = (word >> (8 * i)) & 0xffu;
+                        asm volatile("st.shared.u8 [%0], %1;" ::"r"(stage + off), "r"(b) : "memory");
+                        recp[off] = (uint8_t)b;
+                    }
+                }
+                if ((c & 7) == 0) {
+                    const uint32_t off = (uint32_t)qrec_scale_off(is_v, slot, c >> 3, 16, D);
+                    const uint32_t sv = to_elem<BF16>(scale);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + off), "h"((uint16_t)sv) : "memory");
+                    *reinterpret_cast<uint16_t*>(recp + off) = (uint16_t)sv;
+                }
+            }
+        }
+    }
+}
+
 // Issue the TMA copies for one (page, kv head) tile: D/64 boxes of 32 rows x 64 elems.
 template <int D>
 __device__ __forceinline__ void issue_tile(const CUtensorMap* map, uint32_t stage, uint32_t bar, int row0) {
@@ -575,7 +631,7 @@ __device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int n
 }
 
 // Warp roles: 0 = producer, 1..C = consumers, C+1 = merger.
-// Q8: the layer holds int8 records; a tile is one record fetched as one box of a byte tensor map, no fused append.
+// Q8: the layer holds int8 records; a tile is one record fetched as one box of a byte tensor map.
 template <int D, int C, bool BF16, bool Q8>
 __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
     constexpr uint32_t UNIT = Q8 ? (uint32_t)(2 * 16 * D + 2 * 16 * (D / 32) * 2) : 32u * D * 2u;
@@ -885,6 +941,20 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 }
                 const bool need_mask = (lp * 16 + 15 > cur.q_pos) || (a.window > 0 && lp * 16 + a.window <= cur.q_pos);
                 if constexpr (Q8) {
+                    if (a.k_new != nullptr && lp == cur.page_last) {
+                        // fused append: quantise the new K/V row into the tile just fetched and into its record
+                        const int phys = a.step.tables[cur.tbl_off + lp];
+                        if (phys >= 0 && phys < a.geo.num_pages) {
+                            const size_t rowi = ((size_t)cur.tok_off * Hkv + cur.h) * D;
+                            q8_append_row<D, BF16>(stage, reinterpret_cast<uint8_t*>(a.arena) + ((size_t)phys * Hkv + cur.h) * UNIT,
+                                                   reinterpret_cast<const uint16_t*>(a.k_new) + rowi,
+                                                   reinterpret_cast<const uint16_t*>(a.v_new) + rowi, cur.q_pos & 15, lane);
+                        } else if (lane == 0) {
+                            atomicOr(a.status, ST_BAD_PAGE);
+                        }
+                        fence_proxy_async();  // the stage is refilled by the copy engine later
+                        __syncwarp();
+                    }
                     Q8Tile<D> regs;
                     q8_load<D>(stage, lane, regs);
                     __syncwarp();
@@ -1290,7 +1360,6 @@ static cudaError_t launch_decode_d(const CUtensorMap& map, const DecodeArgs& a, 
 
 cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_ctas, int consumers, int smem, bool pdl, bool bf16, cudaStream_t st, bool q8) {
     if (a.n_stages < consumers || a.n_stages % consumers != 0) return cudaErrorInvalidValue;
-    if (q8 && a.k_new != nullptr) return cudaErrorInvalidValue;  // no fused append into int8 records
     switch (a.geo.d) {
         case 64: return launch_decode_d<64>(map, a, n_ctas, consumers, smem, pdl, bf16, q8, st);
         case 128: return launch_decode_d<128>(map, a, n_ctas, consumers, smem, pdl, bf16, q8, st);
