@@ -714,11 +714,12 @@ int32_t cbkv_rope_destroy(cbkv_rope* rope) {
     return CBKV_OK;
 }
 
+// k_out non-null: rotated k goes to that dense buffer and nothing is written to pages (int8 layers,
+// whose append quantises afterwards).
 static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk_norm* norm, const void* q, const void* k,
-                               const void* v, void* q_out, cudaStream_t st) {
+                               const void* v, void* q_out, void* k_out, cudaStream_t st) {
     DeviceState* d = dev_of(a);
     if (r->arena != a) { set_error("rope tables belong to another arena"); return CBKV_ERR_ARG; }
-    if (d->layers[(size_t)layer].quant) { set_error("the fused rotation does not write int8 pages: rotate, then cbkv_attention"); return CBKV_ERR_ARG; }
     for (const SeqMeta& m : a->step_meta)
         if ((int64_t)m.pos + m.snew > r->max_position) {
             set_error("rope table shorter than the step's positions: " + std::to_string((int64_t)m.pos + m.snew) + " > " +
@@ -727,7 +728,7 @@ static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk
         }
     RopeArgs args{};
     args.step = d->step; args.geo = geom(a);
-    args.q = q; args.k = k; args.v = v; args.q_out = q_out;
+    args.q = q; args.k = k; args.v = v; args.q_out = q_out; args.k_out = k_out;
     args.arena = d->layers[(size_t)layer].base;
     args.table = r->table; args.max_position = r->max_position;
     args.q_weight = norm ? norm->q_weight : nullptr;
@@ -737,7 +738,20 @@ static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk
     args.status = d->status;
     CU_TRY(launch_rope_append(args, a->cfg.dtype == CBKV_BF16, st));
     g_launches++;
-    d->last_kv_writer = layer;
+    if (!k_out) d->last_kv_writer = layer;
+    return CBKV_OK;
+}
+
+// Scratch for the rotated q (and, for int8 layers, the rotated k) of the current layer.
+static int32_t rope_scratch(Arena* a, cudaStream_t st, size_t bytes) {
+    DeviceState* d = dev_of(a);
+    if (bytes <= d->qrot_cap) return CBKV_OK;
+    CU_TRY(cudaStreamSynchronize(st));  // an earlier layer may still read the old buffer
+    if (d->qrot) cudaFree(d->qrot);
+    d->qrot = nullptr;
+    d->qrot_cap = 0;
+    CU_TRY(cudaMalloc(&d->qrot, bytes * 2));
+    d->qrot_cap = bytes * 2;
     return CBKV_OK;
 }
 
@@ -751,7 +765,14 @@ int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CU_TRY(cudaSetDevice(dev_of(a)->device));
     if ((rc = materialize(a, layer, st))) return rc;
-    return run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, q_out, st);
+    DeviceState* d = dev_of(a);
+    if (d->layers[(size_t)layer].quant) {  // rotate k to scratch, then the quantising append (kv.rs:746-768)
+        const size_t kb = ((size_t)a->step_tokens * a->cfg.n_kv_heads * a->cfg.head_dim * 2 + 255) & ~(size_t)255;
+        if ((rc = rope_scratch(a, st, kb))) return rc;
+        if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, q_out, d->qrot, st))) return rc;
+        return run_append(a, layer, d->qrot, v, st);
+    }
+    return run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, q_out, nullptr, st);
 }
 
 int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
@@ -766,16 +787,19 @@ int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* r
     DeviceState* d = dev_of(a);
     CU_TRY(cudaSetDevice(d->device));
     if ((rc = materialize(a, layer, st))) return rc;
-    const size_t qb = (size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2;
-    if (qb > d->qrot_cap) {
-        CU_TRY(cudaStreamSynchronize(st));  // an earlier layer may still read the old buffer
-        if (d->qrot) cudaFree(d->qrot);
-        d->qrot = nullptr;
-        d->qrot_cap = 0;
-        CU_TRY(cudaMalloc(&d->qrot, qb * 2));
-        d->qrot_cap = qb * 2;
+    const size_t qb = ((size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2 + 255) & ~(size_t)255;
+    const size_t kb = ((size_t)a->step_tokens * a->cfg.n_kv_heads * a->cfg.head_dim * 2 + 255) & ~(size_t)255;
+    const bool quant = d->layers[(size_t)layer].quant;
+    if ((rc = rope_scratch(a, st, qb + (quant ? kb : 0)))) return rc;
+    if (quant) {  // int8 pages: rotate q and k to scratch; the append (fused into the decode kernel when it can be) quantises
+        uint8_t* krot = d->qrot + qb;
+        if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, d->qrot, krot, st))) return rc;
+        if (d->fast && a->step_is_decode && !(debug_flags() & 16))
+            return run_attention(a, layer, d->qrot, krot, v, out, scale, window, st);
+        if ((rc = run_append(a, layer, krot, v, st))) return rc;
+        return run_attention(a, layer, d->qrot, nullptr, nullptr, out, scale, window, st);
     }
-    if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, d->qrot, st))) return rc;
+    if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, d->qrot, nullptr, st))) return rc;
     return run_attention(a, layer, d->qrot, nullptr, nullptr, out, scale, window, st);
 }
 

@@ -152,6 +152,7 @@ struct RopeArgs {
     const void* k;
     const void* v;
     void* q_out;
+    void* k_out;   // non-null: rotated k goes here (dense, same layout as k) and v is left alone; `arena` is unused
     void* arena;
     const void* table;
     int64_t max_position;

@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int d = a.geo.d, half = d >> 1, chunks = half >> 1;  // a chunk = 2 elements = 4 bytes
     const int64_t q_rows = (int64_t)a.step.n_tokens * a.geo.n_q, kv_rows = (int64_t)a.step.n_tokens * a.geo.n_kv;
-    const int64_t total = q_rows + 2 * kv_rows;
+    const int64_t total = q_rows + (a.k_out ? 1 : 2) * kv_rows;
     for (int64_t R = warp0; R < total; R += nwarps) {
         const int kind = R < q_rows ? 0 : (R < q_rows + kv_rows ? 1 : 2);  // 0 = q, 1 = k, 2 = v
         const int64_t row = kind == 0 ? R : (kind == 1 ? R - q_rows : R - q_rows - kv_rows);
@@ -178,6 +178,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeArgs a) {
         uint32_t* dst;
         if (kind == 0) {
             dst = reinterpret_cast<uint32_t*>(a.q_out) + row * (d >> 1);
+        } else if (a.k_out) {
+            dst = reinterpret_cast<uint32_t*>(a.k_out) + row * (d >> 1);
         } else {
             int phys = a.step.tables[sm.tbl_off + gpos / a.geo.page_size];  // kv.rs:728
             if (phys < 0 || phys >= a.geo.num_pages) { if (lane == 0) atomicOr(a.status, ST_BAD_PAGE); continue; }
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(256) rope_append_vec_kernel(const RopeArgs a) 
     // row counts fit 32 bits (the launcher checks)
     const uint32_t warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
     const uint32_t q_rows = (uint32_t)a.step.n_tokens * a.geo.n_q, kv_rows = (uint32_t)a.step.n_tokens * a.geo.n_kv;
-    const uint32_t total = q_rows + 2 * kv_rows;
+    const uint32_t total = q_rows + (a.k_out ? 1u : 2u) * kv_rows;
     for (uint32_t R0 = warp0 * RPW; R0 < total; R0 += nwarps * RPW) {
         const uint32_t R = R0 + sub;
         const bool live = R < total;
@@ -290,6 +292,8 @@ __global__ void __launch_bounds__(256) rope_append_vec_kernel(const RopeArgs a) 
         bool ok = live;
         if (kind == 0) {
             dst = reinterpret_cast<uint4*>(a.q_out) + (size_t)row * (2 * T);
+        } else if (a.k_out) {
+            dst = reinterpret_cast<uint4*>(a.k_out) + (size_t)row * (2 * T);
         } else {
             int phys = a.step.tables[sm.tbl_off + gpos / a.geo.page_size];
             if (phys < 0 || phys >= a.geo.num_pages) { if (live && t == 0) atomicOr(a.status, ST_BAD_PAGE); phys = 0; ok = false; }
@@ -350,7 +354,7 @@ static cudaError_t launch_rope_t(const RopeArgs& a, int64_t rows, cudaStream_t s
 }
 
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, cudaStream_t st) {
-    const int64_t rows = (int64_t)a.step.n_tokens * (a.geo.n_q + 2 * a.geo.n_kv);
+    const int64_t rows = (int64_t)a.step.n_tokens * (a.geo.n_q + (a.k_out ? 1 : 2) * a.geo.n_kv);
     if (rows <= 0) return cudaSuccess;
     return bf16 ? launch_rope_t<true>(a, rows, st) : launch_rope_t<false>(a, rows, st);
 }

@@ -78,11 +78,11 @@ def _oracle_prepare(q, k, pos, cos, sin, norm):
 
 
 def _run_case(n_q, n_kv, d, steps, theta=10000.0, scaling=None, norm=None, window=None, seed=0, n_seqs=2,
-              pages_exact=True, max_len=256):
+              pages_exact=True, max_len=256, quantize=False):
     rng = np.random.default_rng(seed)
     npages = n_seqs * ((max_len + 15) // 16)
-    g = KVArena(1, n_q, n_kv, d, max_len, num_pages=npages)
-    o = OracleArena(1, n_kv, d, max_len, num_pages=npages, rolling=False, dtype="f16")
+    g = KVArena(1, n_q, n_kv, d, max_len, num_pages=npages, quantize_kv=quantize)
+    o = OracleArena(1, n_kv, d, max_len, num_pages=npages, rolling=False, dtype="f16", quantize_kv=quantize)
     perm = rng.permutation(npages)
     g.set_free_list(perm); o.set_free_list(perm)
     gs = [g.new_seq() for _ in range(n_seqs)]
@@ -114,6 +114,10 @@ def _run_case(n_q, n_kv, d, steps, theta=10000.0, scaling=None, norm=None, windo
     for b in range(n_seqs):
         assert list(gs[b].block_table()) == list(os_[b].block_table())
         for page in gs[b].block_table():
+            if quantize:  # rotated k, then kv_quantize: packed words and scales bit for bit
+                for x, y in zip(g.export_page_quant(0, int(page)), o.page_quant(0, int(page))):
+                    assert np.array_equal(x, y if y.dtype == np.int32 else y.view(np.uint16))
+                continue
             gk, gv = g.export_page(0, int(page))
             ok, ov = o.page(0, int(page))
             assert np.array_equal(gv, ov.view(np.uint16)), "V pages are a bit copy"
@@ -171,3 +175,9 @@ def test_rotate_and_append_alone_is_bit_exact_and_may_run_in_place():
     zk = torch.zeros(56 * n_kv * d, dtype=torch.float16, device="cuda")
     with pytest.raises(CbkvError, match="rope table shorter"):
         R.rope_append(g, 0, small, z, zk, zk)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_q,n_kv,d", [(28, 4, 128), (8, 4, 64)])
+def test_rotation_into_int8_pages(n_q, n_kv, d):
+    _run_case(n_q, n_kv, d, [(70, 33), (1, 1), (1, 1), (5, 1), (1, 1)], seed=3 * d, quantize=True)
