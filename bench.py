@@ -136,7 +136,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU port (oracle) timing
-def time_cpu_port(n_seqs: int, n_layers: int, budget_s: float, lens: np.ndarray) -> dict:
+def time_cpu_port(n_seqs: int, n_layers: int, limit_s: float, lens: np.ndarray) -> dict:
     """The oracle's batch driver (a port of the reference algorithm: per-page scatter,
     materialised gather, repeat_kv, f32 upcast, scores, softmax, P.V) on host cores."""
     import oracle
@@ -165,7 +165,7 @@ def time_cpu_port(n_seqs: int, n_layers: int, budget_s: float, lens: np.ndarray)
             arena.batch_layer(seqs, ones, layer, q, k, v, N_Q, SCALE)
         steps += 1
         el = time.perf_counter() - t0
-        if el >= budget_s or steps >= 64:
+        if el >= limit_s or steps >= 64:
             break
     # a token = one sequence advanced through all 28 layers
     value = n_seqs * steps * (n_layers / LAYERS) / el
@@ -178,8 +178,8 @@ def run_reference(args, rank: int, world: int) -> None:
         return
     lens = context_lengths(0)
     # every "step" is a bounded sample: all 32 sequences, 2 of the 28 layers
-    total_budget = 8.0 * max(1, args.steps + args.warmup)
-    res = time_cpu_port(BATCH, 2, min(90.0, total_budget), lens)
+    total_limit = 8.0 * max(1, args.steps + args.warmup)
+    res = time_cpu_port(BATCH, 2, min(90.0, total_limit), lens)
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": BATCH / res["value"] * 1e3,

@@ -1267,13 +1267,13 @@ DecodeConfig decode_config(int d, int n_rep, int ctas_per_sm, int stages, int co
     if (consumers == 4 || consumers == 6 || consumers == 8 || (consumers == 12 && d <= 128)) c = consumers;  // 12 warps of head_dim 256 spill
     if (ctas_per_sm > 0) ctas = ctas_per_sm;
     const int comb_cols = std::min(8, (n_rep + 1) & ~1);
-    const int budget = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
+    const int smem_limit = std::min(227 * 1024, (228 * 1024) / ctas - 1024);
     if (stages <= 0) {
         stages = 8 * c;
-        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols, 1, q8) > budget) stages -= c;
+        while (stages > c && decode_smem_bytes(d, c, stages, comb_cols, 1, q8) > smem_limit) stages -= c;
     }
     stages = std::max(c, (stages / c) * c);
-    const int bufs = decode_smem_bytes(d, c, stages, comb_cols, 2, q8) <= budget ? 2 : 1;
+    const int bufs = decode_smem_bytes(d, c, stages, comb_cols, 2, q8) <= smem_limit ? 2 : 1;
     return {c, stages, decode_smem_bytes(d, c, stages, comb_cols, bufs, q8), ctas, comb_cols, bufs};
 }
 ChunkConfig chunk_config(int d) {

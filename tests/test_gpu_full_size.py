@@ -156,3 +156,92 @@ def test_cfg5_shared_prefix_long_tails_and_churn():
     top = int(w.arena.free_list()[-1])
     w.arena.begin_step([w.seqs[victims[0]]], [1])  # the next append reuses the most recently freed page
     assert int(w.seqs[victims[0]].block_table()[-1]) == top
+
+
+def test_cfg2_int8_pages_hold_the_half_step_bound_and_decode_tracks_float64():
+    """Benchmark geometry and lengths with quantize_kv: every exported page de-quantises to within
+    half a step of what was appended (kv.rs:926-953), and a decode step over the int8 records matches
+    a float64 attention computed from those de-quantised pages."""
+    n_q, n_kv, d = 28, 4, 128
+    rng = np.random.default_rng(0xC0B50002)
+    lens = rng.integers(1024, 4097, 32)
+    pages = 8192
+    arena = KVArena(1, n_q, n_kv, d, 4200, 16, pages, quantize_kv=True)
+    arena.set_free_list(rng.permutation(pages))
+    seqs = [arena.new_seq() for _ in lens]
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    ntok = int(lens.sum())
+    kf = torch.randn(ntok * n_kv * d, device="cuda", generator=gen).half()
+    vf = torch.randn(ntok * n_kv * d, device="cuda", generator=gen).half()
+    arena.begin_step(seqs, [int(x) for x in lens])
+    arena.append(0, kf, vf)
+    one = [1] * len(lens)
+    q = torch.randn(len(lens) * n_q * d, device="cuda", generator=gen).half()
+    k1 = torch.randn(len(lens) * n_kv * d, device="cuda", generator=gen).half()
+    v1 = torch.randn(len(lens) * n_kv * d, device="cuda", generator=gen).half()
+    arena.begin_step(seqs, one)
+    out = arena.attention(0, q, k1, v1, d ** -0.5).cpu().numpy().reshape(len(lens), n_q, d)
+    assert arena.device_status() == 0
+    kh, vh = kf.cpu().numpy(), vf.cpu().numpy()
+    off = 0
+    for b, L in enumerate(lens):
+        L = int(L)
+        if b in (0, 7, 31):  # three sequences in full
+            kb = kh[off:off + L * n_kv * d].reshape(n_kv, L, d)
+            vb = vh[off:off + L * n_kv * d].reshape(n_kv, L, d)
+            K = np.zeros((n_kv, L + 1, d), np.float32)
+            V = np.zeros_like(K)
+            for lp, pg in enumerate(seqs[b].block_table()):
+                kp, ks, vp, vs = arena.export_page_quant(0, int(pg))
+                n = min(16, L + 1 - lp * 16)
+                for packed, scales, dst in ((kp, ks, K), (vp, vs, V)):
+                    by = packed.view(np.uint8).reshape(n_kv, 16, d).astype(np.int32)
+                    qv = np.where(np.arange(d) % 4 == 3, by.astype(np.int8).astype(np.int32), by - 128)   # kv.rs:326-346
+                    sc = np.repeat(scales.view(np.float16).astype(np.float32), 32, axis=-1)
+                    dst[:, lp * 16:lp * 16 + n] = (qv * sc).astype(np.float16).astype(np.float32)[:, :n]
+            for src, dq in ((kb, K), (vb, V)):
+                groups = src.astype(np.float32).reshape(n_kv, L, d // 32, 32)
+                err = np.abs(groups - dq[:, :L].reshape(n_kv, L, d // 32, 32)).max(-1)
+                # half a step (kv.rs:940) plus what f16 storage adds: the scale and the product q * scale are each rounded to 11 bits
+                bound = np.abs(groups).max(-1) * (1.0 / 254.0 + 2.0 ** -10) + 1e-4
+                assert np.all(err <= bound)
+            qb = q.cpu().numpy().reshape(len(lens), n_q, d)[b].astype(np.float64)
+            for h in range(n_kv):
+                ref = attend_f64(qb[h * 7:(h + 1) * 7], K[h], V[h], d ** -0.5)
+                assert_attention_close(out[b, h * 7:(h + 1) * 7], ref.astype(np.float32), f"seq {b} kv head {h}")
+        off += L * n_kv * d
+    assert arena.num_free_pages() == pages - sum((int(L) + 1 + 15) // 16 for L in lens)
+
+
+def test_cfg4_chunk_rotation_preserves_norms_and_is_linear():
+    """One 512-token chunk of the cfg4 prompts through the rotate-and-append kernel: a rotation keeps
+    the norm of every (i, i + d/2) pair, position 0 is the identity, and rope(a) + rope(b) = rope(a + b)
+    up to storage rounding."""
+    from combsengine_b200 import rope as R
+    n_q, n_kv, d, batch, chunk = 32, 8, 128, 8, 512
+    arena = KVArena(1, n_q, n_kv, d, 2 * chunk, 16, batch * (2 * chunk // 16))
+    seqs = [arena.new_seq() for _ in range(batch)]
+    rope = R.RotaryEmbedding(arena, 500000.0, 2 * chunk)
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    ntok = batch * chunk
+    mk = lambda heads: torch.randn(ntok * heads * d, device="cuda", generator=gen).half()
+    qa, qb, k, v = mk(n_q), mk(n_q), mk(n_kv), mk(n_kv)
+    arena.begin_step(seqs, [chunk] * batch)                       # positions 0..511
+    ra0 = R.rope_append(arena, 0, rope, qa, k, v).float().view(batch, n_q, chunk, d)
+    assert torch.equal(ra0[:, :, 0], qa.float().view(batch, n_q, chunk, d)[:, :, 0])          # position 0: identity
+    arena.begin_step(seqs, [chunk] * batch)                       # positions 512..1023
+    ra = R.rope_append(arena, 0, rope, qa, k, v).float().view(batch, n_q, chunk, d)
+    rb = R.rope_append(arena, 0, rope, qb, k, v).float().view(batch, n_q, chunk, d)
+    rab = R.rope_append(arena, 0, rope, (qa.float() + qb.float()).half(), k, v).float().view(batch, n_q, chunk, d)
+    x = qa.float().view(batch, n_q, chunk, d)
+    pair = lambda t: t[..., : d // 2] ** 2 + t[..., d // 2:] ** 2
+    assert torch.allclose(pair(ra), pair(x), rtol=6e-3, atol=6e-3)
+    assert torch.allclose(ra + rb, rab, rtol=0, atol=2e-2)
+    assert arena.device_status() == 0
+    # v is a bit copy into the page slots of positions 512 + 80 .. 512 + 95 of sequence 3
+    pg = int(seqs[3].block_table()[chunk // 16 + 5])
+    gk, gv = arena.export_page(0, pg)
+    assert np.array_equal(gv, v.view(batch, n_kv, chunk, d)[3, :, 80:96].cpu().numpy().view(np.uint16))
+    kr = gk.view(np.float16).astype(np.float32)
+    kx = k.view(batch, n_kv, chunk, d)[3, :, 80:96].float().cpu().numpy()
+    assert np.allclose(kr[..., : d // 2] ** 2 + kr[..., d // 2:] ** 2, kx[..., : d // 2] ** 2 + kx[..., d // 2:] ** 2, rtol=6e-3, atol=6e-3)
