@@ -383,7 +383,8 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         layers = args.layers
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    arena = KVArena(layers, n_q, n_kv, d, prompt + 64, 16, batch * (prompt // 16 + 4), device=local_rank)
+    arena = KVArena(layers, n_q, n_kv, d, prompt + 64, 16, batch * (prompt // 16 + 4), device=local_rank,
+                    quantize_kv=bool(args.quantize_kv))
     arena.set_free_list(np.random.default_rng(0xC0B50004).permutation(arena.num_pages))
     if args.chunk_kernel:
         arena.set_chunk_kernel(args.chunk_kernel)
@@ -427,7 +428,8 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         "n_gpus": 1, "steps": passes, "warmup": max(1, args.warmup // 8), "ms_per_step": ms, "higher_is_better": True,
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"cfg4 llama-3-8b geometry chunked prefill: {layers} layers, 32/8/128, 8 prompts x 8192 in 512-token "
-                               "chunks, append + causal attention over paged prefix + chunk",
+                               "chunks, append + causal attention over paged prefix + chunk"
+                               + (", int8 KV pages (de-quantised per step into a float scratch layer)" if args.quantize_kv else ""),
                    "chunk_kernel": {0: "auto (tcgen05, two query tiles per CTA)", 1: "mma.sync", 2: "tcgen05, one query tile per CTA", 3: "tcgen05, two query tiles per CTA"}[args.chunk_kernel]},
         "roofline": {"bound": "tensor", "achieved": tfl, "peak": peak, "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None,
                      "algorithmic_flops_per_pass": flops},

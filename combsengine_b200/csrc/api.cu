@@ -96,6 +96,8 @@ struct DeviceState {
     // host-buffer entry point staging
     uint8_t* io = nullptr;
     size_t io_cap = 0;
+    // one float layer that int8 layers are de-quantised into for the tensor-core chunk kernels
+    LayerArena qscratch;
     // rotated q of the current layer (cbkv_attention_rope)
     uint8_t* qrot = nullptr;
     size_t qrot_cap = 0;
@@ -182,6 +184,8 @@ int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D
     return CBKV_OK;
 }
 
+int32_t alloc_float_layer(Arena* a, LayerArena* Lp, cudaStream_t st);
+
 // Arenas appear on a layer's first write, zero-filled (kv.rs:695-713).
 int32_t materialize(Arena* a, int layer, cudaStream_t st) {
     DeviceState* d = dev_of(a);
@@ -208,6 +212,12 @@ int32_t materialize(Arena* a, int layer, cudaStream_t st) {
         }
         return CBKV_OK;
     }
+    return alloc_float_layer(a, &L, st);
+}
+
+int32_t alloc_float_layer(Arena* a, LayerArena* Lp, cudaStream_t st) {
+    DeviceState* d = dev_of(a);
+    LayerArena& L = *Lp;
     CU_TRY(cudaMalloc(&L.base, d->layer_bytes));
     CU_TRY(cudaMemsetAsync(L.base, 0, d->layer_bytes, st));
     if (d->fast) {
@@ -434,7 +444,19 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     const float scale_log2 = (float)(scale * 1.4426950408889634);
     // int8 pages: decode steps stream the records through the decode kernel; everything else (chunks,
     // shapes outside the fast path) de-quantises on the fly in the generic kernel
-    if (L.quant && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
+    LayerArena* KV = &L;  // where the chunk kernels read K/V from
+    if (L.quant && d->fast && !a->step_is_decode && !(debug_flags() & 16)) {
+        // chunks over an int8 layer: de-quantise the pages of the step's sequences into the scratch layer
+        // (kv_dequantize, kv.rs:771-780) and run the float chunk kernels over that
+        if (!d->qscratch.base) {
+            int32_t rc = alloc_float_layer(a, &d->qscratch, st);
+            if (rc) return rc;
+        }
+        GeomDev g = geom(a);
+        CU_TRY(launch_dequant_pages(d->step.tables, (int)a->step_tables.size(), g, L.base, d->qscratch.base, d->status, bf16, st));
+        g_launches++;
+        KV = &d->qscratch;
+    } else if (L.quant && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
         GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
         ProfScope ps(d, st);
         CU_TRY(launch_generic_quant(args, bf16, st));
@@ -487,8 +509,8 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
             if (d->tile_host.n_items <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
         }
         ProfScope ps(d, st);
-        if (use_tc2) CU_TRY(launch_chunk_tc2(L.map_kv, args, bf16, st));
-        else CU_TRY(launch_chunk_tc(L.map_k16, L.map_kv, args, bf16, st));
+        if (use_tc2) CU_TRY(launch_chunk_tc2(KV->map_kv, args, bf16, st));
+        else CU_TRY(launch_chunk_tc(KV->map_k16, KV->map_kv, args, bf16, st));
         g_launches++;
         d->last_kv_writer = -1;
         return CBKV_OK;
@@ -498,7 +520,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         if (rc) return rc;
         ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2, 0, nullptr};
         ProfScope ps(d, st);
-        CU_TRY(launch_chunk(L.map_kv, args, bf16, st));
+        CU_TRY(launch_chunk(KV->map_kv, args, bf16, st));
         g_launches++;
         return CBKV_OK;
     }
@@ -536,6 +558,7 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
         if (d->status) cudaFree(d->status);
         if (d->io) cudaFree(d->io);
         if (d->qrot) cudaFree(d->qrot);
+        if (d->qscratch.base) cudaFree(d->qscratch.base);
         for (auto& sl : d->io_slots) {
             if (sl.dev) cudaFree(sl.dev);
             if (sl.in_done) { cudaEventDestroy(sl.in_done); cudaEventDestroy(sl.k_done); cudaEventDestroy(sl.out_done); }

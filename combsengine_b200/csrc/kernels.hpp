@@ -176,6 +176,8 @@ cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, 
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_init_quant(void* arena, size_t n_records, int page_size, int d, cudaStream_t st);
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);
+cudaError_t launch_dequant_pages(const int32_t* tables, int n_entries, const GeomDev& geo, const void* arena, void* scratch,
+                                 int32_t* status, bool bf16, cudaStream_t st);
 cudaError_t launch_generic_quant(const GenericArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_rope_append(const RopeArgs& a, bool bf16, cudaStream_t st);
 // host side of the rotary tables (rope.cu): frequencies, then [max_position][head_dim] f32 tables

@@ -107,6 +107,40 @@ __global__ void init_quant_kernel(uint8_t* arena, size_t n_records, int P, int d
     }
 }
 
+// kv_dequantize (kv.rs:319-358) of every page the step's sequences hold, into a float layer in the tiled
+// row order, so that the tensor-core chunk kernels can run over an int8 layer.  One warp per
+// (block-table entry, kv head): value = elem(q * scale), exactly what the reference's gather produces.
+template <bool BF16>
+__global__ void __launch_bounds__(256) dequant_pages_kernel(const int32_t* tables, int n_entries, GeomDev geo, const uint8_t* arena,
+                                                            uint16_t* scratch, int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int D = geo.d, P = geo.page_size, Hkv = geo.n_kv;
+    const size_t rec = qrec_bytes(P, D);
+    for (int64_t it = warp0; it < (int64_t)n_entries * Hkv; it += nwarps) {
+        const int e = (int)(it / Hkv), h = (int)(it - (int64_t)e * Hkv);
+        const int phys = tables[e];
+        if (phys < 0 || phys >= geo.num_pages) { if (lane == 0) atomicOr(status, ST_BAD_PAGE); continue; }
+        const uint8_t* recp = arena + ((size_t)phys * Hkv + h) * rec;
+        uint16_t* dst = scratch + ((size_t)phys * Hkv + h) * 2 * P * D;
+        for (int r = 0; r < 2 * P; r++) {
+            const int is_v = r >= P, slot = is_v ? r - P : r;
+            uint16_t* drow = dst + (size_t)page_row(is_v, slot, P, geo.tiled != 0) * D;
+            for (int c = lane; c < D / 4; c += 32) {
+                const float sc = q_up<BF16>(*reinterpret_cast<const uint16_t*>(recp + qrec_scale_off(is_v, slot, c >> 3, P, D)));
+                uint16_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int qi = (int)recp[qrec_value_off(is_v, slot, 4 * c + i, P, D)] - 128;
+                    o[i] = q_down<BF16>(__fmul_rn((float)qi, sc));
+                }
+                *reinterpret_cast<uint2*>(drow + 4 * c) = make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
+            }
+        }
+    }
+}
+
 // One warp per query row, any page size and head_dim (multiple of 32, <= 512).
 template <bool BF16>
 __global__ void generic_quant_kernel(const GenericArgs a) {
@@ -200,6 +234,16 @@ cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st)
     const int blocks = (int)std::min<int64_t>((rows + 7) / 8, 148 * 8);
     if (bf16) append_quant_kernel<true><<<blocks, 256, 0, st>>>(a);
     else append_quant_kernel<false><<<blocks, 256, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_pages(const int32_t* tables, int n_entries, const GeomDev& geo, const void* arena, void* scratch,
+                                 int32_t* status, bool bf16, cudaStream_t st) {
+    const int64_t items = (int64_t)n_entries * geo.n_kv;
+    if (items <= 0) return cudaSuccess;
+    const int blocks = (int)std::min<int64_t>((items + 7) / 8, 148 * 8);
+    if (bf16) dequant_pages_kernel<true><<<blocks, 256, 0, st>>>(tables, n_entries, geo, reinterpret_cast<const uint8_t*>(arena), reinterpret_cast<uint16_t*>(scratch), status);
+    else dequant_pages_kernel<false><<<blocks, 256, 0, st>>>(tables, n_entries, geo, reinterpret_cast<const uint8_t*>(arena), reinterpret_cast<uint16_t*>(scratch), status);
     return cudaGetLastError();
 }
 

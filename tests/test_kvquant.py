@@ -176,3 +176,16 @@ def test_bf16_quantized_decode_against_a_float32_reading_of_its_own_pages():
         p = np.exp(sc - sc.max()); p /= p.sum()
         ref[h] = p @ V[h // (n_q // n_kv)]
     assert np.abs(got - ref).max() < 2e-2, np.abs(got - ref).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_q,n_kv,d,chunks", [(32, 8, 128, (300, 150)), (9, 3, 64, (200, 90)), (8, 4, 256, (130, 40))])
+def test_chunks_over_int8_layers_run_on_the_tensor_core_kernels(n_q, n_kv, d, chunks):
+    # chunk steps de-quantise the sequences' pages into a float scratch layer and run the chunk kernels over it
+    p = Pair(2, n_q, n_kv, d, 1024, num_pages=120, seed=7 + d, shuffle_free_list=True, quantize_kv=True)
+    a, b = p.new_seq(), p.new_seq()
+    p.step([a, b], list(chunks))
+    p.step([a, b], [1, 1])
+    p.step([a, b], [chunks[1], chunks[0]], window=200)     # a second chunk over the cached prefix, with a window
+    p.step([a, b], [1, 1])
+    p.assert_state_equal(pages="used")
