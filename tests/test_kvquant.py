@@ -189,3 +189,26 @@ def test_chunks_over_int8_layers_run_on_the_tensor_core_kernels(n_q, n_kv, d, ch
     p.step([a, b], [chunks[1], chunks[0]], window=200)     # a second chunk over the cached prefix, with a window
     p.step([a, b], [1, 1])
     p.assert_state_equal(pages="used")
+
+
+@pytest.mark.gpu
+def test_int8_pages_with_prefix_sharing_and_churn():
+    # shared prefix pages (refcounted), decode with the quantising append inside the kernel, rollback to the
+    # prefix and replacement: private pages only are ever written, packed records stay bit-exact
+    p = Pair(2, 28, 4, 128, 2048, num_pages=300, shuffle_free_list=True, seed=0xC0B5, popn_refuses=False, quantize_kv=True)
+    root = p.new_seq()
+    p.step([root], [64])
+    live = [p.fork(root, 64) for _ in range(8)]
+    p.step(live, [int(x) for x in p.rng.integers(8, 200, len(live))], check=False)
+    for it in range(2):
+        for _ in range(4):
+            p.step(live, [1] * len(live))
+        e = live[int(p.rng.integers(len(live)))]
+        n = e[0].seq_len() - 64
+        assert e[0].popn(n) == n and e[1].popn(n) == n
+        live.remove(e)
+        p.drop(e)
+        live.append(p.fork(root, 64))
+        p.step(live[-1:], [int(p.rng.integers(20, 90))], check=False)
+    p.step(live, [1] * len(live))
+    p.assert_state_equal(pages="used")
