@@ -213,6 +213,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     arena.set_free_list(np.random.default_rng(SEED + 7 + rank).permutation(ARENA_PAGES))
     if args.ctas_per_sm or args.stages or args.consumers or args.no_overlap:
         arena.set_decode_tuning(args.ctas_per_sm, args.stages, args.consumers, 0, not args.no_overlap)
+    if args.split:
+        arena.set_decode_split(*[int(x) for x in args.split.split(",")])
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
 
     def fill(which, counts):
@@ -522,10 +524,15 @@ def main():
     ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
     ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8, 12)")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
+    ap.add_argument("--split", default="", help="tuning: tail_pct,min_item,max_levels of the decode work split (min_item 0 = static split)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quantize-kv", action="store_true", help="int8 KV pages (the reference's CacheConfig::quantize_kv)")
+    ap.add_argument("--measure", action="store_true", help="load the measurement build (timers, CBKV_DEBUG switches)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer than the 28 layers (small ncu case)")
     args = ap.parse_args()
+    if args.measure:
+        from combsengine_b200 import _lib as _l
+        _l.use_measure_build()
     if args.config == "cfg4":
         return run_prefill(args, int(os.environ.get("RANK", "0")), 1, int(os.environ.get("LOCAL_RANK", "0")))
     if args.config == "rope":

@@ -96,10 +96,23 @@ PROTOTYPES = {
     "cbkv_set_decode_tuning": (I32, [P, I32, I32, I32, I32, I32]),
     "cbkv_set_chunk_kernel": (I32, [P, I32]),
     "cbkv_debug_begin_step_host": (I32, [P, C.POINTER(P), C.POINTER(I64), C.POINTER(I64), I32]),
-    "cbkv_debug_decode_plan": (I64, [P, I64, I32, C.POINTER(I32), I64]),
+    "cbkv_debug_decode_plan": (I64, [P, I64, I32, I32, I32, C.POINTER(I32), I64]),
+    "cbkv_set_decode_split": (I32, [P, I32, I32, I32]),
+    "cbkv_debug_set_wait_limit": (I32, [P, I64, I32]),
+    "cbkv_static_status": (I32, [P, C.POINTER(I32)]),
+    "cbkv_debug_raise": (I32, [I32]),
 }
 
 _lib = None
+
+
+def use_measure_build() -> None:
+    """Load the measurement flavour (python -m combsengine_b200._build --measure) instead of the
+    product library; must be called before the first load()."""
+    global LIB_PATH
+    if _lib is not None:
+        raise RuntimeError("the library is already loaded")
+    LIB_PATH = os.path.join(HERE, "libcombskv_measure.so")
 
 
 def load() -> C.CDLL:

@@ -12,6 +12,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -61,7 +62,10 @@ struct StepSlot {
 
 struct DecodePlanDev {
     DecodePlan host;
-    const int32_t *seg_unit_begin, *seg_page_lo, *seg_first_cta, *seg_nparts, *seg_part_base, *cta_unit_begin, *cta_first_seg;
+    const SegInfo* segs = nullptr;     // in the step slot
+    const ItemInfo* items = nullptr;   // in the step slot
+    size_t unit_row_off = 0;           // offset (ints) of this plan's unit_row in DeviceState::unit_rows
+    bool fresh = true;                 // unit_row was written by a kernel no decode launch has waited for yet
 };
 
 struct DeviceState {
@@ -74,7 +78,14 @@ struct DeviceState {
     int cur = 0;
     uint64_t uploaded_step = 0;
     StepDev step{};
-    std::map<int64_t, DecodePlanDev> decode_plans;
+    std::map<std::pair<int64_t, int>, DecodePlanDev> decode_plans;  // by (window, consumer warps)
+    int32_t* unit_rows = nullptr;  // unit_row arrays of the step's plans, one after the other
+    size_t unit_rows_cap = 0, unit_rows_used = 0;
+    int32_t* work_counters = nullptr;  // four claim counters of the decode kernel, rotating per launch
+    uint32_t launch_seq = 0;
+    DecodeSplit split;
+    uint32_t wait_us = 100000;  // limit of the kernels' bounded waits
+    int32_t fault_tile = -1;    // test hook, see cbkv_debug_set_wait_limit
     bool chunk_plan_ok = false;
     ChunkPlan chunk_host;
     const int32_t* chunk_item_begin = nullptr;
@@ -111,8 +122,10 @@ struct DeviceState {
     IoSlot io_slots[4];
     int io_cur = 0;
     cudaStream_t h2d = nullptr, d2h = nullptr;
-    unsigned long long* dbg_buf = nullptr;  // CBKV_DEBUG bit 4: per-CTA timestamps of the last decode launch
+#ifdef CBKV_MEASURE
+    unsigned long long* dbg_buf = nullptr;  // per-CTA timestamps / cycle counters of the last launch
     int dbg_ctas = 0;
+#endif
     // profiling
     bool profile = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof;
@@ -165,20 +178,24 @@ int32_t ensure_device(Arena* a) {
     return CBKV_OK;
 }
 
+#ifdef CBKV_MEASURE
+// Measurement build only (python -m combsengine_b200._build --measure): switches read from CBKV_DEBUG.
 int debug_flags() {
     static int f = -1;
     if (f < 0) { const char* e = getenv("CBKV_DEBUG"); f = e ? atoi(e) : 0; }
     return f;
 }
+#else
+constexpr int debug_flags() { return 0; }  // the product build ignores the environment
+#endif
 
-int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D, int box_rows, bool linear = false) {
+int32_t encode_map(CUtensorMap* map, bool bf16, void* base, uint64_t rows, int D, int box_rows) {
     cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {linear ? (cuuint32_t)D : 64u, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode_fn()(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims,
-                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             linear ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
     return CBKV_OK;
@@ -228,10 +245,6 @@ int32_t alloc_float_layer(Arena* a, LayerArena* Lp, cudaStream_t st) {
         if (rc) return rc;
         rc = encode_map(&L.map_k16, bf16, L.base, rows, a->cfg.head_dim, 16);
         if (rc) return rc;
-        if (a->cfg.head_dim <= 256 && (debug_flags() & 2)) {
-            rc = encode_map(&L.map_lin, bf16, L.base, rows, a->cfg.head_dim, 32, true);
-            if (rc) return rc;
-        }
     }
     return CBKV_OK;
 }
@@ -261,9 +274,8 @@ int32_t slot_upload(DeviceState* d, const void* src, size_t bytes, cudaStream_t 
             p = d->step.tables; fix(p); d->step.tables = (const int32_t*)p;
             for (auto& kv : d->decode_plans) {
                 DecodePlanDev& pd = kv.second;
-                const int32_t** arr[] = {&pd.seg_unit_begin, &pd.seg_page_lo, &pd.seg_first_cta, &pd.seg_nparts,
-                                         &pd.seg_part_base, &pd.cta_unit_begin, &pd.cta_first_seg};
-                for (auto pp : arr) { p = *pp; fix(p); *pp = (const int32_t*)p; }
+                p = pd.segs; fix(p); pd.segs = (const SegInfo*)p;
+                p = pd.items; fix(p); pd.items = (const ItemInfo*)p;
             }
             p = d->chunk_item_begin; fix(p); d->chunk_item_begin = (const int32_t*)p;
             p = d->tile_item_begin; fix(p); d->tile_item_begin = (const int32_t*)p;
@@ -294,6 +306,10 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->tile_item_begin = nullptr;
     d->step = StepDev{};
     d->last_kv_writer = -1;  // the upload is a full stream dependency
+    d->unit_rows_used = 0;
+    // tickets and claim counters start every step at zero, whatever an earlier launch that gave up left behind
+    if (d->seg_counter) CU_TRY(cudaMemsetAsync(d->seg_counter, 0, d->counter_cap * sizeof(int32_t), st));
+    if (d->work_counters) CU_TRY(cudaMemsetAsync(d->work_counters, 0, 4 * sizeof(int32_t), st));
     if (a->step_meta.empty()) {  // an empty step: nothing to upload, nothing will launch
         d->uploaded_step = a->step_id;
         return CBKV_OK;
@@ -316,47 +332,73 @@ GeomDev geom(const Arena* a) {
                    a->cfg.page_size, (int32_t)a->num_pages, (a->dev && dev_of(const_cast<Arena*>(a))->fast) ? 1 : 0};
 }
 
-int32_t get_decode_plan(Arena* a, int64_t window, cudaStream_t st, DecodePlanDev** out) {
+int32_t get_decode_plan(Arena* a, int64_t window, bool quant, cudaStream_t st, DecodePlanDev** out) {
     DeviceState* d = dev_of(a);
-    auto it = d->decode_plans.find(window);
+    DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers, quant);
+    const auto key = std::make_pair(window, dc.consumers);
+    auto it = d->decode_plans.find(key);
     if (it != d->decode_plans.end()) { *out = &it->second; return CBKV_OK; }
-    DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers);
     DecodePlanDev pd{};
     // at least one page per consumer warp, at most one resident wave of CTAs
     int max_ctas = d->sm_count * dc.ctas_per_sm;
     if (d->decode_max_ctas > 0) max_ctas = std::min(max_ctas, d->decode_max_ctas);
-    build_decode_plan(*a, window, max_ctas, &pd.host);
+    build_decode_plan(*a, window, max_ctas, d->split, &pd.host);
     {
         int want = std::max(1, (pd.host.n_units + dc.consumers - 1) / dc.consumers);
-        if (want < pd.host.n_ctas) build_decode_plan(*a, window, want, &pd.host);
+        if (want < pd.host.n_ctas) build_decode_plan(*a, window, want, d->split, &pd.host);
     }
-    std::vector<int32_t> flat;
-    auto push = [&](const std::vector<int32_t>& v) { size_t o = flat.size(); flat.insert(flat.end(), v.begin(), v.end()); return o; };
-    size_t o0 = push(pd.host.seg_unit_begin), o1 = push(pd.host.seg_page_lo), o2 = push(pd.host.seg_first_cta),
-           o3 = push(pd.host.seg_nparts), o4 = push(pd.host.seg_part_base), o5 = push(pd.host.cta_unit_begin),
-           o6 = push(pd.host.cta_first_seg);
+    // segment and item records in one upload
+    const size_t seg_bytes = pd.host.segs.size() * sizeof(SegInfo), item_bytes = pd.host.items.size() * sizeof(ItemInfo);
+    std::vector<uint8_t> flat(seg_bytes + item_bytes);
+    memcpy(flat.data(), pd.host.segs.data(), seg_bytes);
+    memcpy(flat.data() + seg_bytes, pd.host.items.data(), item_bytes);
     const void* p = nullptr;
-    int32_t rc = slot_upload(d, flat.data(), flat.size() * sizeof(int32_t), st, &p);
+    int32_t rc = slot_upload(d, flat.data(), flat.size(), st, &p);
     if (rc) return rc;
-    const int32_t* base = (const int32_t*)p;
-    pd.seg_unit_begin = base + o0; pd.seg_page_lo = base + o1; pd.seg_first_cta = base + o2; pd.seg_nparts = base + o3;
-    pd.seg_part_base = base + o4; pd.cta_unit_begin = base + o5; pd.cta_first_seg = base + o6;
+    pd.segs = reinterpret_cast<const SegInfo*>(p);
+    pd.items = reinterpret_cast<const ItemInfo*>(reinterpret_cast<const uint8_t*>(p) + seg_bytes);
     // scratch for partial results and the per-segment tickets
     if ((size_t)pd.host.n_parts > d->part_cap) {
         CU_TRY(cudaStreamSynchronize(st));
         if (d->part_o) { cudaFree(d->part_o); cudaFree(d->part_ml); }
-        d->part_cap = std::max<size_t>((size_t)pd.host.n_parts * 2, 1024);
+        d->part_o = d->part_ml = nullptr;
+        d->part_cap = std::max<size_t>((size_t)pd.host.n_parts * 2, 2048);
         CU_TRY(cudaMalloc(&d->part_o, d->part_cap * 8 * a->cfg.head_dim * sizeof(float)));
         CU_TRY(cudaMalloc(&d->part_ml, d->part_cap * 16 * sizeof(float)));
     }
     if ((size_t)pd.host.n_segs > d->counter_cap) {
         CU_TRY(cudaStreamSynchronize(st));
         if (d->seg_counter) cudaFree(d->seg_counter);
+        d->seg_counter = nullptr;
         d->counter_cap = std::max<size_t>((size_t)pd.host.n_segs * 2, 1024);
         CU_TRY(cudaMalloc(&d->seg_counter, d->counter_cap * sizeof(int32_t)));
         CU_TRY(cudaMemsetAsync(d->seg_counter, 0, d->counter_cap * sizeof(int32_t), st));
     }
-    auto ins = d->decode_plans.emplace(window, std::move(pd));
+    if (!d->work_counters) {
+        CU_TRY(cudaMalloc(&d->work_counters, 4 * sizeof(int32_t)));
+        CU_TRY(cudaMemsetAsync(d->work_counters, 0, 4 * sizeof(int32_t), st));
+    }
+    // the record index of every unit, resolved through the block tables once for all layers of the step
+    const size_t need = d->unit_rows_used + (size_t)pd.host.n_units;
+    if (need > d->unit_rows_cap) {
+        CU_TRY(cudaStreamSynchronize(st));
+        const size_t ncap = std::max<size_t>(need * 2, (size_t)1 << 18);
+        int32_t* nb = nullptr;
+        CU_TRY(cudaMalloc(&nb, ncap * sizeof(int32_t)));
+        if (d->unit_rows) {
+            if (d->unit_rows_used) CU_TRY(cudaMemcpy(nb, d->unit_rows, d->unit_rows_used * sizeof(int32_t), cudaMemcpyDeviceToDevice));
+            cudaFree(d->unit_rows);
+        }
+        d->unit_rows = nb;
+        d->unit_rows_cap = ncap;
+    }
+    pd.unit_row_off = d->unit_rows_used;
+    d->unit_rows_used = need;
+    CU_TRY(launch_resolve_units(pd.segs, pd.host.n_segs, d->step.tables, a->cfg.n_kv_heads, (int)a->num_pages,
+                                d->unit_rows + pd.unit_row_off, pd.host.n_units, d->status, st));
+    g_launches++;
+    pd.fresh = true;
+    auto ins = d->decode_plans.emplace(key, std::move(pd));
     *out = &ins.first->second;
     return CBKV_OK;
 }
@@ -465,19 +507,23 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     }
     if (d->fast && a->step_is_decode) {
         DecodePlanDev* pd = nullptr;
-        int32_t rc = get_decode_plan(a, w, st, &pd);
+        int32_t rc = get_decode_plan(a, w, L.quant, st, &pd);
         if (rc) return rc;
+        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers, L.quant);
         DecodeArgs args{};
-        args.step = d->step; args.geo = geom(a);
-        args.seg_unit_begin = pd->seg_unit_begin; args.seg_page_lo = pd->seg_page_lo; args.seg_first_cta = pd->seg_first_cta;
-        args.seg_nparts = pd->seg_nparts; args.seg_part_base = pd->seg_part_base; args.cta_unit_begin = pd->cta_unit_begin;
-        args.cta_first_seg = pd->cta_first_seg; args.n_segs = pd->host.n_segs;
+        args.geo = geom(a);
+        args.segs = pd->segs; args.items = pd->items; args.unit_row = d->unit_rows + pd->unit_row_off;
+        args.n_segs = pd->host.n_segs; args.n_items = pd->host.n_items; args.n_ctas = pd->host.n_ctas;
         args.q = q; args.out = out; args.k_new = k_fused; args.v_new = v_fused; args.arena = L.base;
         args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
+        args.work_counters = d->work_counters; args.work_slot = (int32_t)(d->launch_seq++ & 3u);
         args.window = (int32_t)w; args.scale_log2 = scale_log2;
-        DecodeConfig dc = decode_config(a->cfg.head_dim, a->n_rep(), d->decode_ctas_per_sm, d->decode_stages, d->decode_consumers, L.quant);
         args.n_stages = dc.stages; args.comb_cols = dc.comb_cols; args.comb_bufs = dc.comb_bufs;
-        args.kv_dep = d->last_kv_writer == layer ? 1 : 0;
+        // the producer may run ahead of earlier work in the stream unless that work wrote what it reads
+        args.kv_dep = (d->last_kv_writer == layer || pd->fresh) ? 1 : 0;
+        pd->fresh = false;
+        args.wait_us = d->wait_us; args.fault_tile = d->fault_tile;
+#ifdef CBKV_MEASURE
         args.debug = debug_flags();
         if (args.debug & 4) {
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
@@ -485,9 +531,9 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
             args.dbg_buf = d->dbg_buf;
             d->dbg_ctas = pd->host.n_ctas;
         }
+#endif
         ProfScope ps(d, st);
-        if (L.quant) args.debug &= ~2;
-        CU_TRY(launch_decode((args.debug & 2) ? L.map_lin : L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st, L.quant));
+        CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st, L.quant));
         g_launches++;
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
@@ -502,12 +548,16 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         const int rs = rep_slots_of(a->n_rep());
         int32_t rc = get_tile_plan(a, (use_tc2 ? 2 : 1) * (128 / rs), st);
         if (rc) return rc;
-        ChunkArgs args{d->step, geom(a), d->tile_item_begin, d->tile_host.n_items, q, out, d->status, (int32_t)w, scale_log2, rs, nullptr};
-        if (debug_flags() & 8) {  // measurement only: per-role cycle counters of the first 4096 CTAs
+        ChunkArgs args{};
+        args.step = d->step; args.geo = geom(a); args.item_begin = d->tile_item_begin; args.n_items = d->tile_host.n_items;
+        args.q = q; args.out = out; args.status = d->status; args.window = (int32_t)w; args.scale_log2 = scale_log2; args.rep_slots = rs;
+#ifdef CBKV_MEASURE
+        if (debug_flags() & 8) {  // per-role cycle counters of the first 4096 CTAs
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
             CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
             if (d->tile_host.n_items <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
         }
+#endif
         ProfScope ps(d, st);
         if (use_tc2) CU_TRY(launch_chunk_tc2(KV->map_kv, args, bf16, st));
         else CU_TRY(launch_chunk_tc(KV->map_k16, KV->map_kv, args, bf16, st));
@@ -518,7 +568,9 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     if (d->fast) {
         int32_t rc = get_chunk_plan(a, st);
         if (rc) return rc;
-        ChunkArgs args{d->step, geom(a), d->chunk_item_begin, d->chunk_host.n_items, q, out, d->status, (int32_t)w, scale_log2, 0, nullptr};
+        ChunkArgs args{};
+        args.step = d->step; args.geo = geom(a); args.item_begin = d->chunk_item_begin; args.n_items = d->chunk_host.n_items;
+        args.q = q; args.out = out; args.status = d->status; args.window = (int32_t)w; args.scale_log2 = scale_log2;
         ProfScope ps(d, st);
         CU_TRY(launch_chunk(KV->map_kv, args, bf16, st));
         g_launches++;
@@ -538,13 +590,16 @@ extern "C" {
 const char* cbkv_last_error(void) { return last_error(); }
 
 int32_t cbkv_arena_create(const cbkv_config* cfg, cbkv_arena** out) {
+    return fenced([&]() -> int32_t {
     Arena* a = nullptr;
     int32_t rc = arena_create(cfg, &a);
     if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_arena*>(a);
     return rc;
+    });
 }
 
 int32_t cbkv_arena_destroy(cbkv_arena* arena) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a) return CBKV_OK;
     if (a->dev) {
@@ -555,6 +610,11 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
         for (auto& s : d->slots) { if (s.host) cudaFreeHost(s.host); if (s.dev) cudaFree(s.dev); if (s.ev) cudaEventDestroy(s.ev); }
         if (d->part_o) { cudaFree(d->part_o); cudaFree(d->part_ml); }
         if (d->seg_counter) cudaFree(d->seg_counter);
+        if (d->unit_rows) cudaFree(d->unit_rows);
+        if (d->work_counters) cudaFree(d->work_counters);
+#ifdef CBKV_MEASURE
+        if (d->dbg_buf) cudaFree(d->dbg_buf);
+#endif
         if (d->status) cudaFree(d->status);
         if (d->io) cudaFree(d->io);
         if (d->qrot) cudaFree(d->qrot);
@@ -570,9 +630,11 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
     while (!a->seqs.empty()) seq_destroy(a->seqs.back());
     delete a;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_set_free_list(cbkv_arena* arena, const int64_t* ids, int64_t n) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !ids) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (!a->alloc.set_initial(ids, n)) {
@@ -580,25 +642,33 @@ int32_t cbkv_set_free_list(cbkv_arena* arena, const int64_t* ids, int64_t n) {
         return CBKV_ERR_ARG;
     }
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_seq_create(cbkv_arena* arena, cbkv_seq** out) {
+    return fenced([&]() -> int32_t {
     Seq* s = nullptr;
     int32_t rc = seq_create(reinterpret_cast<Arena*>(arena), &s);
     if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_seq*>(s);
     return rc;
+    });
 }
-int32_t cbkv_seq_destroy(cbkv_seq* seq) { return seq_destroy(reinterpret_cast<Seq*>(seq)); }
+int32_t cbkv_seq_destroy(cbkv_seq* seq) {
+    return fenced([&]() -> int32_t { return seq_destroy(reinterpret_cast<Seq*>(seq)); });
+}
 
 int32_t cbkv_seq_fork_prefix(cbkv_seq* parent, int64_t n_tokens, cbkv_seq** out) {
+    return fenced([&]() -> int32_t {
     Seq* c = nullptr;
     int32_t rc = seq_fork_prefix(reinterpret_cast<Seq*>(parent), n_tokens, &c);
     if (rc == CBKV_OK) *out = reinterpret_cast<cbkv_seq*>(c);
     return rc;
+    });
 }
 
 int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens, const int64_t* pos,
                         int32_t n_seqs, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
     // The device must be reachable before any state is advanced: there is no CPU path.
@@ -607,9 +677,11 @@ int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t*
     rc = begin_step(a, reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs);
     if (rc) return rc;
     return upload_step(a, static_cast<cudaStream_t>(stream));
+    });
 }
 
 int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void* v, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -619,10 +691,12 @@ int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void*
     CU_TRY(cudaSetDevice(dev_of(a)->device));
     if ((rc = materialize(a, layer, st))) return rc;
     return run_append(a, layer, k, v, st);
+    });
 }
 
 int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, void* out, double scale, int64_t window,
                              void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -632,10 +706,12 @@ int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, vo
     CU_TRY(cudaSetDevice(dev_of(a)->device));
     if ((rc = materialize(a, layer, st))) return rc;
     return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
+    });
 }
 
 int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const void* k, const void* v, void* out,
                        double scale, int64_t window, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -649,6 +725,7 @@ int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const vo
         return run_attention(a, layer, q, k, v, out, scale, window, st);  // the append rides inside the decode kernel
     if ((rc = run_append(a, layer, k, v, st))) return rc;
     return run_attention(a, layer, q, nullptr, nullptr, out, scale, window, st);
+    });
 }
 
 // ---- rotary embedding + QK norm fused into the append (rope.cu) ----------------
@@ -671,6 +748,7 @@ static int32_t check_rope_cfg(const cbkv_rope_config* c) {
 }
 
 int32_t cbkv_rope_inv_freq_host(const cbkv_rope_config* cfg, double* inv_out, double* mscale_out) {
+    return fenced([&]() -> int32_t {
     int32_t rc = check_rope_cfg(cfg);
     if (rc) return rc;
     if (!inv_out || !mscale_out) { set_error("null output"); return CBKV_ERR_ARG; }
@@ -678,9 +756,11 @@ int32_t cbkv_rope_inv_freq_host(const cbkv_rope_config* cfg, double* inv_out, do
     if ((rc = rope_inv_freq(*cfg, &inv, mscale_out))) return rc;
     std::copy(inv.begin(), inv.end(), inv_out);
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_rope_tables_host(const cbkv_rope_config* cfg, float* cos_out, float* sin_out) {
+    return fenced([&]() -> int32_t {
     int32_t rc = check_rope_cfg(cfg);
     if (rc) return rc;
     if (!cos_out || !sin_out) { set_error("null output"); return CBKV_ERR_ARG; }
@@ -689,9 +769,11 @@ int32_t cbkv_rope_tables_host(const cbkv_rope_config* cfg, float* cos_out, float
     if ((rc = rope_inv_freq(*cfg, &inv, &mscale))) return rc;
     rope_tables(*cfg, inv, mscale, cos_out, sin_out);
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_rope** out) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
     int32_t rc = check_rope_cfg(cfg);
@@ -726,15 +808,18 @@ int32_t cbkv_rope_create(cbkv_arena* arena, const cbkv_rope_config* cfg, cbkv_ro
     }
     *out = reinterpret_cast<cbkv_rope*>(r);
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_rope_destroy(cbkv_rope* rope) {
+    return fenced([&]() -> int32_t {
     Rope* r = reinterpret_cast<Rope*>(rope);
     if (!r) return CBKV_OK;
     cudaSetDevice(r->device);
     if (r->table) cudaFree(r->table);
     delete r;
     return CBKV_OK;
+    });
 }
 
 // k_out non-null: rotated k goes to that dense buffer and nothing is written to pages (int8 layers,
@@ -780,6 +865,7 @@ static int32_t rope_scratch(Arena* a, cudaStream_t st, size_t bytes) {
 
 int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
                          const void* q, const void* k, const void* v, void* q_out, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -796,11 +882,13 @@ int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope
         return run_append(a, layer, d->qrot, v, st);
     }
     return run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, q_out, nullptr, st);
+    });
 }
 
 int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
                             const void* q, const void* k, const void* v, void* out, double scale, int64_t window,
                             void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -824,10 +912,12 @@ int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* r
     }
     if ((rc = run_rope_append(a, layer, reinterpret_cast<const Rope*>(rope), norm, q, k, v, d->qrot, nullptr, st))) return rc;
     return run_attention(a, layer, d->qrot, nullptr, nullptr, out, scale, window, st);
+    });
 }
 
 int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
                             const void* v_host, void* out_host, double scale, int64_t window, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -858,10 +948,12 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
     CU_TRY(cudaMemcpyAsync(out_host, od, qb, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
                                   const void* v_host, void* out_host, double scale, int64_t window, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -908,9 +1000,11 @@ int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* 
     CU_TRY(cudaEventRecord(sl.out_done, d->d2h));
     sl.used = true;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_host_sync(cbkv_arena* arena) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
     if (!a->dev) return CBKV_OK;
@@ -919,25 +1013,50 @@ int32_t cbkv_host_sync(cbkv_arena* arena) {
     for (auto& sl : d->io_slots)
         if (sl.used) CU_TRY(cudaEventSynchronize(sl.out_done));
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_host_alloc(size_t bytes, void** out) {
+    return fenced([&]() -> int32_t {
     if (!out) { set_error("null argument"); return CBKV_ERR_ARG; }
     CU_TRY(cudaMallocHost(out, bytes));
     return CBKV_OK;
+    });
 }
 int32_t cbkv_host_free(void* p) {
+    return fenced([&]() -> int32_t {
     if (p) CU_TRY(cudaFreeHost(p));
     return CBKV_OK;
+    });
 }
 
-int32_t cbkv_popn(cbkv_seq* seq, int64_t n, int64_t* popped) { return popn(reinterpret_cast<Seq*>(seq), n, popped); }
-int32_t cbkv_reset(cbkv_seq* seq) { return reset(reinterpret_cast<Seq*>(seq)); }
-int64_t cbkv_seq_len(const cbkv_seq* seq) { return reinterpret_cast<const Seq*>(seq)->seq_len; }
-int64_t cbkv_pages_used(const cbkv_seq* seq) { return (int64_t)reinterpret_cast<const Seq*>(seq)->table.size(); }
-int64_t cbkv_num_free_pages(const cbkv_arena* arena) { return reinterpret_cast<const Arena*>(arena)->alloc.num_free(); }
+int32_t cbkv_popn(cbkv_seq* seq, int64_t n, int64_t* popped) {
+    return fenced([&]() -> int32_t { return popn(reinterpret_cast<Seq*>(seq), n, popped); });
+}
+int32_t cbkv_reset(cbkv_seq* seq) {
+    return fenced([&]() -> int32_t { return reset(reinterpret_cast<Seq*>(seq)); });
+}
+int64_t cbkv_seq_len(const cbkv_seq* seq) {
+    return fenced64([&]() -> int64_t {
+        if (!seq) { set_error("null sequence"); return (int64_t)CBKV_ERR_ARG; }
+        return reinterpret_cast<const Seq*>(seq)->seq_len;
+    });
+}
+int64_t cbkv_pages_used(const cbkv_seq* seq) {
+    return fenced64([&]() -> int64_t {
+        if (!seq) { set_error("null sequence"); return (int64_t)CBKV_ERR_ARG; }
+        return (int64_t)reinterpret_cast<const Seq*>(seq)->table.size();
+    });
+}
+int64_t cbkv_num_free_pages(const cbkv_arena* arena) {
+    return fenced64([&]() -> int64_t {
+        if (!arena) { set_error("null arena"); return (int64_t)CBKV_ERR_ARG; }
+        return reinterpret_cast<const Arena*>(arena)->alloc.num_free();
+    });
+}
 
 int32_t cbkv_page_stats(const cbkv_seq* seq, cbkv_page_stats_t* out) {
+    return fenced([&]() -> int32_t {
     const Seq* s = reinterpret_cast<const Seq*>(seq);
     if (!s || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
     int64_t mat = 0;
@@ -945,30 +1064,41 @@ int32_t cbkv_page_stats(const cbkv_seq* seq, cbkv_page_stats_t* out) {
         for (auto& L : static_cast<DeviceState*>(s->arena->dev)->layers) if (L.base) mat++;
     page_stats(s, mat, out);
     return CBKV_OK;
+    });
 }
 
 int64_t cbkv_page_bytes(const cbkv_arena* arena) {
+    return fenced64([&]() -> int64_t {
     const Arena* a = reinterpret_cast<const Arena*>(arena);
+    if (!a) { set_error("null arena"); return (int64_t)CBKV_ERR_ARG; }
     int64_t total = 0;  // what one page id costs over all layers: float pages, or records with bytes + scales
     for (int l = 0; l < a->cfg.num_layers; l++)
         total += a->layer_quant(l) ? (int64_t)a->cfg.n_kv_heads * (int64_t)qrec_bytes(a->cfg.page_size, a->cfg.head_dim)
                                    : (int64_t)a->cfg.page_size * a->cfg.n_kv_heads * a->cfg.head_dim * 2 * 2;
     return total;
+    });
 }
 
 int64_t cbkv_export_block_table(const cbkv_seq* seq, int64_t* out, int64_t cap) {
+    return fenced64([&]() -> int64_t {
     const Seq* s = reinterpret_cast<const Seq*>(seq);
+    if (!s || (!out && cap > 0)) { set_error("null argument"); return (int64_t)CBKV_ERR_ARG; }
     for (int64_t i = 0; i < (int64_t)s->table.size() && i < cap; i++) out[i] = s->table[(size_t)i];
     return (int64_t)s->table.size();
+    });
 }
 
 int64_t cbkv_export_free_list(const cbkv_arena* arena, int64_t* out, int64_t cap) {
+    return fenced64([&]() -> int64_t {
+    if (!arena || (!out && cap > 0)) { set_error("null argument"); return (int64_t)CBKV_ERR_ARG; }
     const auto& st = reinterpret_cast<const Arena*>(arena)->alloc.stack();
     for (int64_t i = 0; i < (int64_t)st.size() && i < cap; i++) out[i] = st[(size_t)i];
     return (int64_t)st.size();
+    });
 }
 
 int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k_out_host, void* v_out_host, void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !k_out_host || !v_out_host) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (layer < 0 || layer >= a->cfg.num_layers || page < 0 || page >= a->num_pages) { set_error("layer or page out of range"); return CBKV_ERR_ARG; }
@@ -996,16 +1126,20 @@ int32_t cbkv_export_page(cbkv_arena* arena, int32_t layer, int64_t page, void* k
                    buf.data() + ((size_t)h * 2 * P + page_row(1, slot, P, d->fast)) * rowb, rowb);
         }
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_layer_is_quantized(const cbkv_arena* arena, int32_t layer) {
+    return fenced([&]() -> int32_t {
     const Arena* a = reinterpret_cast<const Arena*>(arena);
     if (!a || layer < 0 || layer >= a->cfg.num_layers) { set_error("layer out of range"); return CBKV_ERR_ARG; }
     return a->layer_quant(layer) ? 1 : 0;
+    });
 }
 
 int32_t cbkv_export_page_quant(cbkv_arena* arena, int32_t layer, int64_t page, int32_t* kp, void* ks, int32_t* vp, void* vs,
                                void* stream) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !kp || !ks || !vp || !vs) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (layer < 0 || layer >= a->cfg.num_layers || page < 0 || page >= a->num_pages) { set_error("layer or page out of range"); return CBKV_ERR_ARG; }
@@ -1032,17 +1166,22 @@ int32_t cbkv_export_page_quant(cbkv_arena* arena, int32_t layer, int64_t page, i
                 // records hold q + 128 in every byte; the reference's words keep lane 3 signed (kv.rs:276-283)
                 for (int j = 0; j < D; j++) pk[j] = r[qrec_value_off(is_v, slot, j, P, D)] ^ ((j & 3) == 3 ? 0x80 : 0x00);
                 for (int g = 0; g < G; g++) memcpy(sc + 2 * g, r + qrec_scale_off(is_v, slot, g, P, D), 2);
-            }
+}
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_page_refcount(const cbkv_arena* arena, int64_t page) {
+    return fenced([&]() -> int32_t {
     const Arena* a = reinterpret_cast<const Arena*>(arena);
+    if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
     if (page < 0 || page >= a->num_pages) return -1;
     return a->refcnt[(size_t)page];
+    });
 }
 
 int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !status) { set_error("null argument"); return CBKV_ERR_ARG; }
     *status = 0;
@@ -1054,15 +1193,20 @@ int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status) {
     if (*status) {
         CU_TRY(cudaMemset(d->status, 0, sizeof(int32_t)));
         if (d->seg_counter) CU_TRY(cudaMemset(d->seg_counter, 0, d->counter_cap * sizeof(int32_t)));
+        if (d->work_counters) CU_TRY(cudaMemset(d->work_counters, 0, 4 * sizeof(int32_t)));
         set_error("kernel status word = " + std::to_string(*status));
         return CBKV_ERR_DEVICE;
     }
     return CBKV_OK;
+    });
 }
 
-int64_t cbkv_launch_count(void) { return g_launches.load(); }
+int64_t cbkv_launch_count(void) {
+    return fenced64([&]() -> int64_t { return g_launches.load(); });
+}
 
 int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
     int32_t rc = ensure_device(a);
@@ -1070,9 +1214,11 @@ int32_t cbkv_profile_enable(cbkv_arena* arena, int32_t on) {
     dev_of(a)->profile = on != 0;
     dev_of(a)->prof_used = 0;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || !a->dev || !total_ms || !launches) { set_error("null argument"); return CBKV_ERR_ARG; }
     DeviceState* d = dev_of(a);
@@ -1084,6 +1230,7 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         CU_TRY(cudaEventElapsedTime(&ms, d->prof[i].first, d->prof[i].second));
         sum += ms;
     }
+#ifdef CBKV_MEASURE
     if ((debug_flags() & 8) && d->dbg_buf && d->dbg_ctas < 0) {
         const int n = -d->dbg_ctas;
         std::vector<unsigned long long> h((size_t)n * 16);
@@ -1103,16 +1250,11 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
         unsigned long long t0 = ~0ull;
         for (int c = 0; c < d->dbg_ctas; c++) if (h[(size_t)c * 16]) t0 = std::min(t0, h[(size_t)c * 16]);
-        const char* names[8] = {"entry", "rows_resolved", "first_round_issued", "q_loaded", "first_tile_ready", "last_piece_arrived", "merger_exit", "producer_done"};
+        const char* names[8] = {"entry", "-", "first_round_issued", "q_loaded", "first_tile_ready", "last_piece_arrived", "merger_exit", "producer_done"};
         for (int s2 = 0; s2 < 8; s2++) {
             double mn = 1e18, mx = 0, av = 0; int cnt = 0;
             for (int c = 0; c < d->dbg_ctas; c++) { unsigned long long v = h[(size_t)c * 16 + s2]; if (!v) continue; double x = (double)(v - t0) * 1e-3; mn = std::min(mn, x); mx = std::max(mx, x); av += x; cnt++; }
             if (cnt) fprintf(stderr, "[cbkv timeline] %-22s min %7.2f avg %7.2f max %7.2f us (%d CTAs)\n", names[s2], mn, av / cnt, mx, cnt);
-        }
-        {
-            double w = 0, tot = 0, n = 0;
-            for (int c = 0; c < d->dbg_ctas; c++) { w += (double)h[(size_t)c * 16 + 13]; tot += (double)h[(size_t)c * 16 + 14]; n += (double)h[(size_t)c * 16 + 15]; }
-            if (n > 0) fprintf(stderr, "[cbkv consumer0] per tile: %.0f cycles waiting for the tile, %.0f cycles in all (%.1f tiles per CTA)\n", w / n, tot / n, n / d->dbg_ctas);
         }
         std::vector<int> order(d->dbg_ctas);
         for (int c = 0; c < d->dbg_ctas; c++) order[c] = c;
@@ -1120,19 +1262,22 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         auto us = [&](int c, int s2) { return h[(size_t)c * 16 + s2] ? (double)(h[(size_t)c * 16 + s2] - t0) * 1e-3 : -1.0; };
         for (int i = 0; i < d->dbg_ctas; i += (i < 8 ? 1 : d->dbg_ctas / 8)) {
             int c = order[i];
-            fprintf(stderr, "[cbkv cta] rank %3d cta %3d sm %3llu tiles %3llu pieces %llu merges %llu parts %llu | first_tile %.1f prod_done %.1f last_piece %.1f exit %.1f\n",
-                    i, c, h[(size_t)c * 16 + 11], h[(size_t)c * 16 + 12], h[(size_t)c * 16 + 8], h[(size_t)c * 16 + 9], h[(size_t)c * 16 + 10],
+            fprintf(stderr, "[cbkv cta] rank %3d cta %3d sm %3llu tiles %3llu items %llu pieces %llu merges %llu parts %llu | first_tile %.1f prod_done %.1f last_piece %.1f exit %.1f\n",
+                    i, c, h[(size_t)c * 16 + 11], h[(size_t)c * 16 + 12], h[(size_t)c * 16 + 13], h[(size_t)c * 16 + 8], h[(size_t)c * 16 + 9], h[(size_t)c * 16 + 10],
                     us(c, 4), us(c, 7), us(c, 5), us(c, 6));
         }
     }
+#endif
     *total_ms = sum;
     *launches = (int64_t)d->prof_used;
     d->prof_used = 0;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
                                int32_t max_ctas, int32_t overlap_launches) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || ctas_per_sm < 0 || ctas_per_sm > 8 || stages < 0 || stages > 64 || max_ctas < 0 ||
         !(consumers == 0 || consumers == 4 || consumers == 6 || consumers == 8 || consumers == 12)) {
@@ -1152,9 +1297,11 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
     d->pdl = overlap_launches != 0;
     d->decode_plans.clear();  // the split depends on the CTA count
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
+    return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a || mode < 0 || mode > 3) { set_error("bad argument"); return CBKV_ERR_ARG; }
     int32_t rc = ensure_device(a);
@@ -1165,28 +1312,80 @@ int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
     if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64 and 128 with 16-token pages only"); return CBKV_ERR_ARG; }
     dev_of(a)->chunk_mode = mode;
     return CBKV_OK;
+    });
 }
 
-// Host-only view of the decode work split for the step in flight (used by the CPU
-// tests of the partition): out = [n_ctas, n_segs, n_units, n_parts, cta_unit_begin...,
-// seg_unit_begin..., seg_page_lo..., seg_first_cta..., seg_nparts..., seg_part_base..., cta_first_seg...].
-int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t* out, int64_t cap) {
+// Host-only view of the decode work split for the step in flight (used by the CPU tests of
+// the partition): out = [n_ctas, n_items, n_segs, n_units, n_parts, levels,
+// segs (n_segs + 1 records of 8 ints), items (n_items records of 4 ints)].
+int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t tail_pct, int32_t min_item,
+                               int32_t* out, int64_t cap) {
+    return fenced64([&]() -> int64_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
-    if (!a || a->step_meta.empty()) return -1;
+    if (!a || a->step_meta.empty() || !out) return -1;
     DecodePlan pl;
-    build_decode_plan(*a, window, n_ctas, &pl);
-    std::vector<int32_t> flat = {pl.n_ctas, pl.n_segs, pl.n_units, pl.n_parts};
-    for (auto* v : {&pl.cta_unit_begin, &pl.seg_unit_begin, &pl.seg_page_lo, &pl.seg_first_cta, &pl.seg_nparts,
-                    &pl.seg_part_base, &pl.cta_first_seg})
-        flat.insert(flat.end(), v->begin(), v->end());
+    DecodeSplit sp;
+    if (tail_pct >= 0) sp.tail_pct = tail_pct;
+    if (min_item >= 0) sp.min_item = min_item;
+    build_decode_plan(*a, window, n_ctas, sp, &pl);
+    std::vector<int32_t> flat = {pl.n_ctas, pl.n_items, pl.n_segs, pl.n_units, pl.n_parts, pl.levels};
+    const int32_t* sp32 = reinterpret_cast<const int32_t*>(pl.segs.data());
+    flat.insert(flat.end(), sp32, sp32 + pl.segs.size() * 8);
+    const int32_t* ip32 = reinterpret_cast<const int32_t*>(pl.items.data());
+    flat.insert(flat.end(), ip32, ip32 + pl.items.size() * 4);
     for (int64_t i = 0; i < (int64_t)flat.size() && i < cap; i++) out[i] = flat[(size_t)i];
     return (int64_t)flat.size();
+    });
+}
+
+// How a CTA's share of a decode launch is cut into a head item and a tail of dynamically claimed
+// items (manager.hpp, DecodeSplit); negative = keep.  min_item = 0 switches the tail off.
+int32_t cbkv_set_decode_split(cbkv_arena* arena, int32_t tail_pct, int32_t min_item, int32_t max_levels) {
+    return fenced([&]() -> int32_t {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || tail_pct > 90 || max_levels > 8) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    DeviceState* d = dev_of(a);
+    if (tail_pct >= 0) d->split.tail_pct = tail_pct;
+    if (min_item >= 0) d->split.min_item = min_item;
+    if (max_levels >= 2) d->split.max_levels = max_levels;
+    d->decode_plans.clear();
+    return CBKV_OK;
+    });
+}
+
+// Test hook for the kernels' failure path.  wait_us > 0 replaces the limit of the decode kernel's
+// bounded waits (default 100000); fault_tile >= 0 makes the producer of CTA 0 skip the copy of that
+// tile, so the consumer that owns it finds its wait running out, the status word gets
+// ST_WAIT_TIMEOUT and the launch returns without a result; -1 switches the hook off.  Nothing is
+// read or written outside the kernel's own buffers either way.
+int32_t cbkv_debug_set_wait_limit(cbkv_arena* arena, int64_t wait_us, int32_t fault_tile) {
+    return fenced([&]() -> int32_t {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || wait_us < 0 || wait_us > 10000000) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    if (wait_us > 0) dev_of(a)->wait_us = (uint32_t)wait_us;
+    dev_of(a)->fault_tile = fault_tile;
+    return CBKV_OK;
+    });
+}
+
+// Test hook for the boundary itself: the body throws, the caller must see a return code.
+int32_t cbkv_debug_raise(int32_t kind) {
+    return fenced([&]() -> int32_t {
+        if (kind == 1) throw std::bad_alloc();
+        if (kind == 2) throw std::runtime_error("raised on request");
+        if (kind == 3) throw 42;
+        return CBKV_OK;
+    });
 }
 
 // Host-only bookkeeping of a step without touching a device (CPU tests of the manager).
 int32_t cbkv_debug_begin_step_host(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
                                    const int64_t* pos, int32_t n_seqs) {
-    return begin_step(reinterpret_cast<Arena*>(arena), reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs);
+    return fenced([&]() -> int32_t { return begin_step(reinterpret_cast<Arena*>(arena), reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs); });
 }
 
 }  // extern "C"

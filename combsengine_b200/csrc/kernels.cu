@@ -330,6 +330,7 @@ template <int D, bool BF16>
 __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&qf)[1][D / 16][2], float (&o)[1][D / 16][4],
                                           float (&m)[1][2], float (&l)[1][2], int kpos0, const int (&qpos)[1][2],
                                           int window, float scale_log2, bool need_mask, int lane, int dbg = 0) {
+    (void)dbg;  // phase switches exist in the measurement build only
     constexpr int G = D / 32;
     const int g = lane >> 2;
     const uint2 (&kx)[G] = r.kx; const uint2 (&ky)[G] = r.ky; const uint2 (&va)[G] = r.va; const uint2 (&vb)[G] = r.vb;
@@ -337,7 +338,9 @@ __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&q
     const uint32_t (&vs0)[G] = r.vs0; const uint32_t (&vs1)[G] = r.vs1;
     // ---- S^T = sum over groups of scale_K[token][grp] * (Kq . Q^T)
     float s[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!(dbg & 32))  // measurement only: skip the score phase
+#ifdef CBKV_MEASURE
+    if (!(dbg & 32))  // skip the score phase
+#endif
 #pragma unroll
     for (int grp = 0; grp < G; grp++) {
         const uint32_t x0 = q8_fix<BF16>(kx[grp].x), x1 = q8_fix<BF16>(kx[grp].y);
@@ -367,7 +370,9 @@ __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&q
     }
     float alpha[2] = {1.f, 1.f};
     bool moved = false;
-    if (!(dbg & 64))  // measurement only: skip the softmax
+#ifdef CBKV_MEASURE
+    if (!(dbg & 64))  // skip the softmax
+#endif
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         float mx = fmaxf(s[j], s[j + 2]);
@@ -395,7 +400,9 @@ __device__ __forceinline__ void q8_attend(const Q8Tile<D>& r, const uint32_t (&q
     pb0 = movmatrix_trans(pb0);  // tokens 2t, 2t+1 of column g
     pb1 = movmatrix_trans(pb1);  // tokens 2t+8, 2t+9
     // ---- O^T += sum over groups of Vq^T . (P^T * scale_V[token][grp])
-    if (!(dbg & 128))  // measurement only: skip the output phase
+#ifdef CBKV_MEASURE
+    if (!(dbg & 128))  // skip the output phase
+#endif
 #pragma unroll
     for (int grp = 0; grp < G; grp++) {
         const uint32_t a0 = q8_fix<BF16>(va[grp].x), a1 = q8_fix<BF16>(va[grp].y);  // d 4g, 4g+1 | 4g+2, 4g+3 of tokens 2t, 2t+1
@@ -504,41 +511,46 @@ __global__ void append_kernel(const AppendArgs a) {
 }
 
 // ------------------------------------------------------------------ decode
-// Each CTA owns a contiguous range of (sequence, kv head, page) units; a range may
-// cover the tail of one segment, whole segments and the head of another ("pieces").
+// The launch's (sequence, kv head, page) units are cut into work items (manager.hpp): CTA c
+// starts with item c and then claims further items from a device counter, larger ones first,
+// so CTAs on SMs that stream more slowly take fewer of them and all finish together.  An item
+// may cover the tail of one segment, whole segments and the head of another ("pieces").
 //
-// Warp 0 is the producer: its lanes resolve physical pages through the block table
-// (a round of lanes at a time, one look-up round ahead) and issue the TMA copies
-// into a CTA-wide ring of NS stages.  The other C warps consume: tile n of the CTA
-// lives in stage n % NS and belongs to consumer warp n % C, and NS is a multiple of
-// C, so every stage has one producer and one consumer that visit it in order (an
-// mbarrier parity wait is only unambiguous for a waiter at most one phase ahead).
-// Each consumer keeps a running (max, sum, numerator) state in registers; the
-// states are merged in shared memory when a piece ends.  A
-// segment cut across CTAs leaves partials in global scratch; the CTA that finishes
-// last (atomic ticket, nobody waits) merges them.
+// Warp 0 is the producer: it claims items two ahead, publishes them to the other warps
+// through a small queue in shared memory, reads each tile's record index from the per-step
+// unit_row array (one coalesced load per 32 tiles) and issues the TMA copies into a CTA-wide
+// ring of NS stages.  The next C warps consume: tile n of the CTA (counted across items)
+// lives in stage n % NS and belongs to consumer warp n % C, and NS is a multiple of C, so
+// every stage has one producer and one consumer that visit it in order (an mbarrier parity
+// wait is only unambiguous for a waiter at most one phase ahead).  Each consumer keeps a
+// running (max, sum, numerator) state in registers; when a piece ends the states go to
+// shared memory and the last warp (merger) combines them off the consumers' path.  A segment
+// cut across items leaves partials in global scratch; whoever draws the segment's last ticket
+// merges them (nobody waits for another CTA).
 //
-// Every wait is bounded; a warp that gives up records it in the status word and
-// falls through the remaining barriers without computing.
+// Every wait is bounded; a warp that gives up records it in the status word, raises the CTA's
+// failure flag and falls through the remaining barriers without computing.  The producer
+// leaves last, after every copy it issued has landed.
+constexpr int QN = 8;          // slots of the item queue (a power of two)
+constexpr int DEFER_CAP = 20;  // segments a CTA can leave to its cooperative merge at the end
+
 struct Piece {
-    int sb, se;        // unit range of the segment
-    int b, h;
-    int q_pos, page_lo, page_last, tbl_off, tok_off;
+    int sb, se;  // unit range of the segment
+    int h;
+    int q_pos, page_lo, page_last, tok_off, nparts, part_base;
 };
 
 __device__ __forceinline__ Piece load_piece(const DecodeArgs& a, int seg) {
-    Piece p;
-    p.sb = a.seg_unit_begin[seg];
-    p.se = a.seg_unit_begin[seg + 1];
-    p.b = seg / a.geo.n_kv;
-    p.h = seg - p.b * a.geo.n_kv;
-    const SeqMeta sm = a.step.seq_meta[p.b];
-    p.q_pos = sm.pos + sm.snew - 1;  // decode: the one new token, at the end of the window
-    p.page_lo = a.seg_page_lo[seg];
-    p.page_last = p.q_pos >> 4;
-    p.tbl_off = sm.tbl_off;
-    p.tok_off = sm.tok_off;
-    return p;
+    // this segment's record and the first word of the next one (the array has n_segs + 1 entries)
+    const int4* p = reinterpret_cast<const int4*>(a.segs + seg);
+    const int4 x = __ldg(p), y = __ldg(p + 1), z = __ldg(p + 2);
+    Piece pc;
+    pc.sb = x.x; pc.page_lo = x.y; pc.q_pos = x.z; pc.tok_off = x.w;
+    pc.nparts = y.x; pc.part_base = y.y;
+    pc.se = z.x;
+    pc.h = seg % a.geo.n_kv;
+    pc.page_last = pc.q_pos >> 4;  // decode: the one new token, at the end of the window
+    return pc;
 }
 
 template <int D>
@@ -554,7 +566,7 @@ __device__ __forceinline__ void load_q_frags(const DecodeArgs& a, const Piece& p
     }
 }
 
-// The same fragments in the contraction order of the quantised K tiles (see attend_tile_q8).
+// The same fragments in the contraction order of the quantised K tiles (see q8_attend).
 template <int D>
 __device__ __forceinline__ void load_q_frags_q8(const DecodeArgs& a, const Piece& p, int g, int t, uint32_t (&qf)[1][D / 16][2]) {
     const int n_rep = a.geo.n_rep;
@@ -577,14 +589,23 @@ __device__ __forceinline__ void consumer_sync(int nthreads) {
 }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// measurement only (debug bit 4): per-CTA timestamps, 8 slots each
-__device__ __forceinline__ void stamp(const DecodeArgs& a, int slot) {
-    if ((a.debug & 4) && a.dbg_buf) a.dbg_buf[(size_t)blockIdx.x * 16 + slot] = global_ns();
+__device__ __forceinline__ int4 lds128(uint32_t addr) {
+    int4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, int4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-constexpr int ROWS_CAP = 512;  // tiles whose rows are resolved per batch (a multiple of the producer round)
-constexpr int SEG_CAP = 64;    // segments of a CTA's range kept in shared memory
+#ifdef CBKV_MEASURE
+// per-CTA timestamps, 16 slots each
+#define CBKV_STAMP(slot) do { if ((a.debug & 4) && a.dbg_buf) a.dbg_buf[(size_t)blockIdx.x * 16 + (slot)] = global_ns(); } while (0)
+#define CBKV_DBG(bit) (a.debug & (bit))
+#else
+#define CBKV_STAMP(slot) do { } while (0)
+#define CBKV_DBG(bit) 0
+#endif
 
 // Merge the partial results of one segment (log-sum-exp combine) and store its output.
 // Thread r of T takes every T-th (column, 4 d-values) item; the loads of up to eight
@@ -630,25 +651,47 @@ __device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int n
     }
 }
 
+// Record index (page * n_kv + kv head) of every unit of a decode plan, once per step and
+// window: the decode launches of all layers read it instead of chasing the block tables.
+__global__ void resolve_units_kernel(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
+                                     int32_t* unit_row, int n_units, int32_t* status) {
+    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < n_units; u += gridDim.x * blockDim.x) {
+        int lo = 0, hi = n_segs - 1;  // last segment whose first unit is <= u (an empty segment shares its successor's)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (segs[mid].unit_begin <= u) lo = mid; else hi = mid - 1;
+        }
+        const SegInfo sg = segs[lo];
+        const int phys = tables[sg.tbl_off + sg.page_lo + (u - sg.unit_begin)];
+        if (phys < 0 || phys >= num_pages) {
+            atomicOr(status, ST_BAD_PAGE);
+            unit_row[u] = -1;  // the decode kernel reads page 0 instead and writes nothing
+        } else {
+            unit_row[u] = phys * n_kv + lo % n_kv;
+        }
+    }
+}
+
 // Warp roles: 0 = producer, 1..C = consumers, C+1 = merger.
 // Q8: the layer holds int8 records; a tile is one record fetched as one box of a byte tensor map.
 template <int D, int C, bool BF16, bool Q8>
 __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeArgs a) {
     constexpr uint32_t UNIT = Q8 ? (uint32_t)(2 * 16 * D + 2 * 16 * (D / 32) * 2) : 32u * D * 2u;
+    constexpr int DP = D + 4;  // row pitch of the merge buffers: the four lanes of a quad land in different banks
     extern __shared__ __align__(1024) uint8_t smem[];
     const int NS = a.n_stages;            // multiple of C (checked by the host)
-    const int R = NS < 8 ? 4 : 8;         // producer lanes per round; R <= NS keeps a round free of self-dependencies
     const int ccols = a.comb_cols;
     const int NB = a.comb_bufs;           // 1 or 2 state buffers between consumers and merger
-    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [NB][C][ccols][D]
-    float* comb_ml = comb_o + (size_t)NB * C * ccols * D;                     // [NB][C][8][2]
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(comb_ml + NB * C * 16); // [NS] tile landed
+    float* comb_o = reinterpret_cast<float*>(smem + (size_t)NS * UNIT);      // [NB][C][ccols][DP]
+    float* comb_ml = comb_o + (size_t)NB * C * ccols * DP;                    // [NB][C][8][2]
+    int4* qitems = reinterpret_cast<int4*>(comb_ml + NB * C * 16);            // [QN] published items
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(qitems + QN);           // [NS] tile landed
     uint64_t* bar_empty = bar_full + NS;                                      // [NS] tile consumed
     uint64_t* bar_cfull = bar_empty + NS;                                     // [2] all consumers stored their states
     uint64_t* bar_cempty = bar_cfull + 2;                                     // [2] merger is done with the buffer
-    int* flag = reinterpret_cast<int*>(bar_cempty + 2);                       // [1] a warp gave up, [2] deferred merges, [4..7] their segments
-    int* rows = flag + 8;                                                     // [ROWS_CAP] first arena row of each tile
-    int* segtab = rows + ROWS_CAP;                                            // [SEG_CAP][3] unit begin, first page, table offset
+    uint64_t* bar_qfull = bar_cempty + 2;                                     // [QN] item published
+    uint64_t* bar_qempty = bar_qfull + QN;                                    // [QN] item read by consumers and merger
+    int* flag = reinterpret_cast<int*>(bar_qempty + QN);                      // [1] a warp gave up, [2] merges left to the end, [4..4+DEFER_CAP) their segments
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
@@ -656,108 +699,155 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
         return;
     }
-    const int u0 = a.cta_unit_begin[cta], u1 = a.cta_unit_begin[cta + 1];
-    if (u0 >= u1) return;
-    if (tid == 0) stamp(a, 0);
-    const int ntiles = u1 - u0;
+    if (tid == 0) CBKV_STAMP(0);
     const uint32_t ring = smem_u32(smem);
     const uint32_t full0 = smem_u32(bar_full), empty0 = smem_u32(bar_empty);
     const uint32_t cfull0 = smem_u32(bar_cfull), cempty0 = smem_u32(bar_cempty);
+    const uint32_t qfull0 = smem_u32(bar_qfull), qempty0 = smem_u32(bar_qempty), qitems0 = smem_u32(qitems);
     const int Hkv = a.geo.n_kv;
-    const int first_seg = a.cta_first_seg[cta];
+    const uint64_t lim = (uint64_t)a.wait_us * 1000ull;
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
         for (int i = 0; i < NS; i++) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, 1); }
         for (int i = 0; i < 2; i++) { mbar_init(cfull0 + i * 8, C); mbar_init(cempty0 + i * 8, 1); }
+        for (int i = 0; i < QN; i++) { mbar_init(qfull0 + i * 8, 1); mbar_init(qempty0 + i * 8, C + 1); }
         flag[0] = 0; flag[1] = 0; flag[2] = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
-    // the segments this range can touch: one round of independent loads
-    const int nseg_tab = min(SEG_CAP, a.n_segs - first_seg);
-    for (int i = tid; i < nseg_tab; i += (C + 2) * 32) {
-        const int sg = first_seg + i;
-        segtab[i * 3 + 0] = a.seg_unit_begin[sg];
-        segtab[i * 3 + 1] = a.seg_page_lo[sg];
-        segtab[i * 3 + 2] = a.step.seq_meta[sg / Hkv].tbl_off;
-    }
     __syncthreads();
-    pdl_launch_dependents();
-
-    // Physical rows of the CTA's tiles through the block table: one more round of loads.
-    auto resolve_rows = [&](int from, int to, int t0, int nthreads) {
-        for (int n = from + t0; n < to; n += nthreads) {
-            const int u = u0 + n;
-            int i = 0;
-            while (i + 1 < nseg_tab && segtab[(i + 1) * 3] <= u) i++;
-            int sg = first_seg + i, sub = segtab[i * 3], plo = segtab[i * 3 + 1], toff = segtab[i * 3 + 2];
-            if (i + 1 == nseg_tab && sg + 1 < a.n_segs && a.seg_unit_begin[sg + 1] <= u) {
-                // range longer than the table (many tiny sequences): search the global arrays
-                int lo = sg, hi = a.n_segs - 1;
-                while (lo < hi) {
-                    const int mid = (lo + hi + 1) >> 1;
-                    if (a.seg_unit_begin[mid] <= u) lo = mid; else hi = mid - 1;
-                }
-                sg = lo; sub = a.seg_unit_begin[lo]; plo = a.seg_page_lo[lo]; toff = a.step.seq_meta[lo / Hkv].tbl_off;
-            }
-            const int h = sg % Hkv;
-            int phys = a.step.tables[toff + plo + (u - sub)];
-            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
-            rows[n % ROWS_CAP] = Q8 ? (phys * Hkv + h) : (phys * Hkv + h) * 32;  // record index, or first arena row
-        }
-    };
-    resolve_rows(0, min(ntiles, ROWS_CAP), tid, (C + 2) * 32);
-    __syncthreads();
-    if (tid == 0) stamp(a, 1);
+    volatile int* vflag = flag;
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        // The pages read here were written by earlier steps; only when the previous
-        // launch wrote this same layer must it be waited for.
+        // The pages read here were written by earlier steps; only when earlier work in the
+        // stream wrote this layer's pages or the unit_row array must it be waited for.
         if (a.kv_dep) pdl_wait();
         bool failed = false;
-        int issued_end = 0;
-        // this lane's stage and ring revolution, advanced by R per round (no division in the loop)
-        int p_st = lane % NS, p_rev = lane / NS;
-#pragma unroll 1
-        for (int base = 0; base < ntiles && !failed; base += R) {
-            if (base > 0 && base % ROWS_CAP == 0) {  // long ranges: next batch of rows (all tiles before `base` are issued)
-                __syncwarp();
-                resolve_rows(base, min(ntiles, base + ROWS_CAP), lane, 32);
-                __syncwarp();
-            }
-            const int n = base + lane;
-            if (lane < R && n < ntiles) {
-                const int st = p_st;
-                const int row0 = rows[n % ROWS_CAP];
-                if (n >= NS && !mbar_wait_bounded(empty0 + st * 8, (p_rev - 1) & 1)) failed = true;
-                if (!failed && Q8) {
-                    mbar_expect_tx(full0 + st * 8, UNIT);  // one box of UNIT/128 rows x 128 bytes = one record
-                    tma_load_2d(ring + st * UNIT, &tmap, 0, row0 * (int)(UNIT / 128u), full0 + st * 8);
-                } else if (!failed) {
-                    if (a.debug & 2) {  // measurement only: one unswizzled box per tile (math would be wrong)
-                        mbar_expect_tx(full0 + st * 8, UNIT);
-                        tma_load_2d(ring + st * UNIT, &tmap, 0, row0, full0 + st * 8);
-                    } else {
-                        issue_tile<D>(&tmap, ring + st * UNIT, full0 + st * 8, row0);
-                    }
+        const int rshift = NS < 8 ? 2 : 3;  // lanes per issue round (4 or 8): never more than the ring has stages
+        auto fetch = [&](int id) -> int4 {
+            return id < a.n_items ? __ldg(reinterpret_cast<const int4*>(a.items) + id) : make_int4(-1, -1, 0, 0);
+        };
+        // A claim is issued (one atomic by lane 0) when an item starts and picked up after the item's
+        // first round of copies is out, so the counter's round trip never holds up a copy.
+        auto claim_issue = [&]() -> int {
+            int v = 0;
+            if (lane == 0) v = a.n_ctas + atomicAdd(a.work_counters + a.work_slot, 1);
+            return v;
+        };
+        auto publish = [&](int j, int4 info) {
+            if (lane == 0) {
+                const int s = j & (QN - 1);
+                if (j >= QN && !mbar_wait_bounded(qempty0 + s * 8, ((j / QN) - 1) & 1, 4 * lim)) {
+                    failed = true;
+                } else {
+                    sts128(qitems0 + s * 16, info);
+                    mbar_arrive(qfull0 + s * 8);
                 }
             }
-            p_st += R;
-            if (p_st >= NS) { p_st -= NS; p_rev++; }  // R <= NS
             failed = __any_sync(0xffffffffu, failed);
-            if (!failed) issued_end = min(ntiles, base + R);
-            if (base == 0 && lane == 0) stamp(a, 2);
+        };
+        int raw = claim_issue();  // this CTA's second item
+        int4 cur = fetch(cta);
+        publish(0, cur);
+        int4 nxt = make_int4(-1, -1, 0, 0);
+        int j = 0, T = 0;  // items started, tile slots used (copies and the fillers between items)
+#pragma unroll 1
+        while (!failed) {
+            const int ub = cur.x, ntl = cur.y - cur.x;
+            bool to_publish = true;
+            int row_next = lane < ntl ? __ldcg(a.unit_row + ub + lane) : 0;
+#pragma unroll 1
+            for (int base = 0; base < ntl && !failed; base += 32) {
+                const int row = row_next;
+                if (base + 32 + lane < ntl) row_next = __ldcg(a.unit_row + ub + base + 32 + lane);
+                const int nb = min(32, ntl - base);
+                const int Tl = T + base + lane;
+                const int st = Tl % NS, rev = Tl / NS;
+                for (int r = 0; (r << rshift) < nb; r++) {
+                    if ((lane >> rshift) == r && lane < nb) {
+                        if (Tl >= NS && !mbar_wait_bounded(empty0 + st * 8, (rev - 1) & 1, lim)) {
+                            failed = true;
+                        } else if (!(cta == 0 && Tl == a.fault_tile)) {
+                            const int rec = row < 0 ? 0 : row;
+                            if constexpr (Q8) {
+                                mbar_expect_tx(full0 + st * 8, UNIT);  // one box of UNIT/128 rows x 128 bytes = one record
+                                tma_load_2d(ring + st * UNIT, &tmap, 0, rec * (int)(UNIT / 128u), full0 + st * 8);
+                            } else {
+                                issue_tile<D>(&tmap, ring + st * UNIT, full0 + st * 8, rec * 32);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    // The item after this one is published once the first round is out: that round only
+                    // needs stages of earlier items, whereas later rounds may need this item's own tiles
+                    // consumed, and its consumers may already be waiting for the queue entry.
+                    if (to_publish) {
+                        nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
+                        publish(j + 1, nxt);
+                        to_publish = false;
+                    }
+                }
+                failed = __any_sync(0xffffffffu, failed) || vflag[1] != 0;
+                if (j == 0 && base == 0 && lane == 0) CBKV_STAMP(2);
+            }
+            if (to_publish && !failed) {  // an item without tiles (the host never makes one)
+                nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
+                publish(j + 1, nxt);
+            }
+            T += ntl;
+            if (nxt.x < 0 || failed) break;  // the end marker is already in the queue
+            // Fillers: every item starts on a tile slot that is a multiple of C, so that a tile's consumer
+            // warp depends on its place in the item only and results do not depend on which CTA ran which
+            // item.  A filler slot carries no copy: its barrier is completed by a plain arrival.
+            const int pad = (C - T % C) % C;
+            if (pad) {
+                const int Tl = T + lane;
+                if (lane < pad) {
+                    const int st = Tl % NS, rev = Tl / NS;
+                    if (Tl >= NS && !mbar_wait_bounded(empty0 + st * 8, (rev - 1) & 1, lim)) failed = true;
+                    else mbar_arrive(full0 + st * 8);
+                }
+                failed = __any_sync(0xffffffffu, failed);
+                T += pad;
+            }
+            cur = nxt;
+            j++;
+            raw = claim_issue();
         }
-        if (lane == 0) stamp(a, 7);
-        if (failed) {
-            if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
-            // wait (bounded) for the copies still in flight before leaving
-            for (int n = max(0, issued_end - NS) + lane; n < issued_end; n += 32)
-                mbar_wait_bounded(full0 + (n % NS) * 8, (n / NS) & 1, 20000000ull);
+        if (lane == 0) CBKV_STAMP(7);
+        // Leave last: the stages of the final tiles are released by their consumers, which means the
+        // copies have landed.  After a failure nobody may be consuming, so the copies themselves are awaited.
+        {
+            const int from = max(0, T - NS);
+            bool bad = failed || vflag[1] != 0;
+            for (int n = from + lane; n < T && !bad; n += 32)
+                if (!mbar_wait_bounded(empty0 + (n % NS) * 8, (n / NS) & 1, 4 * lim)) bad = true;
+            bad = __any_sync(0xffffffffu, bad) || vflag[1] != 0;
+            if (bad) {
+                if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+                for (int n = from + lane; n < T; n += 32)
+                    if (!(cta == 0 && n == a.fault_tile)) mbar_wait_bounded(full0 + (n % NS) * 8, (n / NS) & 1, 20000000ull);
+            }
         }
         return;
     }
+
+    // consumers and merger: read entry j of the item queue (false: no more items, or a wait ran out)
+    bool failed = false;
+    auto get_item = [&](int j, int4& out) -> bool {
+        if (failed) return false;
+        const int s = j & (QN - 1);
+        if (!mbar_wait_bounded(qfull0 + s * 8, (j / QN) & 1, 4 * lim)) {
+            failed = true;
+            if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+            return false;
+        }
+        out = lds128(qitems0 + s * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(qempty0 + s * 8);
+        return out.x >= 0;
+    };
 
     const int n_rep = a.geo.n_rep;
     if (warp == C + 1) {
@@ -766,135 +856,187 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         // plus a ticket; the last ticket holder merges the segment's partials), and hands
         // the buffer back.  The consumers never wait on global memory.
         pdl_wait();  // out and the scratch are shared with earlier launches
-        int seg = first_seg, pb = u0, k = 0;
-        int dbg_merges = 0, dbg_parts = 0;
-        int deferred[4] = {0, 0, 0, 0}, n_deferred = 0;
-#pragma unroll 1
-        while (pb < u1) {
-            const int pe = min(u1, a.seg_unit_begin[seg + 1]);
-            const int b = seg / Hkv, h = seg - b * Hkv;
-            const int tok_off = a.step.seq_meta[b].tok_off;
-            const int nparts = a.seg_nparts[seg];
-            const int slot = nparts > 1 ? a.seg_part_base[seg] + (cta - a.seg_first_cta[seg]) : 0;
-            const int buf = NB == 2 ? (k & 1) : 0, use = NB == 2 ? (k >> 1) : k;
-            if (!mbar_wait_bounded(cfull0 + buf * 8, use & 1, 400000000ull)) {
-                if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
-                break;
+        if (cta == 0 && lane == 0) a.work_counters[(a.work_slot + 2) & 3] = 0;  // for the launch after the next one
+        // Only now may the next launch start: at most two launches are alive at a time, which is
+        // what lets four claim counters rotate.
+        pdl_launch_dependents();
+        int k = 0, kk = 0, n_deferred = 0;
+        // The ticket of a cut piece is drawn right after its partial is stored but looked at one piece
+        // later, so the counter's round trip overlaps the wait for the next piece.  A segment whose
+        // last ticket this CTA drew is merged at the end of the CTA by all its warps (the consumers
+        // are idle by then); only when the list is full does this warp merge alone.
+        int pend_seg = -1, pend_np = 0, pend_raw = 0;
+        auto settle = [&]() {
+            if (pend_seg < 0) return;
+            int last = 0;
+            if (lane == 0 && pend_raw == pend_np - 1) {
+                last = 1;
+                a.seg_counter[pend_seg] = 0;  // ready for the next launch
+                __threadfence();              // acquire the other parts
             }
-            if (pe >= u1 && lane == 0) stamp(a, 5);
-            const float* co = comb_o + (size_t)buf * C * ccols * D;
-            const float* cml = comb_ml + buf * C * 16;
-            uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
-            // lane owns 4 consecutive d-values (per pass of 128) of every query column
-            constexpr int PASSES = (D + 127) / 128;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                if (n_deferred < DEFER_CAP) {
+                    if (lane == 0) flag[4 + n_deferred] = pend_seg;
+                    n_deferred++;
+                } else {
+                    const int4* sp = reinterpret_cast<const int4*>(a.segs + pend_seg);
+                    const int4 x = __ldg(sp), y = __ldg(sp + 1);
+                    uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + ((size_t)x.w * a.geo.n_q + (size_t)(pend_seg % Hkv) * n_rep) * D;
+                    merge_parts<D, BF16>(a, y.y, y.x, orow, n_rep, lane, 32);
+                }
+            }
+            pend_seg = -1;
+        };
+#ifdef CBKV_MEASURE
+        int dbg_tiles = 0, dbg_cut = 0;
+#endif
+        int4 it;
+        bool have = get_item(0, it);
+#pragma unroll 1
+        while (have) {
+            int seg = it.z, pb = it.x;
+#pragma unroll 1
+            while (pb < it.y) {
+                const int4* sp = reinterpret_cast<const int4*>(a.segs + seg);
+                const int4 x = __ldg(sp), y = __ldg(sp + 1), z = __ldg(sp + 2);
+                const int pe = min(it.y, z.x);
+                const int h = seg % Hkv;
+                const int tok_off = x.w, nparts = y.x;
+                const int slot = nparts > 1 ? y.y + (seg == it.z ? it.w : 0) : 0;
+                const int buf = NB == 2 ? (kk & 1) : 0, use = NB == 2 ? (kk >> 1) : kk;
+                if (!mbar_wait_bounded(cfull0 + buf * 8, use & 1, 4 * lim)) {
+                    failed = true;
+                    if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+                    break;
+                }
+                if (lane == 0) CBKV_STAMP(5);
+                const float* co = comb_o + (size_t)buf * C * ccols * DP;
+                const float* cml = comb_ml + buf * C * 16;
+                uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
+                // lane owns 4 consecutive d-values (per pass of 128) of every query column
+                constexpr int PASSES = (D + 127) / 128;
 #pragma unroll
-            for (int ps = 0; ps < PASSES; ps++) {
-                const int j4 = ps * 32 + lane;  // float4 index within a row of D
-                if (j4 * 4 < D) {
+                for (int ps = 0; ps < PASSES; ps++) {
+                    const int j4 = ps * 32 + lane;  // float4 index within a row of D
+                    if (j4 * 4 < D) {
 #pragma unroll
-                    for (int col = 0; col < 8; col++) {
-                        if (col < n_rep) {
-                            float M = -INFINITY;
+                        for (int col = 0; col < 8; col++) {
+                            if (col < n_rep) {
+                                float M = -INFINITY;
 #pragma unroll
-                            for (int ww = 0; ww < C; ww++) M = fmaxf(M, cml[(ww * 8 + col) * 2]);
-                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                            float ls = 0.f;
+                                for (int ww = 0; ww < C; ww++) M = fmaxf(M, cml[(ww * 8 + col) * 2]);
+                                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                                float ls = 0.f;
 #pragma unroll
-                            for (int ww = 0; ww < C; ww++) {
-                                const float mw = cml[(ww * 8 + col) * 2];
-                                const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-                                const float4 v = *reinterpret_cast<const float4*>(co + ((size_t)ww * ccols + col) * D + j4 * 4);
-                                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
-                                ls += f * cml[(ww * 8 + col) * 2 + 1];
-                            }
-                            if (nparts == 1) {
-                                const float inv = 1.f / ls;
-                                uint2 pk;
-                                pk.x = pack2<BF16>(acc.x * inv, acc.y * inv);
-                                pk.y = pack2<BF16>(acc.z * inv, acc.w * inv);
-                                *reinterpret_cast<uint2*>(out_row + col * D + j4 * 4) = pk;
-                            } else {
-                                *reinterpret_cast<float4*>(a.part_o + ((size_t)slot * 8 + col) * D + j4 * 4) = acc;
-                                if (j4 == 0) *reinterpret_cast<float2*>(a.part_ml + ((size_t)slot * 8 + col) * 2) = make_float2(M, ls);
+                                for (int ww = 0; ww < C; ww++) {
+                                    const float mw = cml[(ww * 8 + col) * 2];
+                                    const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+                                    const float4 v = *reinterpret_cast<const float4*>(co + ((size_t)ww * ccols + col) * DP + j4 * 4);
+                                    acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+                                    ls += f * cml[(ww * 8 + col) * 2 + 1];
+                                }
+                                if (nparts == 1) {
+                                    const float inv = 1.f / ls;
+                                    uint2 pk;
+                                    pk.x = pack2<BF16>(acc.x * inv, acc.y * inv);
+                                    pk.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+                                    *reinterpret_cast<uint2*>(out_row + col * D + j4 * 4) = pk;
+                                } else {
+                                    *reinterpret_cast<float4*>(a.part_o + ((size_t)slot * 8 + col) * D + j4 * 4) = acc;
+                                    if (j4 == 0) *reinterpret_cast<float2*>(a.part_ml + ((size_t)slot * 8 + col) * 2) = make_float2(M, ls);
+                                }
                             }
                         }
                     }
                 }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(cempty0 + buf * 8);  // the consumers may store the next piece here
-            if (nparts > 1) {
-                int last = 0;
-                if (lane == 0) {
-                    __threadfence();  // the warp's partial (ordered before by __syncwarp) becomes visible before the ticket
-                    const int ticket = atomicAdd(a.seg_counter + seg, 1);
-                    last = ticket == nparts - 1;
-                    if (last) { a.seg_counter[seg] = 0; __threadfence(); }  // ready for the next launch; acquire the others' partials
+                __syncwarp();
+                if (lane == 0) mbar_arrive(cempty0 + buf * 8);  // the consumers may store the next piece here
+                settle();  // the previous cut piece's ticket has had a whole piece to come back
+                if (nparts > 1) {
+                    if (lane == 0) {
+                        __threadfence();  // the warp's partial (ordered before by __syncwarp) becomes visible before the ticket
+                        pend_raw = atomicAdd(a.seg_counter + seg, 1);
+                    }
+                    pend_seg = seg;
+                    pend_np = nparts;
+#ifdef CBKV_MEASURE
+                    dbg_cut++;
+#endif
                 }
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    dbg_merges++; dbg_parts += nparts;
-                    // Near the end of the CTA the merge is deferred: the consumer warps are idle then
-                    // and help (below).  With plenty of tiles still to stream this warp merges alone,
-                    // off the consumers' path, so the end of the CTA is not burdened with it.
-                    if (u1 - pe < 24 && n_deferred < 4) deferred[n_deferred++] = seg;
-                    else merge_parts<D, BF16>(a, a.seg_part_base[seg], nparts, out_row, n_rep, lane, 32);
-                }
+#ifdef CBKV_MEASURE
+                dbg_tiles += pe - pb;
+#endif
+                kk++;
+                seg++;
+                pb = pe;
             }
+            if (failed) break;
             k++;
-            seg++;
-            pb = pe;
+            have = get_item(k, it);
         }
-        // hand the deferred segments to the whole CTA
-        if (lane == 0) {
-            flag[2] = n_deferred;
-            for (int i = 0; i < 4; i++) flag[4 + i] = deferred[i];
-        }
+        settle();
+        // hand the segments to merge to the whole CTA
+        if (lane == 0) flag[2] = n_deferred;
         __syncwarp();
         consumer_sync((C + 1) * 32);
         for (int i = 0; i < n_deferred; i++) {
-            const int sg = deferred[i];
-            const int b = sg / Hkv, h = sg - b * Hkv;
-            uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
-                                ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
-            merge_parts<D, BF16>(a, a.seg_part_base[sg], a.seg_nparts[sg], out_row, n_rep, C * 32 + lane, (C + 1) * 32);
+            const int sg = flag[4 + i];
+            const int4* sp = reinterpret_cast<const int4*>(a.segs + sg);
+            const int4 x = __ldg(sp), y = __ldg(sp + 1);
+            uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)x.w * a.geo.n_q + (size_t)(sg % Hkv) * n_rep) * D;
+            merge_parts<D, BF16>(a, y.y, y.x, out_row, n_rep, C * 32 + lane, (C + 1) * 32);
         }
+#ifdef CBKV_MEASURE
         if (lane == 0) {
-            stamp(a, 6);
+            CBKV_STAMP(6);
             if ((a.debug & 4) && a.dbg_buf) {
                 unsigned smid;
                 asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-                a.dbg_buf[(size_t)blockIdx.x * 16 + 8] = (unsigned long long)k;
-                a.dbg_buf[(size_t)blockIdx.x * 16 + 9] = (unsigned long long)dbg_merges;
-                a.dbg_buf[(size_t)blockIdx.x * 16 + 10] = (unsigned long long)dbg_parts;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 8] = (unsigned long long)kk;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 9] = (unsigned long long)n_deferred;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 10] = (unsigned long long)dbg_cut;
                 a.dbg_buf[(size_t)blockIdx.x * 16 + 11] = (unsigned long long)smid;
-                a.dbg_buf[(size_t)blockIdx.x * 16 + 12] = (unsigned long long)ntiles;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 12] = (unsigned long long)dbg_tiles;
+                a.dbg_buf[(size_t)blockIdx.x * 16 + 13] = (unsigned long long)k;
             }
         }
+#endif
         return;
     }
 
     // ---------------------------------------------------------------- consumers
     const int cw = warp - 1, g = lane >> 2, t = lane & 3;
-    Piece cur = load_piece(a, first_seg);  // plan and block tables were uploaded by a copy: always visible
+    int4 it;
+    bool have = get_item(0, it);  // plan and block tables were uploaded by a copy: always visible
+    int seg = have ? it.z : 0, pb = have ? it.x : 0;
+    Piece cur = load_piece(a, seg);
     pdl_wait();  // q, k_new and v_new come from earlier work in the stream
     uint32_t qf[1][D / 16][2];
     if constexpr (Q8) load_q_frags_q8<D>(a, cur, g, t, qf);
     else load_q_frags<D>(a, cur, g, t, qf);
-    if (tid == 32) stamp(a, 3);
-    bool failed = false;
-    int seg = first_seg, pb = u0, k = 0;
+    if (tid == 32) CBKV_STAMP(3);
+    int k = 0, kk = 0, nbase = 0;  // items read, pieces handed over, tiles of the CTA before the current item
+#ifdef CBKV_MEASURE
     bool first_tile = true;
-    long long dbg_wait = 0, dbg_t0 = (a.debug & 4) ? clock64() : 0;  // measurement only
-    int dbg_tiles = 0;
+#endif
 #pragma unroll 1
-    while (pb < u1) {
-        const int pe = min(u1, cur.se);
+    while (have) {
+        const int pe = min(it.y, cur.se);
+        const bool more = pe < it.y;
+        // what comes next (the item's next segment, or the first piece of the next item): its
+        // metadata and queries arrive while this piece is processed
+        int4 nit = it;
+        bool nhave = true;
+        int nseg = seg + 1;
+        if (!more) {
+            nhave = get_item(k + 1, nit);
+            nseg = nit.z;
+        }
         Piece nxt = cur;
         uint32_t qf_next[1][D / 16][2];
-        const bool more = pe < u1;
-        if (more) {  // next piece's metadata and queries arrive while this one is processed
-            nxt = load_piece(a, seg + 1);
+        if (nhave) {
+            nxt = load_piece(a, nseg);
             if constexpr (Q8) load_q_frags_q8<D>(a, nxt, g, t, qf_next);
             else load_q_frags<D>(a, nxt, g, t, qf_next);
         }
@@ -903,27 +1045,32 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         for (int mt = 0; mt < D / 16; mt++) { o[0][mt][0] = o[0][mt][1] = o[0][mt][2] = o[0][mt][3] = 0.f; }
         const int qpos[1][2] = {{cur.q_pos, cur.q_pos}};
 
-        const int n0 = pb - u0;
-        const int u_first = pb + (cw - n0 % C + C) % C;
+        const int n0 = nbase + (pb - it.x);  // the piece's first tile, counted over the CTA's items
+        const int n1 = n0 + (pe - pb);
+        int T = n0 + (cw - n0 % C + C) % C;  // this warp's first tile of the piece
         // stage and revolution parity of this warp's tiles, advanced by C per tile (NS is a multiple of C)
-        int st = (u_first - u0) % NS, par = ((u_first - u0) / NS) & 1;
+        int st = T % NS, par = (T / NS) & 1;
 #pragma unroll 1
-        for (int u = u_first; u < pe; u += C, st += C) {
+        for (; T < n1; T += C, st += C) {
             if (st >= NS) { st -= NS; par ^= 1; }
             const uint32_t stage = ring + st * UNIT;
-            const long long tw0 = (a.debug & 4) ? clock64() : 0;
-            if (!failed && !mbar_wait_bounded(full0 + st * 8, par)) {
+            const int u = pb + (T - n0);
+            if (!failed && !mbar_wait_bounded(full0 + st * 8, par, lim)) {
                 failed = true;
                 if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
             }
-            if (a.debug & 4) { dbg_wait += clock64() - tw0; dbg_tiles++; }
-            if (first_tile && tid == 32) { stamp(a, 4); first_tile = false; }
+            // After a failure nothing is released any more: a stage given back before its copy has landed
+            // would be armed a second time.  The producer then finds its own wait running out and stops.
+            if (failed) break;
+#ifdef CBKV_MEASURE
+            if (first_tile && tid == 32) { CBKV_STAMP(4); first_tile = false; }
+#endif
             const int lp = cur.page_lo + (u - cur.sb);
-            if (!failed && !(a.debug & 1)) {
+            if (!CBKV_DBG(1)) {
                 if (!Q8 && a.k_new != nullptr && lp == cur.page_last) {
                     // fused append: put the new K/V row into the tile just fetched and into its page
                     const int slot = cur.q_pos & 15;
-                    const int phys = a.step.tables[cur.tbl_off + lp];
+                    const int rec = __ldcg(a.unit_row + u);
                     for (int c = lane; c < 2 * (D / 8); c += 32) {
                         int kv = c / (D / 8), j = c - kv * (D / 8);
                         const uint4 val = *(reinterpret_cast<const uint4*>(kv ? a.v_new : a.k_new) +
@@ -931,8 +1078,8 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                         uint32_t row = page_row(kv, slot, 16, true);
                         uint32_t addr = stage + (j >> 3) * 4096u + swz(row, j & 7);
                         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
-                        if (phys >= 0 && phys < a.geo.num_pages) {
-                            size_t drow = ((size_t)phys * Hkv + cur.h) * 32 + row;
+                        if (rec >= 0) {
+                            size_t drow = (size_t)rec * 32 + row;
                             reinterpret_cast<uint4*>(a.arena)[drow * (D / 8) + j] = val;
                         }
                     }
@@ -943,14 +1090,12 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 if constexpr (Q8) {
                     if (a.k_new != nullptr && lp == cur.page_last) {
                         // fused append: quantise the new K/V row into the tile just fetched and into its record
-                        const int phys = a.step.tables[cur.tbl_off + lp];
-                        if (phys >= 0 && phys < a.geo.num_pages) {
+                        const int rec = __ldcg(a.unit_row + u);
+                        if (rec >= 0) {
                             const size_t rowi = ((size_t)cur.tok_off * Hkv + cur.h) * D;
-                            q8_append_row<D, BF16>(stage, reinterpret_cast<uint8_t*>(a.arena) + ((size_t)phys * Hkv + cur.h) * UNIT,
+                            q8_append_row<D, BF16>(stage, reinterpret_cast<uint8_t*>(a.arena) + (size_t)rec * UNIT,
                                                    reinterpret_cast<const uint16_t*>(a.k_new) + rowi,
                                                    reinterpret_cast<const uint16_t*>(a.v_new) + rowi, cur.q_pos & 15, lane);
-                        } else if (lane == 0) {
-                            atomicOr(a.status, ST_BAD_PAGE);
                         }
                         fence_proxy_async();  // the stage is refilled by the copy engine later
                         __syncwarp();
@@ -959,7 +1104,11 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     q8_load<D>(stage, lane, regs);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty0 + st * 8);  // the tile is in registers: the stage may be refilled
+#ifdef CBKV_MEASURE
                     q8_attend<D, BF16>(regs, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane, a.debug);
+#else
+                    q8_attend<D, BF16>(regs, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
+#endif
                     continue;
                 }
                 attend_tile<D, 1, BF16>(stage, qf, o, m, l, lp * 16, qpos, a.window, a.scale_log2, need_mask, lane);
@@ -969,9 +1118,9 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         }
 
         // ---- hand this warp's state for the piece to the merger (double-buffered)
-        const int buf = NB == 2 ? (k & 1) : 0, use = NB == 2 ? (k >> 1) : k;
-        if (*reinterpret_cast<volatile int*>(flag + 1)) failed = true;  // another warp gave up: stop waiting
-        if (use >= 1 && !failed && !mbar_wait_bounded(cempty0 + buf * 8, (use - 1) & 1, 400000000ull)) {
+        const int buf = NB == 2 ? (kk & 1) : 0, use = NB == 2 ? (kk >> 1) : kk;
+        if (vflag[1] != 0) failed = true;  // another warp gave up: stop waiting
+        if (use >= 1 && !failed && !mbar_wait_bounded(cempty0 + buf * 8, (use - 1) & 1, 4 * lim)) {
             failed = true;
             if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
         }
@@ -981,20 +1130,20 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 8);
             l[0][j] += __shfl_xor_sync(0xffffffffu, l[0][j], 16);
         }
-        float* co = comb_o + ((size_t)buf * C + cw) * ccols * D;
+        float* co = comb_o + ((size_t)buf * C + cw) * ccols * DP;
         float* cml = comb_ml + (buf * C + cw) * 16;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
-            // the d-values behind rows g and g+8 of m-tile mt (permuted for quantised tiles, see attend_tile_q8)
+            // the d-values behind rows g and g+8 of m-tile mt (permuted for quantised tiles, see q8_attend)
             const int d0 = Q8 ? 32 * (mt >> 1) + 4 * g + 2 * (mt & 1) : mt * 16 + g;
             const int d1 = Q8 ? d0 + 1 : d0 + 8;
             if (2 * t < ccols) {
-                co[(2 * t) * D + d0] = o[0][mt][0];
-                co[(2 * t) * D + d1] = o[0][mt][2];
+                co[(2 * t) * DP + d0] = o[0][mt][0];
+                co[(2 * t) * DP + d1] = o[0][mt][2];
             }
             if (2 * t + 1 < ccols) {
-                co[(2 * t + 1) * D + d0] = o[0][mt][1];
-                co[(2 * t + 1) * D + d1] = o[0][mt][3];
+                co[(2 * t + 1) * DP + d0] = o[0][mt][1];
+                co[(2 * t + 1) * DP + d1] = o[0][mt][3];
             }
         }
         if (g == 0) {
@@ -1003,29 +1152,42 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(cfull0 + buf * 8);
-        k++;
-        seg++;
-        pb = pe;
+        kk++;
+        if (!nhave) break;
         if (more) {
-            cur = nxt;
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
+            pb = pe;
+        } else {
+            // the filler slots up to the next multiple of C (see the producer): this warp owns at most one
+            const int n_pad = (n1 + C - 1) / C * C;
+            const int Tp = n1 + (cw - n1 % C + C) % C;
+            if (Tp < n_pad) {
+                const int fs = Tp % NS;
+                if (!failed && !mbar_wait_bounded(full0 + fs * 8, (Tp / NS) & 1, lim)) {
+                    failed = true;
+                    if (lane == 0) { atomicOr(a.status, ST_WAIT_TIMEOUT); atomicExch(flag + 1, 1); }
+                }
+                __syncwarp();
+                if (lane == 0 && !failed) mbar_arrive(empty0 + fs * 8);
+            }
+            nbase = n_pad;
+            k++;
+            it = nit;
+            pb = it.x;
         }
-    }
-    if ((a.debug & 4) && a.dbg_buf && tid == 32) {  // measurement only: consumer 0's cycles waiting for tiles / in total / tiles
-        a.dbg_buf[(size_t)blockIdx.x * 16 + 13] = (unsigned long long)dbg_wait;
-        a.dbg_buf[(size_t)blockIdx.x * 16 + 14] = (unsigned long long)(clock64() - dbg_t0);
-        a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = (unsigned long long)dbg_tiles;
+        seg = nseg;
+        cur = nxt;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) { qf[0][ks][0] = qf_next[0][ks][0]; qf[0][ks][1] = qf_next[0][ks][1]; }
     }
     // idle now: help merge the segments whose last ticket this CTA drew
     consumer_sync((C + 1) * 32);
     const int n_deferred = flag[2];
     for (int i = 0; i < n_deferred; i++) {
         const int sg = flag[4 + i];
-        const int b = sg / Hkv, h = sg - b * Hkv;
-        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) +
-                            ((size_t)a.step.seq_meta[b].tok_off * a.geo.n_q + (size_t)h * n_rep) * D;
-        merge_parts<D, BF16>(a, a.seg_part_base[sg], a.seg_nparts[sg], out_row, n_rep, cw * 32 + lane, (C + 1) * 32);
+        const int4* sp = reinterpret_cast<const int4*>(a.segs + sg);
+        const int4 x = __ldg(sp), y = __ldg(sp + 1);
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(a.out) + ((size_t)x.w * a.geo.n_q + (size_t)(sg % Hkv) * n_rep) * D;
+        merge_parts<D, BF16>(a, y.y, y.x, out_row, n_rep, cw * 32 + lane, (C + 1) * 32);
     }
 }
 
@@ -1239,8 +1401,8 @@ template <> struct DecodeCfg<256> { static constexpr int C = 6, CTAS = 1; };
 
 static int decode_smem_bytes(int d, int consumers, int stages, int comb_cols, int comb_bufs, bool q8 = false) {
     const int unit = q8 ? (int)qrec_bytes(16, d) : 32 * d * 2;
-    return stages * unit + comb_bufs * (consumers * comb_cols * d * 4 + consumers * 16 * 4) + (2 * stages + 4) * 8 + 32 +
-           ROWS_CAP * 4 + SEG_CAP * 12;
+    return stages * unit + comb_bufs * (consumers * comb_cols * (d + 4) * 4 + consumers * 16 * 4) + QN * 16 +
+           (2 * stages + 4 + 2 * QN) * 8 + (4 + DEFER_CAP) * 4;
 }
 
 template <int D> struct ChunkCfg;
@@ -1383,6 +1545,14 @@ cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, 
         case 256: return bf16 ? launch_chunk_t<256, true>(map, a, st) : launch_chunk_t<256, false>(map, a, st);
         default: return cudaErrorInvalidValue;
     }
+}
+
+cudaError_t launch_resolve_units(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
+                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st) {
+    if (n_units <= 0) return cudaSuccess;
+    const int blocks = std::min((n_units + 255) / 256, 148 * 4);
+    resolve_units_kernel<<<blocks, 256, 0, st>>>(segs, n_segs, tables, n_kv, num_pages, unit_row, n_units, status);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st) {

@@ -64,7 +64,6 @@ struct LayerArena {
     bool quant = false;  // base holds quantised records, no tensor maps
     CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
     CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile)
-    CUtensorMap map_lin; // measurement only: box 32 rows x d elems, no swizzle
 };
 
 struct StepDev {
@@ -80,16 +79,11 @@ struct GeomDev {
 };
 
 struct DecodeArgs {
-    StepDev step;
     GeomDev geo;
-    const int32_t* seg_unit_begin;
-    const int32_t* seg_page_lo;
-    const int32_t* seg_first_cta;
-    const int32_t* seg_nparts;
-    const int32_t* seg_part_base;
-    const int32_t* cta_unit_begin;
-    const int32_t* cta_first_seg;
-    int32_t n_segs;
+    const SegInfo* segs;        // n_segs + 1 records (manager.hpp)
+    const ItemInfo* items;      // n_items work items in claim order; item c < n_ctas is CTA c's first
+    const int32_t* unit_row;    // per unit: page * n_kv + kv head (the record the tile lives in), -1 = bad table entry
+    int32_t n_segs, n_items, n_ctas;
     const void* q;
     void* out;
     const void* k_new;  // non-null: write the step's new row into its page and attend it (fused append)
@@ -97,16 +91,22 @@ struct DecodeArgs {
     void* arena;        // this layer's pages (for the fused append's global write)
     float* part_o;      // [n_parts][8][d] partial numerators
     float* part_ml;     // [n_parts][8][2] running max (log2 domain) and denominator
-    int32_t* seg_counter;
+    int32_t* seg_counter;    // per segment: tickets of the parts that are done (0 between launches)
+    int32_t* work_counters;  // four claim counters; launch i uses slot i % 4 and clears slot (i + 2) % 4
+    int32_t work_slot;
     int32_t* status;
     int32_t window;
     float scale_log2;
     int32_t n_stages;   // stages of the CTA's TMA ring
     int32_t comb_cols;  // query columns kept in the merge buffers (n_rep rounded up to even)
     int32_t comb_bufs;  // 1 or 2 merge buffers
-    int32_t kv_dep;     // 1: the previous launch in the stream wrote this layer's pages
-    unsigned long long* dbg_buf;  // measurement only: per-CTA timestamps
-    int32_t debug;      // measurement switches (0 in production): 1 = skip the math, 2 = one linear box per tile
+    int32_t kv_dep;     // 1: earlier work in the stream wrote this layer's pages or unit_row: the producer waits for it
+    uint32_t wait_us;   // limit of every bounded wait on a tile, microseconds
+    int32_t fault_tile; // test hook: the copy of this tile of CTA 0 is never issued (-1 = none), so its consumer's wait runs out
+#ifdef CBKV_MEASURE
+    unsigned long long* dbg_buf;  // per-CTA timestamps
+    int32_t debug;                // 1 = skip the math, 4 = timestamps, 32/64/128 = skip phases of the int8 tile
+#endif
 };
 
 struct ChunkArgs {
@@ -120,7 +120,9 @@ struct ChunkArgs {
     int32_t window;
     float scale_log2;
     int32_t rep_slots;  // tcgen05 kernel: q heads per kv head rounded up to a power of two (rows per token in a tile)
-    unsigned long long* dbg_buf;  // measurement only: per-CTA cycle counters of the tcgen05 kernel
+#ifdef CBKV_MEASURE
+    unsigned long long* dbg_buf;  // per-CTA cycle counters of the tcgen05 kernel
+#endif
 };
 
 struct AppendArgs {
@@ -174,6 +176,9 @@ cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_cta
                           bool q8 = false);  // q8: the layer holds int8 records, `map` is the byte view with one record per box
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
+// unit_row of a decode plan from its segments and the step's block tables (once per step and window)
+cudaError_t launch_resolve_units(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
+                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st);
 cudaError_t launch_init_quant(void* arena, size_t n_records, int page_size, int d, cudaStream_t st);
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_dequant_pages(const int32_t* tables, int n_entries, const GeomDev& geo, const void* arena, void* scratch,

@@ -9,6 +9,9 @@ namespace cbkv {
 
 static thread_local std::string g_err;
 void set_error(const std::string& msg) { g_err = msg; }
+void set_error_nothrow(const char* msg) noexcept {
+    try { g_err = msg; } catch (...) { g_err.clear(); }  // clear() cannot throw
+}
 const char* last_error() { return g_err.c_str(); }
 
 void Allocator::init(int64_t n) {
@@ -111,11 +114,13 @@ int32_t begin_step(Arena* a, Seq* const* seqs, const int64_t* new_tokens, const 
     if (!a || (n > 0 && (!seqs || !new_tokens)) || n < 0) { set_error("null argument"); return CBKV_ERR_ARG; }
     const int64_t P = a->cfg.page_size;
     int64_t pages_wanted = 0, tokens = 0;
+    const uint64_t mark = ++a->mark_gen;  // a sequence seen in this call carries the call's mark
     // validate everything first: state is only mutated when the whole step fits
     for (int32_t b = 0; b < n; b++) {
         Seq* s = seqs[b];
         if (!s || s->arena != a) { set_error("sequence does not belong to this arena"); return CBKV_ERR_ARG; }
-        for (int32_t c = 0; c < b; c++) if (seqs[c] == s) { set_error("sequence listed twice in one step"); return CBKV_ERR_ARG; }
+        if (s->mark == mark) { set_error("sequence listed twice in one step"); return CBKV_ERR_ARG; }
+        s->mark = mark;
         if (new_tokens[b] < 1) { set_error("new_tokens must be >= 1"); return CBKV_ERR_ARG; }
         if (pos && pos[b] != s->seq_len) {  // kv.rs:671-674
             set_error("paged cache expects dense contiguous appends (pos == seq_len)"); return CBKV_ERR_POS;
@@ -218,14 +223,13 @@ void page_stats(const Seq* s, int64_t layers_materialized, cbkv_page_stats_t* ou
     out->layers_sliding = 0;  // windows are masks over pages here; no rolling stores exist
 }
 
-void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, DecodePlan* pl) {
+void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, const DecodeSplit& split, DecodePlan* pl) {
     const int64_t P = a.cfg.page_size;
     const int Hkv = a.cfg.n_kv_heads;
     const int n = (int)a.step_meta.size();
     pl->window = window;
     pl->n_segs = n * Hkv;
-    pl->seg_unit_begin.assign((size_t)pl->n_segs + 1, 0);
-    pl->seg_page_lo.assign((size_t)pl->n_segs, 0);
+    pl->segs.assign((size_t)pl->n_segs + 1, SegInfo{});
     int64_t units = 0;
     for (int b = 0; b < n; b++) {
         const SeqMeta& m = a.step_meta[(size_t)b];
@@ -234,41 +238,79 @@ void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, DecodePla
         int64_t lo_key = window > 0 ? std::max<int64_t>(0, q_pos - window + 1) : 0;  // keys in (p - w, p], kv.rs:112-115
         int64_t p_lo = lo_key / P, p_hi = q_pos / P;
         for (int h = 0; h < Hkv; h++) {
-            size_t s = (size_t)b * Hkv + h;
-            pl->seg_unit_begin[s] = (int32_t)units;
-            pl->seg_page_lo[s] = (int32_t)p_lo;
+            SegInfo& sg = pl->segs[(size_t)b * Hkv + h];
+            sg.unit_begin = (int32_t)units;
+            sg.page_lo = (int32_t)p_lo;
+            sg.q_pos = (int32_t)q_pos;
+            sg.tok_off = m.tok_off;
+            sg.nparts = 0;
+            sg.part_base = -1;
+            sg.tbl_off = m.tbl_off;
             units += p_hi - p_lo + 1;
         }
     }
-    pl->seg_unit_begin[(size_t)pl->n_segs] = (int32_t)units;
+    pl->segs[(size_t)pl->n_segs].unit_begin = (int32_t)units;
     pl->n_units = (int32_t)units;
     n_ctas = (int32_t)std::max<int64_t>(1, std::min<int64_t>(n_ctas, units));
     pl->n_ctas = n_ctas;
-    pl->cta_unit_begin.resize((size_t)n_ctas + 1);
-    for (int g = 0; g <= n_ctas; g++) pl->cta_unit_begin[(size_t)g] = (int32_t)(units * g / n_ctas);
-    pl->cta_first_seg.assign((size_t)n_ctas, 0);
-    pl->seg_first_cta.assign((size_t)pl->n_segs, 0);
-    pl->seg_nparts.assign((size_t)pl->n_segs, 1);
-    pl->seg_part_base.assign((size_t)pl->n_segs, -1);
-    // sweep segments and CTAs together (both are sorted by unit index)
-    int g = 0, parts = 0;
+
+    // Levels of the tail, decided on the shortest range so that every range has the same number of items.
+    const int64_t lmin = units / n_ctas;
+    int levels = 1;
+    {
+        const int64_t tail = lmin * split.tail_pct / 100;
+        if (split.min_item > 0 && tail >= split.min_item) {
+            int pieces = 1;
+            while (pieces + 1 < split.max_levels && (tail >> pieces) >= split.min_item) pieces++;
+            levels = 1 + pieces;
+        }
+    }
+    pl->levels = levels;
+    pl->n_items = n_ctas * levels;
+    pl->items.assign((size_t)pl->n_items, ItemInfo{});
+    // item (level j, range c) sits at claim index j * n_ctas + c; inside a range the levels follow each other
+    for (int c = 0; c < n_ctas; c++) {
+        const int64_t rb = units * c / n_ctas, re = units * (c + 1) / n_ctas;
+        const int64_t len = re - rb;
+        int64_t rest = levels > 1 ? len * split.tail_pct / 100 : 0;
+        int64_t at = rb;
+        for (int j = 0; j < levels; j++) {
+            int64_t take;
+            if (j == 0) take = len - rest;
+            else if (j == levels - 1) take = rest;
+            else take = (rest + 1) / 2;
+            if (j > 0) rest -= take;
+            ItemInfo& it = pl->items[(size_t)j * n_ctas + c];
+            it.u_begin = (int32_t)at;
+            it.u_end = (int32_t)(at + take);
+            at += take;
+        }
+    }
+    // parts of every segment: sweep the items in unit order (range by range, level by level)
+    std::vector<int32_t> order;
+    order.reserve((size_t)pl->n_items);
+    for (int c = 0; c < n_ctas; c++)
+        for (int j = 0; j < levels; j++)
+            if (pl->items[(size_t)j * n_ctas + c].u_end > pl->items[(size_t)j * n_ctas + c].u_begin) order.push_back(j * n_ctas + c);
+    size_t io = 0;
+    int parts = 0;
     for (int s = 0; s < pl->n_segs; s++) {
-        int32_t sb = pl->seg_unit_begin[(size_t)s], se = pl->seg_unit_begin[(size_t)s + 1];
-        if (se == sb) { pl->seg_first_cta[(size_t)s] = g; pl->seg_nparts[(size_t)s] = 0; continue; }
-        while (pl->cta_unit_begin[(size_t)g + 1] <= sb) g++;
-        int first = g, last = g;
-        while (pl->cta_unit_begin[(size_t)last + 1] < se) last++;
-        pl->seg_first_cta[(size_t)s] = first;
-        pl->seg_nparts[(size_t)s] = last - first + 1;
-        if (last > first) { pl->seg_part_base[(size_t)s] = parts; parts += last - first + 1; }
+        SegInfo& sg = pl->segs[(size_t)s];
+        const int32_t sb = sg.unit_begin, se = pl->segs[(size_t)s + 1].unit_begin;
+        if (se == sb) continue;
+        while (io < order.size() && pl->items[(size_t)order[io]].u_end <= sb) io++;
+        int cnt = 0;
+        for (size_t k = io; k < order.size() && pl->items[(size_t)order[k]].u_begin < se; k++) {
+            ItemInfo& it = pl->items[(size_t)order[k]];
+            if (it.u_begin >= sb) { it.first_seg = s; it.first_part = cnt; }
+            cnt++;
+        }
+        sg.nparts = cnt;
+        if (cnt > 1) { sg.part_base = parts; parts += cnt; }
     }
     pl->n_parts = parts;
-    int s = 0;
-    for (int c = 0; c < n_ctas; c++) {
-        int32_t ub = pl->cta_unit_begin[(size_t)c];
-        while (s < pl->n_segs && pl->seg_unit_begin[(size_t)s + 1] <= ub) s++;
-        pl->cta_first_seg[(size_t)c] = std::min(s, pl->n_segs - 1);
-    }
+    for (ItemInfo& it : pl->items)  // empty items (possible only when units < items) are never claimed usefully
+        if (it.u_end <= it.u_begin) { it.first_seg = 0; it.first_part = 0; }
 }
 
 void build_chunk_plan(const Arena& a, int32_t cols_per_item, ChunkPlan* pl) {

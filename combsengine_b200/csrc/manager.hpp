@@ -1,9 +1,11 @@
 // Host-side cache manager: free-list, per-sequence block tables, refcounts, the
 // per-step bookkeeping of the reference's `attention_opts` prologue, and the work
 // partition handed to the kernels.  No CUDA in this file; the device side lives in
-// device.cu.  Reference: engine/core/combs-models/src/kv.rs (lines cited inline).
+// api.cu.  Reference: engine/core/combs-models/src/kv.rs (lines cited inline).
 #pragma once
 #include <cstdint>
+#include <exception>
+#include <new>
 #include <string>
 #include <vector>
 
@@ -13,7 +15,39 @@ namespace cbkv {
 
 // Thread-local error text (combs-ffi/src/lib.rs:41-58).
 void set_error(const std::string& msg);
+void set_error_nothrow(const char* msg) noexcept;
 const char* last_error();
+
+// Every extern "C" entry point runs its body through one of these: a C++ exception (std::bad_alloc
+// from a container, anything a callee throws) becomes CBKV_ERR_INTERNAL plus a message and never
+// crosses the C boundary, where it would end the host process.  The reference's FFI wraps every
+// entry point in catch_unwind for the same reason (combs-ffi/src/lib.rs:143,173-183).
+template <typename F>
+inline int32_t fenced(F&& body) noexcept {
+    try {
+        return body();
+    } catch (const std::bad_alloc&) {
+        set_error_nothrow("out of host memory");
+    } catch (const std::exception& e) {
+        set_error_nothrow(e.what());
+    } catch (...) {
+        set_error_nothrow("unknown C++ exception");
+    }
+    return CBKV_ERR_INTERNAL;
+}
+template <typename F>
+inline int64_t fenced64(F&& body) noexcept {
+    try {
+        return body();
+    } catch (const std::bad_alloc&) {
+        set_error_nothrow("out of host memory");
+    } catch (const std::exception& e) {
+        set_error_nothrow(e.what());
+    } catch (...) {
+        set_error_nothrow("unknown C++ exception");
+    }
+    return CBKV_ERR_INTERNAL;
+}
 
 // PageAllocator (kv.rs:417-446): a stack of page ids.
 class Allocator {
@@ -40,6 +74,7 @@ struct Seq {
     Arena* arena = nullptr;
     std::vector<int64_t> table;  // logical page -> physical page (kv.rs:481)
     int64_t seq_len = 0;
+    uint64_t mark = 0;           // begin_step's duplicate check
 };
 
 // Per-sequence record the kernels read (16 bytes).
@@ -50,21 +85,37 @@ struct SeqMeta {
     int32_t tbl_off;  // offset of this sequence's block table in the flat table array
 };
 
-// Split of one decode launch over `n_ctas` CTAs.  A unit is one (sequence, kv head,
-// visible page); a segment is all units of one (sequence, kv head).  CTAs get equal
-// contiguous unit ranges, so a segment may be cut into several parts whose partial
-// results are merged by the last CTA to finish one.
+// Work split of one decode launch.  A unit is one (sequence, kv head, visible page); a
+// segment is all units of one (sequence, kv head).  The units are first divided into one
+// contiguous range per CTA; each range is then cut into a large head item and a tail of
+// items of decreasing size.  CTA c starts with head item c and afterwards claims items from
+// a device counter in list order (larger tail items first), so that CTAs on slower SMs
+// simply take fewer of them.  A segment cut by item boundaries leaves partial results that
+// the last item to finish one merges.
+struct SegInfo {        // 32 bytes, read by the kernels as two 16-byte words
+    int32_t unit_begin; // first unit of the segment (entry n_segs holds n_units)
+    int32_t page_lo;    // first visible logical page
+    int32_t q_pos;      // absolute position of the sequence's decode query
+    int32_t tok_off;    // index of the sequence's token in the packed q / k / v / out
+    int32_t nparts;     // items that intersect the segment
+    int32_t part_base;  // slot of part 0 in the partial buffers (-1: the segment is not cut)
+    int32_t tbl_off;    // offset of the sequence's block table in the flat table array
+    int32_t pad;
+};
+struct ItemInfo {       // 16 bytes
+    int32_t u_begin, u_end;  // unit range
+    int32_t first_seg;       // segment that holds u_begin
+    int32_t first_part;      // index of the item's first piece among that segment's parts
+};
 struct DecodePlan {
     int64_t window = 0;
-    int32_t n_ctas = 0, n_segs = 0, n_units = 0, n_parts = 0;
-    std::vector<int32_t> seg_unit_begin;  // n_segs + 1
-    std::vector<int32_t> seg_page_lo;     // first visible logical page of the segment
-    std::vector<int32_t> seg_first_cta;   // n_segs
-    std::vector<int32_t> seg_nparts;      // n_segs
-    std::vector<int32_t> seg_part_base;   // n_segs, slot of part 0 in the partial buffer
-    std::vector<int32_t> cta_unit_begin;  // n_ctas + 1
-    std::vector<int32_t> cta_first_seg;   // n_ctas
+    int32_t n_ctas = 0, n_items = 0, n_segs = 0, n_units = 0, n_parts = 0, levels = 0;
+    std::vector<SegInfo> segs;    // n_segs + 1
+    std::vector<ItemInfo> items;  // n_items, in claim order: item c (c < n_ctas) is CTA c's first
 };
+// How the tail of a CTA's range is cut: `tail_pct` percent of the range, halved `levels - 1`
+// times while the pieces stay >= min_item units.
+struct DecodeSplit { int32_t tail_pct = 25, min_item = 0, max_levels = 5; };  // min_item 0: no tail, a static equal split
 
 // Work list of the chunk (prefill) kernel: one item per (sequence, kv head, block of
 // query columns); a column is one (new token, q head of the kv group).
@@ -81,6 +132,7 @@ struct Arena {
     Allocator alloc;
     std::vector<int32_t> refcnt;
     std::vector<Seq*> seqs;  // live sequences
+    uint64_t mark_gen = 0;
 
     // the step in flight
     bool step_open = false;
@@ -91,7 +143,7 @@ struct Arena {
     int64_t step_tokens = 0;
     uint64_t step_id = 0;
 
-    void* dev = nullptr;  // device-side state (device.cu), created on first device use
+    void* dev = nullptr;  // device-side state (api.cu), created on first device use
 
     int n_rep() const { return cfg.n_q_heads / cfg.n_kv_heads; }
     // int8 pages: asked for, head_dim a multiple of the 32-value group, and not a layer with a window of
@@ -112,7 +164,7 @@ int32_t reset(Seq* s);
 void page_stats(const Seq* s, int64_t layers_materialized, cbkv_page_stats_t* out);
 
 // Builders used by the device layer (pure functions of the step state).
-void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, DecodePlan* plan);
+void build_decode_plan(const Arena& a, int64_t window, int32_t n_ctas, const DecodeSplit& split, DecodePlan* plan);
 void build_chunk_plan(const Arena& a, int32_t cols_per_item, ChunkPlan* plan);
 // Work list of the tcgen05 chunk kernel: one item per (sequence, kv head, tile of
 // `tokens_per_tile` new tokens); `cols_per_item` records tokens_per_tile.

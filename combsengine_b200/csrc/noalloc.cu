@@ -8,7 +8,7 @@
 // caller already owns the KV pages and the block tables; all this entry point still
 // needs is the decode kernel's working memory (work split, per-segment tickets,
 // partial results).  Here that working memory is a fixed array that is part of the
-// library image, so every GPU that loads the library pays for it once (about 4 MB)
+// library image, so every GPU that loads the library pays for it once (about 10 MB)
 // and nothing is ever allocated or freed.
 //
 // Consequences of the fixed array:
@@ -20,7 +20,9 @@
 //     them) would write the same array and corrupt each other: keep calls on one
 //     stream or order them yourself;
 //   - the first call on a device looks the array's address up and raises the kernel's
-//     shared-memory limit; make that first call before starting any stream capture.
+//     shared-memory limit; make that first call before starting any stream capture;
+//   - the kernel's status word (a bad block-table entry, a wait that ran out) lives in the
+//     same array and is cleared by every call: read it with cbkv_static_status afterwards.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -36,20 +38,22 @@ using namespace cbkv;
 namespace {
 
 // ---- limits of the static working memory
-constexpr int kMaxSeqs = 128;      // sequences per call
-constexpr int kMaxSegs = 1024;     // sequences x kv heads
-constexpr int kMaxCtas = 296;      // CTAs the work is split over
-constexpr int kMaxParts = 512;     // partial results (segments cut across CTAs)
+constexpr int kMaxSeqs = 128;        // sequences per call
+constexpr int kMaxSegs = 1024;       // sequences x kv heads
+constexpr int kMaxItems = 296 * 8;   // work items the launch is cut into
+constexpr int kMaxParts = 1024;      // partial results (segments cut across items)
+constexpr int kMaxUnits = 1 << 18;   // (sequence, kv head, visible page) triples
 constexpr int kMaxHeadDim = 256;
 
 // ---- layout of the array (byte offsets, all multiples of 256)
-constexpr size_t kOffStatus = 0;                                             // 1 int
-constexpr size_t kOffCounters = 256;                                         // kMaxSegs ints, must be 0 at launch
-constexpr size_t kOffMeta = kOffCounters + kMaxSegs * 4;                     // kMaxSeqs SeqMeta
-constexpr size_t kOffPlan = kOffMeta + kMaxSeqs * sizeof(SeqMeta);           // the seven plan arrays
-constexpr size_t kPlanInts = 5 * (kMaxSegs + 1) + 2 * (kMaxCtas + 1);
-constexpr size_t kOffPartMl = (kOffPlan + kPlanInts * 4 + 255) / 256 * 256;  // kMaxParts x 8 x 2 floats
-constexpr size_t kOffPartO = kOffPartMl + (size_t)kMaxParts * 16 * 4;        // kMaxParts x 8 x head_dim floats
+constexpr size_t kOffStatus = 0;                                              // 1 int
+constexpr size_t kOffWork = 64;                                               // 4 claim counters, 0 at launch
+constexpr size_t kOffCounters = 256;                                          // kMaxSegs tickets, 0 at launch
+constexpr size_t kOffSegs = kOffCounters + kMaxSegs * 4;                      // kMaxSegs + 1 segment records
+constexpr size_t kOffItems = (kOffSegs + (kMaxSegs + 1) * sizeof(SegInfo) + 255) / 256 * 256;  // item records
+constexpr size_t kOffUnits = (kOffItems + kMaxItems * sizeof(ItemInfo) + 255) / 256 * 256;     // kMaxUnits ints
+constexpr size_t kOffPartMl = kOffUnits + (size_t)kMaxUnits * 4;              // kMaxParts x 8 x 2 floats
+constexpr size_t kOffPartO = kOffPartMl + (size_t)kMaxParts * 16 * 4;         // kMaxParts x 8 x head_dim floats
 constexpr size_t kScratchBytes = kOffPartO + (size_t)kMaxParts * 8 * kMaxHeadDim * 4;
 
 // The working memory itself.  In host code this name is only a handle for
@@ -106,6 +110,7 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
                                                 int32_t table_stride, const int32_t* seq_lens_host, int32_t n_seqs,
                                                 int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
                                                 const void* q, void* out, double scale, int64_t window, void* stream) {
+    return fenced([&]() -> int32_t {
     if (!kv_pages || !block_tables || !seq_lens_host || !q || !out) return fail(CBKV_ERR_ARG, "null argument");
     if (n_seqs < 1 || n_q_heads < 1 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || num_pages < 1 || table_stride < 1)
         return fail(CBKV_ERR_ARG, "invalid geometry");
@@ -138,43 +143,50 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
     }
     const DecodeConfig dc = decode_config(head_dim, n_rep, 0, 0, 0);
     DecodePlan pl;
-    int n_ctas = std::min(kMaxCtas, pd->sm_count * dc.ctas_per_sm);
+    DecodeSplit split;
+    int n_ctas = pd->sm_count * dc.ctas_per_sm;
     for (;;) {
-        build_decode_plan(tmp, window, n_ctas, &pl);
+        build_decode_plan(tmp, window, n_ctas, split, &pl);
         const int want = std::max(1, (pl.n_units + dc.consumers - 1) / dc.consumers);
-        if (want < pl.n_ctas) build_decode_plan(tmp, window, want, &pl);
-        if (pl.n_parts <= kMaxParts || n_ctas == 1) break;
-        n_ctas = std::max(1, n_ctas / 2);  // fewer CTAs, fewer cuts
+        if (want < pl.n_ctas) build_decode_plan(tmp, window, want, split, &pl);
+        if ((pl.n_parts <= kMaxParts && pl.n_items <= kMaxItems) || (n_ctas == 1 && split.min_item == 0)) break;
+        if (split.min_item != 0) split.min_item = 0;  // first give up the dynamically claimed tail items,
+        else n_ctas = std::max(1, n_ctas / 2);        // then CTAs: fewer cuts either way
     }
-    if (pl.n_parts > kMaxParts) return fail(CBKV_ERR_ARG, "too many partial results for the static working memory");
-
-    // one block of ints: sequence records, then the seven plan arrays
-    std::vector<int32_t> flat;
-    auto push = [&](const std::vector<int32_t>& v) { size_t o = flat.size(); flat.insert(flat.end(), v.begin(), v.end()); return o; };
-    const size_t o0 = push(pl.seg_unit_begin), o1 = push(pl.seg_page_lo), o2 = push(pl.seg_first_cta), o3 = push(pl.seg_nparts),
-                 o4 = push(pl.seg_part_base), o5 = push(pl.cta_unit_begin), o6 = push(pl.cta_first_seg);
-    if (flat.size() > kPlanInts) return fail(CBKV_ERR_ARG, "work split does not fit the static working memory");
+    if (pl.n_parts > kMaxParts || pl.n_items > kMaxItems)
+        return fail(CBKV_ERR_ARG, "too many partial results for the static working memory");
+    if (pl.n_units > kMaxUnits)
+        return fail(CBKV_ERR_ARG, "too large for the static working memory: at most " + std::to_string(kMaxUnits) +
+                                      " (sequence, kv head, page) triples per call");
 
     unsigned char* S = pd->scratch;
     cudaError_t e;
-    // what must start at zero: the status word and the per-segment tickets
-    e = cudaMemsetAsync(S + kOffStatus, 0, kOffMeta - kOffStatus, st);
+    // what must start at zero: the status word, the claim counters and the per-segment tickets
+    e = cudaMemsetAsync(S + kOffStatus, 0, kOffSegs - kOffStatus, st);
     if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
-    e = cudaMemcpyAsync(S + kOffMeta, tmp.step_meta.data(), tmp.step_meta.size() * sizeof(SeqMeta), cudaMemcpyHostToDevice, st);
+    e = cudaMemcpyAsync(S + kOffSegs, pl.segs.data(), pl.segs.size() * sizeof(SegInfo), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaMemcpyAsync: ") + cudaGetErrorString(e));
-    e = cudaMemcpyAsync(S + kOffPlan, flat.data(), flat.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st);
+    e = cudaMemcpyAsync(S + kOffItems, pl.items.data(), pl.items.size() * sizeof(ItemInfo), cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaMemcpyAsync: ") + cudaGetErrorString(e));
     // the host vectors go out of scope on return: the copies above come from pageable
     // memory, which the runtime stages before returning
+    const SegInfo* segs = reinterpret_cast<const SegInfo*>(S + kOffSegs);
+    int32_t* unit_row = reinterpret_cast<int32_t*>(S + kOffUnits);
+    int32_t* status = reinterpret_cast<int32_t*>(S + kOffStatus);
+    e = launch_resolve_units(segs, pl.n_segs, block_tables, n_kv_heads, (int)num_pages, unit_row, pl.n_units, status, st);
+    if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("launch: ") + cudaGetErrorString(e));
 
     // tensor map over the caller's pages: rows = pages x kv heads x 32, box 32 rows x 64 elements, 128-byte swizzle
     static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void* fp = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fp, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
-            return fail(CBKV_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
-        encode = reinterpret_cast<EncodeTiledFn>(fp);
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!encode) {
+            void* fp = nullptr;
+            cudaDriverEntryPointQueryResult qr;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fp, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
+                return fail(CBKV_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+            encode = reinterpret_cast<EncodeTiledFn>(fp);
+        }
     }
     CUtensorMap map;
     {
@@ -188,27 +200,48 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
         if (r != CUDA_SUCCESS) return fail(CBKV_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
     }
 
-    const int32_t* plan = reinterpret_cast<const int32_t*>(S + kOffPlan);
     DecodeArgs args{};
-    args.step.seq_meta = reinterpret_cast<const SeqMeta*>(S + kOffMeta);
-    args.step.tables = block_tables;
-    args.step.n_seqs = n_seqs;
-    args.step.n_tokens = n_seqs;
     args.geo = GeomDev{n_q_heads, n_kv_heads, n_rep, head_dim, 16, (int32_t)num_pages, 1};
-    args.seg_unit_begin = plan + o0; args.seg_page_lo = plan + o1; args.seg_first_cta = plan + o2; args.seg_nparts = plan + o3;
-    args.seg_part_base = plan + o4; args.cta_unit_begin = plan + o5; args.cta_first_seg = plan + o6;
-    args.n_segs = pl.n_segs;
+    args.segs = segs;
+    args.items = reinterpret_cast<const ItemInfo*>(S + kOffItems);
+    args.unit_row = unit_row;
+    args.n_segs = pl.n_segs; args.n_items = pl.n_items; args.n_ctas = pl.n_ctas;
     args.q = q; args.out = out; args.k_new = nullptr; args.v_new = nullptr; args.arena = nullptr;
     args.part_o = reinterpret_cast<float*>(S + kOffPartO);
     args.part_ml = reinterpret_cast<float*>(S + kOffPartMl);
     args.seg_counter = reinterpret_cast<int32_t*>(S + kOffCounters);
-    args.status = reinterpret_cast<int32_t*>(S + kOffStatus);
+    args.work_counters = reinterpret_cast<int32_t*>(S + kOffWork);
+    args.work_slot = 0;
+    args.status = status;
     args.window = (int32_t)window;
     args.scale_log2 = (float)(scale * 1.4426950408889634);
     args.n_stages = dc.stages; args.comb_cols = dc.comb_cols; args.comb_bufs = dc.comb_bufs;
     args.kv_dep = 1;  // the pages are the caller's: assume the previous work in the stream wrote them
-    args.dbg_buf = nullptr; args.debug = 0;
+    args.wait_us = 100000; args.fault_tile = -1;
     e = launch_decode(map, args, pl.n_ctas, dc.consumers, dc.smem_bytes, /*pdl=*/false, dtype == CBKV_BF16, st);
     if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("launch: ") + cudaGetErrorString(e));
     return CBKV_OK;
+    });
+}
+
+// Reads and clears the status word of the entry point above on the current device.  Waits for
+// `stream`; allocates nothing (one 4-byte copy each way).
+extern "C" int32_t cbkv_static_status(void* stream, int32_t* status) {
+    return fenced([&]() -> int32_t {
+    if (!status) return fail(CBKV_ERR_ARG, "null argument");
+    *status = 0;
+    PerDevice* pd = nullptr;
+    int32_t rc = setup_current_device(&pd);
+    if (rc) return rc;
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
+    e = cudaMemcpy(status, pd->scratch + kOffStatus, sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(e));
+    if (*status) {
+        e = cudaMemset(pd->scratch + kOffStatus, 0, sizeof(int32_t));
+        if (e != cudaSuccess) return fail(CBKV_ERR_CUDA, std::string("cudaMemset: ") + cudaGetErrorString(e));
+        return fail(CBKV_ERR_DEVICE, "kernel status word = " + std::to_string(*status));
+    }
+    return CBKV_OK;
+    });
 }

@@ -164,9 +164,16 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     }
 }
 
-// measurement only: cycle counters per role, 16 slots per CTA
-#define TC_T0() const long long t0__ = a.dbg_buf ? clock64() : 0
+// Cycle counters per role, 16 slots per CTA: measurement build only (-DCBKV_MEASURE).
+#ifdef CBKV_MEASURE
+#define TC_NOW() clock64()
 #define TC_ACC(var) do { if (a.dbg_buf) { const long long t1__ = clock64(); var += t1__ - tprev; tprev = t1__; } } while (0)
+#define TC_DUMP(...) do { if (a.dbg_buf) { __VA_ARGS__ } } while (0)
+#else
+#define TC_NOW() 0ll
+#define TC_ACC(var) do { (void)var; (void)tprev; } while (0)
+#define TC_DUMP(...) do { } while (0)
+#endif
 
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
@@ -264,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
         // threads (below the Q load); every lane issues one box of a tile: lane = page * (2 XB) +
         // column block * 2 + (K or V).
         bool ok = true;
-        long long tprev = clock64(), c_wait = 0, c_issue = 0;
+        long long tprev = TC_NOW(), c_wait = 0, c_issue = 0;
 #pragma unroll 1
         for (int j = 0; j < n_tiles && ok; j++) {
             const int st = j & 1;
@@ -287,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             }
             if (lane == 0) TC_ACC(c_issue);
         }
-        if (a.dbg_buf && lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; }
+        TC_DUMP(if (lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; });
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -308,7 +315,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 }
                 umma_commit(b_s_full + (j & 1) * 8);
             };
-            long long tprev = clock64(), c_wkv = 0, c_wp = 0, c_iss = 0;
+            long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0;
             bool ok = mbar_wait_bounded(b_kv_full, 0);
             if (ok) { tc_fence_after(); issue_qk(0); }
             for (int j = 0; ok && j < n_tiles; j++) {
@@ -337,7 +344,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 umma_commit(b_o_done);
             }
             if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
-            if (a.dbg_buf) { a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss; }
+            TC_DUMP(a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss;);
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue, one row per thread
@@ -352,7 +359,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
         // f16/bf16 with f32 sums, and O needs rescaling only on those rare moves.
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        long long tprev = clock64(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
+        long long tprev = TC_NOW(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
         const long long tstart = tprev;
 #pragma unroll 1
         for (int j = 0; j < n_tiles; j++) {
@@ -439,10 +446,11 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             mbar_arrive(b_p_full);
             TC_ACC(c_st);
         }
-        if (a.dbg_buf && tid == 64) {
+        TC_DUMP(if (tid == 64) {
             unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16;
-            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = clock64() - tstart;
-        }
+            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = TC_NOW() - tstart;
+        });
+        (void)tstart; (void)c_wo;
         // ---- epilogue: O / l -> out
         if (ok) ok = mbar_wait_bounded(b_o_done, (n_tiles - 1) & 1) && !*failed;
         ok = __all_sync(0xffffffffu, ok);
@@ -594,7 +602,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         bool ok = true;
-        long long tprev = clock64(), c_wait = 0, c_issue = 0;
+        long long tprev = TC_NOW(), c_wait = 0, c_issue = 0;
 #pragma unroll 1
         for (int j = 0; j < n_tiles && ok; j++) {
             const int st = j & 1;
@@ -616,7 +624,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             }
             if (lane == 0) TC_ACC(c_issue);
         }
-        if (a.dbg_buf && lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; }
+        TC_DUMP(if (lane == 0) { a.dbg_buf[(size_t)blockIdx.x * 16 + 0] = c_wait; a.dbg_buf[(size_t)blockIdx.x * 16 + 1] = c_issue; a.dbg_buf[(size_t)blockIdx.x * 16 + 15] = n_tiles; });
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -641,7 +649,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                     umma_ts(tmem + 256 + X * 128, tmem + X * 128 + ks * 8, dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv, (j > 0 || ks > 0));
                 umma_commit(b_o_done + X * 8);
             };
-            long long tprev = clock64(), c_wkv = 0, c_wp = 0, c_iss = 0;
+            long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0;
             bool ok = mbar_wait_bounded(b_kv_full, 0);
             if (ok) { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
             for (int j = 0; ok && j < n_tiles; j++) {
@@ -669,7 +677,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                 if (j + 1 < n_tiles) issue_qk(1, j + 1);
             }
             if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
-            if (a.dbg_buf) { a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss; }
+            TC_DUMP(a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss;);
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue of tile X
@@ -684,7 +692,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
         const uint32_t tS = tmem + X * 128 + lane_addr, tO = tmem + 256 + X * 128 + lane_addr;
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        long long tprev = clock64(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
+        long long tprev = TC_NOW(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
         const long long tstart = tprev;
 #pragma unroll 1
         for (int j = 0; j < n_tiles; j++) {
@@ -754,10 +762,11 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             mbar_arrive(b_p_full + X * 8);
             TC_ACC(c_st);
         }
-        if (a.dbg_buf && tid == 64) {
+        TC_DUMP(if (tid == 64) {
             unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16;
-            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = clock64() - tstart;
-        }
+            b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = TC_NOW() - tstart;
+        });
+        (void)tstart; (void)c_wo;
         if (ok) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {

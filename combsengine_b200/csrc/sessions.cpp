@@ -58,6 +58,7 @@ void json_string(std::string& out, const std::string& s) {
 extern "C" {
 
 int32_t cbkv_sessions_create(cbkv_arena* arena, int32_t max_sessions, cbkv_sessions** out) {
+    return fenced([&]() -> int32_t {
     if (!arena || !out) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (max_sessions < 0) { set_error("max_sessions must be >= 0 (0 = the default of 4)"); return CBKV_ERR_ARG; }
     auto* s = new SessionSet();
@@ -65,18 +66,22 @@ int32_t cbkv_sessions_create(cbkv_arena* arena, int32_t max_sessions, cbkv_sessi
     if (max_sessions > 0) s->max_sessions = max_sessions;
     *out = reinterpret_cast<cbkv_sessions*>(s);
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_sessions_destroy(cbkv_sessions* set) {
+    return fenced([&]() -> int32_t {
     auto* s = reinterpret_cast<SessionSet*>(set);
     if (!s) return CBKV_OK;
     for (auto& kv : s->map) cbkv_seq_destroy(kv.second.seq);
     delete s;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_sessions_acquire(cbkv_sessions* set, const char* key, const uint32_t* prompt, int64_t n_prompt,
                               int32_t reuse, cbkv_seq** seq_out, int64_t* lcp_out) {
+    return fenced([&]() -> int32_t {
     auto* s = reinterpret_cast<SessionSet*>(set);
     if (!s || !seq_out || !lcp_out || (n_prompt > 0 && !prompt)) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (n_prompt < 1) { set_error("empty prompt"); return CBKV_ERR_ARG; }  // engine.rs:1235-1237
@@ -110,10 +115,12 @@ int32_t cbkv_sessions_acquire(cbkv_sessions* set, const char* key, const uint32_
     }
     *seq_out = seq;
     return CBKV_OK;
+    });
 }
 
 int32_t cbkv_sessions_release(cbkv_sessions* set, const char* key, cbkv_seq* seq, const uint32_t* history,
                               int64_t n_history, int32_t reuse) {
+    return fenced([&]() -> int32_t {
     auto* s = reinterpret_cast<SessionSet*>(set);
     if (!s || !seq || (n_history > 0 && !history)) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (!reuse) return cbkv_seq_destroy(seq);  // the cache of a request outside the session table is dropped
@@ -142,36 +149,46 @@ int32_t cbkv_sessions_release(cbkv_sessions* set, const char* key, cbkv_seq* seq
         s->evictions++;
     }
     return CBKV_OK;
+    });
 }
 
-int32_t cbkv_sessions_clear(cbkv_sessions* set, int64_t* removed) {  // clear_all, engine.rs:287-291
+int32_t cbkv_sessions_clear(cbkv_sessions* set, int64_t* removed) {
+    return fenced([&]() -> int32_t {  // clear_all, engine.rs:287-291
     auto* s = reinterpret_cast<SessionSet*>(set);
     if (!s) { set_error("null argument"); return CBKV_ERR_ARG; }
     if (removed) *removed = (int64_t)s->map.size();
     for (auto& kv : s->map) cbkv_seq_destroy(kv.second.seq);
     s->map.clear();
     return CBKV_OK;
+    });
 }
 
 int64_t cbkv_sessions_count(const cbkv_sessions* set) {
+    return fenced64([&]() -> int64_t {
     auto* s = reinterpret_cast<const SessionSet*>(set);
     return s ? (int64_t)s->map.size() : 0;
+    });
 }
 
 int64_t cbkv_sessions_evictions(const cbkv_sessions* set) {
+    return fenced64([&]() -> int64_t {
     auto* s = reinterpret_cast<const SessionSet*>(set);
     return s ? (int64_t)s->evictions : 0;
+    });
 }
 
 int64_t cbkv_sessions_history_len(const cbkv_sessions* set, const char* key) {
+    return fenced64([&]() -> int64_t {
     auto* s = reinterpret_cast<const SessionSet*>(set);
     if (!s) return -1;
     auto it = s->map.find(key ? key : "");
     return it == s->map.end() ? -1 : (int64_t)it->second.history.size();
+    });
 }
 
 int32_t cbkv_spec_verify_rollback(cbkv_seq* seq, const uint32_t* draft, const uint32_t* argmax, int32_t k,
                                   int32_t* accepted_out, uint32_t* correction_out) {
+    return fenced([&]() -> int32_t {
     if (!seq || !draft || !argmax || !accepted_out || !correction_out || k < 0) { set_error("null argument"); return CBKV_ERR_ARG; }
     int32_t accepted = 0;
     while (accepted < k && argmax[accepted] == draft[accepted]) accepted++;  // engine.rs:1476-1479
@@ -188,9 +205,11 @@ int32_t cbkv_spec_verify_rollback(cbkv_seq* seq, const uint32_t* draft, const ui
         }
     }
     return CBKV_OK;
+    });
 }
 
 int64_t cbkv_sessions_stats_json(const cbkv_sessions* set, char* buf, int64_t cap) {
+    return fenced64([&]() -> int64_t {
     auto* s = reinterpret_cast<const SessionSet*>(set);
     if (!s) { set_error("null argument"); return CBKV_ERR_ARG; }
     const Arena* a = reinterpret_cast<const Arena*>(s->arena);
@@ -231,6 +250,6 @@ int64_t cbkv_sessions_stats_json(const cbkv_sessions* set, char* buf, int64_t ca
         buf[n] = 0;
     }
     return (int64_t)o.size();
+    });
 }
-
 }  // extern "C"

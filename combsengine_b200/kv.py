@@ -312,22 +312,39 @@ class KVArena:
         CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128)."""
         check(self._lib.cbkv_set_chunk_kernel(self._h, mode))
 
-    def debug_decode_plan(self, window: int, n_ctas: int) -> dict:
-        cap = 8 + 2 * n_ctas + 8 * (self.n_kv_heads * 4096 + 8)
+    def set_decode_split(self, tail_pct: int = -1, min_item: int = -1, max_levels: int = -1) -> None:
+        """How a CTA's share of a decode launch is cut into a head item and dynamically claimed tail items
+        (percent of the share, smallest item in pages with 0 = no tail, levels); negative = keep."""
+        check(self._lib.cbkv_set_decode_split(self._h, tail_pct, min_item, max_levels))
+
+    def debug_set_wait_limit(self, wait_us: int = 0, fault_tile: int = -1) -> None:
+        """Test hook: limit of the decode kernel's bounded waits, and a tile of CTA 0 whose copy is withheld."""
+        check(self._lib.cbkv_debug_set_wait_limit(self._h, wait_us, fault_tile))
+
+    def debug_decode_plan(self, window: int, n_ctas: int, tail_pct: int = -1, min_item: int = -1) -> dict:
+        """The decode work split of the step in flight (host only): counts, `segs` [n_segs + 1, 8] and
+        `items` [n_items, 4] in claim order (see include/combs_kv.h for the columns)."""
+        cap = 1 << 20
         buf = (C.c_int32 * cap)()
-        n = self._lib.cbkv_debug_decode_plan(self._h, window, n_ctas, buf, cap)
+        n = self._lib.cbkv_debug_decode_plan(self._h, window, n_ctas, tail_pct, min_item, buf, cap)
         if n < 0 or n > cap:
             raise CbkvError(-6, "no step in flight or plan too large")
         a = np.frombuffer(buf, dtype=np.int32, count=n).copy()
-        n_ctas, n_segs, n_units, n_parts = (int(x) for x in a[:4])
-        o = 4
-        out = {"n_ctas": n_ctas, "n_segs": n_segs, "n_units": n_units, "n_parts": n_parts}
-        for name, ln in (("cta_unit_begin", n_ctas + 1), ("seg_unit_begin", n_segs + 1), ("seg_page_lo", n_segs),
-                         ("seg_first_cta", n_segs), ("seg_nparts", n_segs), ("seg_part_base", n_segs),
-                         ("cta_first_seg", n_ctas)):
-            out[name] = a[o:o + ln]
-            o += ln
-        return out
+        n_ctas, n_items, n_segs, n_units, n_parts, levels = (int(x) for x in a[:6])
+        segs = a[6:6 + (n_segs + 1) * 8].reshape(n_segs + 1, 8)
+        items = a[6 + (n_segs + 1) * 8:].reshape(n_items, 4)
+        return {"n_ctas": n_ctas, "n_items": n_items, "n_segs": n_segs, "n_units": n_units, "n_parts": n_parts,
+                "levels": levels, "segs": segs, "items": items}
+
+
+def static_status(stream: Optional[torch.cuda.Stream] = None) -> int:
+    """Status word of the last ``decode_attention_static`` call on the current device (0 = clean); waits for
+    the stream, clears the word, allocates nothing."""
+    st = C.c_int32(0)
+    rc = _lib.load().cbkv_static_status(_stream_ptr(stream), C.byref(st))
+    if rc not in (0, -7):
+        check(rc)
+    return st.value
 
 
 def decode_attention_static(kv_pages: torch.Tensor, block_tables: torch.Tensor, seq_lens: Sequence[int],

@@ -8,8 +8,11 @@
  *
  * Conventions (those of the reference's own C ABI, combs-ffi/src/lib.rs:41-71):
  *   - opaque handles, plain pointers and sizes, no C++ or torch types;
- *   - every call returns int32_t: 0 = ok, negative = error; nothing aborts;
- *     on error the cache state is untouched (all-or-nothing, kv.rs:805-806);
+ *   - every call returns int32_t: 0 = ok, negative = error; nothing aborts: no C++
+ *     exception leaves the library (each entry point catches them, as the reference's FFI
+ *     wraps every entry point in catch_unwind, combs-ffi/src/lib.rs:143,173-183), and a
+ *     null handle is an error, not a crash; on error the cache state is untouched
+ *     (all-or-nothing, kv.rs:805-806);
  *   - cbkv_last_error() is thread-local, borrowed, valid until the next call on
  *     the same thread; it carries the reference's panic texts verbatim;
  *   - handles are not thread-safe (the trait is Send, not Sync): one owner
@@ -43,7 +46,9 @@ enum {
     CBKV_ERR_ARG = -4,       /* bad argument / bad geometry (kv.rs:513-516)     */
     CBKV_ERR_CUDA = -5,      /* a CUDA runtime or driver call failed            */
     CBKV_ERR_STATE = -6,     /* call out of order (no step begun, layer mismatch) */
-    CBKV_ERR_DEVICE = -7     /* a kernel reported a problem in its status word   */
+    CBKV_ERR_DEVICE = -7,    /* a kernel reported a problem in its status word   */
+    CBKV_ERR_INTERNAL = -8   /* a C++ exception was stopped at the boundary (the reference's FFI turns a
+                                panic into rc = -1 plus the message, combs-ffi/src/lib.rs:173-183) */
 };
 
 enum { CBKV_F16 = 0, CBKV_BF16 = 1 };
@@ -244,20 +249,28 @@ int64_t cbkv_sessions_stats_json(const cbkv_sessions* set, char* buf, int64_t ca
  * callers that must not allocate device memory while they run (a server that gave
  * the whole GPU to its own pool at start-up, a plugin inside a host that forbids
  * late allocations): nothing is allocated or freed, the kernel's working memory is a
- * fixed ~4 MB array inside the library image.  Limits: at most 128 sequences and
- * 1024 sequence x kv-head pairs per call, head_dim 64/128/256, at most 8 q heads per
- * kv head, 16-token pages; larger problems return CBKV_ERR_ARG.
+ * fixed ~6 MB array inside the library image.  Limits: at most 128 sequences,
+ * 1024 sequence x kv-head pairs and 524288 (sequence, kv head, visible page) triples per
+ * call, head_dim 64/128/256, at most 8 q heads per kv head, 16-token pages; larger problems
+ * return CBKV_ERR_ARG.
  *   kv_pages      device, one layer's pages [num_pages][n_kv][2 (slots 0-7, 8-15)][2 (K,V)][8][head_dim]
  *   block_tables  device, [n_seqs][table_stride] physical page ids
  *   seq_lens_host HOST, [n_seqs]: cached tokens including the one being decoded
  *   q, out        device, [n_seqs][n_q][head_dim]
  * All calls on a device share the working memory: calls that overlap on the GPU
  * race, so keep them on one stream or order them.  The first call on a device does a
- * one-time set-up and should be made before any stream capture begins. */
+ * one-time set-up and should be made before any stream capture begins.  The kernel reports a
+ * bad block-table entry or a wait that ran out in a status word inside the same array, which
+ * every call clears at its start: read it with cbkv_static_status after the call. */
 int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t num_pages, const int32_t* block_tables,
                                      int32_t table_stride, const int32_t* seq_lens_host, int32_t n_seqs,
                                      int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
                                      const void* q, void* out, double scale, int64_t window, void* stream);
+
+/* No counterpart in the reference.  Waits for `stream`, then reads and clears the status word
+ * of the static entry point on the current device (same bits as cbkv_device_status); allocates
+ * nothing.  A non-zero word returns CBKV_ERR_DEVICE with *status set. */
+int32_t cbkv_static_status(void* stream, int32_t* status);
 
 /* ---- rollback / reset / counters ----------------------------------------- */
 
@@ -297,7 +310,10 @@ int32_t cbkv_page_refcount(const cbkv_arena* arena, int64_t page);
 /* ---- diagnostics ----------------------------------------------------------- */
 
 /* Reads and clears the status word the kernels write instead of trapping
- * (0 = clean).  Synchronises `stream`. */
+ * (0 = clean; bits: 1 = a block-table entry outside the arena, which the kernels replace by
+ * page 0 for reading and skip for writing; 2 = a bounded wait ran out; 4 = misaligned shared
+ * memory).  Synchronises `stream`.  A caller should poll it at least once per step: after a
+ * non-zero status the step's outputs are undefined; the next cbkv_begin_step starts clean. */
 int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status);
 /* Kernel launches issued by this library in this process so far. */
 int64_t cbkv_launch_count(void);
@@ -325,11 +341,33 @@ int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode);
  * kv.rs:665-683 itself): lets the manager be exercised where no GPU exists. */
 int32_t cbkv_debug_begin_step_host(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens,
                                    const int64_t* pos, int32_t n_seqs);
+/* The boundary's own test: the body throws (1 = std::bad_alloc, 2 = std::runtime_error, 3 = a non-standard
+ * object, anything else = nothing) and the call must come back with CBKV_ERR_INTERNAL and a message, as a
+ * panic behind the reference's FFI comes back as rc = -1 (combs-ffi/src/lib.rs:173-183). */
+int32_t cbkv_debug_raise(int32_t kind);
+
 /* The decode work split for the step in flight, flattened into `out`:
- * [n_ctas, n_segs, n_units, n_parts, cta_unit_begin(n_ctas+1), seg_unit_begin(n_segs+1),
- *  seg_page_lo, seg_first_cta, seg_nparts, seg_part_base (n_segs each), cta_first_seg(n_ctas)].
+ * [n_ctas, n_items, n_segs, n_units, n_parts, levels, segment records (n_segs + 1 of 8 ints:
+ *  unit_begin, page_lo, q_pos, tok_off, nparts, part_base, tbl_off, 0), item records (n_items of
+ *  4 ints: u_begin, u_end, first_seg, first_part) in claim order].  tail_pct / min_item: how the
+ * tail of a CTA's range is cut into dynamically claimed items (negative = default).
  * Returns the number of words, or -1 without a step. */
-int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t* out, int64_t cap);
+int64_t cbkv_debug_decode_plan(cbkv_arena* arena, int64_t window, int32_t n_ctas, int32_t tail_pct, int32_t min_item,
+                               int32_t* out, int64_t cap);
+
+/* Tuning (no reference counterpart): the share of a CTA's range that is cut into dynamically
+ * claimed tail items (percent), the smallest item (pages; 0 = no tail, a static equal split) and
+ * the number of halvings + 2.  Negative / < 2 = keep. */
+int32_t cbkv_set_decode_split(cbkv_arena* arena, int32_t tail_pct, int32_t min_item, int32_t max_levels);
+
+/* Test hook for the kernels' failure path (the reference has no device-side failure path; its
+ * host-side one is the panic fence above).  wait_us > 0 replaces the limit of the decode
+ * kernel's bounded waits (default 100000 us).  fault_tile >= 0: the producer of CTA 0 never
+ * issues the copy of that tile, so the wait of the warp that owns it runs out: the launch
+ * returns, ST_WAIT_TIMEOUT (2) shows in cbkv_device_status, its output is undefined, and the
+ * next step runs normally.  fault_tile = -1 switches the hook off.  Nothing is read or written
+ * outside the kernel's own buffers either way. */
+int32_t cbkv_debug_set_wait_limit(cbkv_arena* arena, int64_t wait_us, int32_t fault_tile);
 
 #ifdef __cplusplus
 }

@@ -215,8 +215,10 @@ def test_manager_matches_oracle_on_random_histories(seed):
     random_history(seed)
 
 
-@pytest.mark.parametrize("window,n_ctas", [(0, 1), (0, 7), (0, 296), (0, 5000), (100, 13), (1024, 296), (17, 64)])
-def test_decode_plan_covers_every_page_once(window, n_ctas):
+@pytest.mark.parametrize("window,n_ctas,tail_pct,min_item", [(0, 1, -1, -1), (0, 7, -1, -1), (0, 148, -1, -1), (0, 148, 40, 4),
+                                                              (0, 296, 25, 0), (0, 5000, -1, -1), (100, 13, -1, -1),
+                                                              (1024, 148, -1, 2), (17, 64, -1, -1)])
+def test_decode_plan_covers_every_page_once(window, n_ctas, tail_pct, min_item):
     rng = np.random.default_rng(window + n_ctas)
     a = KVArena(1, 28, 4, 128, 5000, 16, 20000)
     seqs = [a.new_seq() for _ in range(24)]
@@ -225,32 +227,51 @@ def test_decode_plan_covers_every_page_once(window, n_ctas):
     a.begin_step_host_only(seqs, [n - 1 for n in lens])   # the cached prefix
     a.begin_step_host_only(seqs, [1] * len(seqs))         # the decode step being split
     L = [s.seq_len() for s in seqs]
-    pl = a.debug_decode_plan(window, n_ctas)
+    pl = a.debug_decode_plan(window, n_ctas, tail_pct, min_item)
     Hkv = 4
-    assert pl["n_segs"] == len(seqs) * Hkv
-    cub, sub = pl["cta_unit_begin"], pl["seg_unit_begin"]
-    assert cub[0] == 0 and cub[-1] == pl["n_units"] == sub[-1]
-    assert np.all(np.diff(cub) >= 0) and np.diff(cub).max() - np.diff(cub).min() <= 1  # balanced to one page
-    parts = 0
+    segs, items = pl["segs"], pl["items"]
+    assert pl["n_segs"] == len(seqs) * Hkv and pl["n_items"] == pl["n_ctas"] * pl["levels"]
+    sub = segs[:, 0]
+    assert sub[0] == 0 and sub[-1] == pl["n_units"]
+    # segments: the visible pages of every (sequence, kv head)
+    tok = 0
     for b, n in enumerate(L):
         q = n - 1
         lo = max(0, q - window + 1) if window else 0
         for h in range(Hkv):
             s = b * Hkv + h
-            assert pl["seg_page_lo"][s] == lo // 16
+            assert segs[s, 1] == lo // 16 and segs[s, 2] == q and segs[s, 3] == tok
             assert sub[s + 1] - sub[s] == q // 16 - lo // 16 + 1
-            first = np.searchsorted(cub, sub[s], side="right") - 1
-            last = np.searchsorted(cub, sub[s + 1] - 1, side="right") - 1
-            assert pl["seg_first_cta"][s] == first
-            assert pl["seg_nparts"][s] == last - first + 1
-            if last > first:
-                assert pl["seg_part_base"][s] == parts
-                parts += last - first + 1
+        tok += 1
+    # items: non-empty, disjoint, and together exactly the units
+    assert np.all(items[:, 1] > items[:, 0])
+    order = np.argsort(items[:, 0], kind="stable")
+    srt = items[order]
+    assert srt[0, 0] == 0 and srt[-1, 1] == pl["n_units"] and np.array_equal(srt[1:, 0], srt[:-1, 1])
+    # claim order: a CTA's first item is the head of its range, and later levels never grow
+    G, J = pl["n_ctas"], pl["levels"]
+    size = (items[:, 1] - items[:, 0]).reshape(J, G)
+    if J > 1:
+        assert size[0].min() >= size[1:].max()
+        assert np.all(size[1:-1].min(axis=1) + 1 >= size[2:].max(axis=1)) if J > 2 else True
+    per_range = size.sum(axis=0)
+    assert per_range.max() - per_range.min() <= 1  # balanced to one page before any claiming
+    # parts: every segment knows how many items touch it, and every item its place among them
+    parts = 0
+    for s in range(pl["n_segs"]):
+        touching = [i for i in order if items[i, 0] < sub[s + 1] and items[i, 1] > sub[s]]
+        assert segs[s, 4] == len(touching)
+        if len(touching) > 1:
+            assert segs[s, 5] == parts
+            parts += len(touching)
+        else:
+            assert segs[s, 5] == -1
+        for rank, i in enumerate(touching):
+            if sub[s] <= items[i, 0] < sub[s + 1]:
+                assert items[i, 2] == s and items[i, 3] == rank
+            else:
+                assert rank == 0  # an item that runs into a segment from before it is that segment's part 0
     assert parts == pl["n_parts"]
-    for g in range(pl["n_ctas"]):
-        s = pl["cta_first_seg"][g]
-        if cub[g] < cub[g + 1]:
-            assert sub[s] <= cub[g] < sub[s + 1]
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour on a machine without a GPU")

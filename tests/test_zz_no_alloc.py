@@ -5,7 +5,9 @@ allocate device memory while they run; it keeps the kernel's working memory in a
 fixed array inside the library.  This file is collected last on purpose: if it
 fails, a run that stops at the first failure has already run everything else.
 The same pages are given to both entry points and two calls are made in a row,
-because the second call reuses whatever the first left in the shared array.
+because the second call reuses whatever the first left in the shared array.  The
+output is also compared with the CPU oracle directly, and the entry point's own
+status word (which lives in the shared array) is read after every call.
 """
 import numpy as np
 import pytest
@@ -18,7 +20,8 @@ pytestmark = pytest.mark.gpu
 
 def test_static_decode_matches_regular_entry_point_twice_in_a_row():
     from combsengine_b200 import KVArena
-    from combsengine_b200.kv import decode_attention_static
+    from combsengine_b200.kv import decode_attention_static, static_status
+    from oracle import OracleContiguous
 
     n_q, n_kv, d, num_pages = 28, 4, 128, 600
     rng = np.random.default_rng(0xA110C)
@@ -62,17 +65,42 @@ def test_static_decode_matches_regular_entry_point_twice_in_a_row():
 
     out = torch.empty(len(seqs) * n_q * d, dtype=torch.float16, device="cuda")
     for call, (scale, window) in enumerate([(d ** -0.5, None), (0.07, 200)]):
-        q = pk([rng.standard_normal((n_q, 1, d)).astype(np.float16) for _ in prefix])
+        qs = [rng.standard_normal((n_q, 1, d)).astype(np.float16) for _ in prefix]
+        q = pk(qs)
         ref = arena.paged_attention(0, q, scale, window).cpu().numpy()
         torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info()[0]
         decode_attention_static(pages, bt, lens, n_q, n_kv, d, q, out, scale, window)
-        torch.cuda.synchronize()
+        assert static_status() == 0, "the static entry point's own status word"
         if call > 0:  # the first call makes the driver load the module that holds the fixed array
             assert torch.cuda.mem_get_info()[0] >= free_before, "the entry point must not allocate device memory"
         got = out.cpu().numpy()
-        assert_attention_close(got, ref, f"static decode, call {call}")
+        assert_attention_close(got, ref, f"static decode vs the regular entry point, call {call}")
+        # and against the oracle itself: the reference's contiguous cache fed the same tokens (kv.rs:360-415)
+        want = []
+        for b, n in enumerate(prefix):
+            c = OracleContiguous(1, n_kv, d, dtype="f16")
+            c.attention_opts(0, np.zeros((n_q, n, d), np.float16), kpre[b], vpre[b], 0, scale, window)
+            want.append(c.attention_opts(0, qs[b], knew[b], vnew[b], n, scale, window).reshape(-1))
+        assert_attention_close(got, np.concatenate(want), f"static decode vs the oracle, call {call}")
     assert arena.device_status() == 0
+
+
+def test_static_decode_reports_a_bad_block_table_entry_in_its_own_status_word():
+    # a page id outside the caller's pages: the kernel reads page 0 instead, finishes, and says so
+    from combsengine_b200.kv import decode_attention_static, static_status
+
+    n_q, n_kv, d, num_pages = 8, 2, 128, 16
+    pages = torch.randn(num_pages, n_kv, 2, 2, 8, d, device="cuda").half()
+    bt = torch.tensor([[3, 5, num_pages + 7, 1], [2, 4, 6, 8]], dtype=torch.int32, device="cuda")
+    q = torch.randn(2 * n_q * d, device="cuda").half()
+    out = decode_attention_static(pages, bt, [60, 50], n_q, n_kv, d, q)
+    assert static_status() == 1  # ST_BAD_PAGE, and the word is cleared by the read
+    assert static_status() == 0
+    assert torch.isfinite(out.float()).all()
+    bt[0, 2] = 9
+    decode_attention_static(pages, bt, [60, 50], n_q, n_kv, d, q)
+    assert static_status() == 0
 
 
 def test_static_decode_refuses_sizes_beyond_its_working_memory():
