@@ -125,6 +125,7 @@ struct DeviceState {
 #ifdef CBKV_MEASURE
     unsigned long long* dbg_buf = nullptr;  // per-CTA timestamps / cycle counters of the last launch
     int dbg_ctas = 0;
+    int dbg_chain_last = -1;
 #endif
     // profiling
     bool profile = false;
@@ -514,6 +515,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.geo = geom(a);
         args.segs = pd->segs; args.items = pd->items; args.unit_row = d->unit_rows + pd->unit_row_off;
         args.n_segs = pd->host.n_segs; args.n_items = pd->host.n_items; args.n_ctas = pd->host.n_ctas;
+        args.n_units = pd->host.n_units; args.tail_pct = pd->host.levels > 1 ? d->split.tail_pct : 0;
         args.q = q; args.out = out; args.k_new = k_fused; args.v_new = v_fused; args.arena = L.base;
         args.part_o = d->part_o; args.part_ml = d->part_ml; args.seg_counter = d->seg_counter; args.status = d->status;
         args.work_counters = d->work_counters; args.work_slot = (int32_t)(d->launch_seq++ & 3u);
@@ -525,7 +527,13 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.wait_us = d->wait_us; args.fault_tile = d->fault_tile;
 #ifdef CBKV_MEASURE
         args.debug = debug_flags();
-        if (args.debug & 4) {
+        if (args.debug & 256) {  // timestamps of the last eight launches, no memset in between (launch overlap stays intact)
+            if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); CU_TRY(cudaMemset(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long))); }
+            args.debug |= 4;
+            args.dbg_buf = d->dbg_buf + (size_t)((d->launch_seq - 1) & 7u) * 512 * 16;
+            d->dbg_ctas = std::min(512, pd->host.n_ctas);
+            d->dbg_chain_last = (int)((d->launch_seq - 1) & 7u);
+        } else if (args.debug & 4) {
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
             CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
             args.dbg_buf = d->dbg_buf;
@@ -1190,6 +1198,32 @@ int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status) {
     CU_TRY(cudaSetDevice(d->device));
     CU_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     CU_TRY(cudaMemcpy(status, d->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+#ifdef CBKV_MEASURE
+    if ((debug_flags() & 256) && d->dbg_buf && d->dbg_chain_last >= 0) {  // the last eight decode launches as they overlapped
+        std::vector<unsigned long long> h((size_t)8 * 512 * 16);
+        cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
+        unsigned long long t0 = ~0ull;
+        const int n = d->dbg_ctas;
+        for (int l = 0; l < 8; l++) for (int c = 0; c < n; c++) { unsigned long long v = h[((size_t)l * 512 + c) * 16]; if (v) t0 = std::min(t0, v); }
+        double prev_exit = 0;
+        for (int k = 1; k <= 8; k++) {
+            const int l = (d->dbg_chain_last + k) & 7;
+            const int slots[5] = {0, 4, 7, 5, 6};
+            const char* names[5] = {"entry", "first_tile", "prod_done", "last_piece", "exit"};
+            char line[512]; int off = snprintf(line, sizeof line, "[cbkv chain] launch %d:", k);
+            double this_exit = 0;
+            for (int s2 = 0; s2 < 5; s2++) {
+                double mn = 1e18, mx = 0, av = 0; int cnt = 0;
+                for (int c = 0; c < n; c++) { unsigned long long v = h[((size_t)l * 512 + c) * 16 + slots[s2]]; if (!v) continue; double x = (double)(v - t0) * 1e-3; mn = std::min(mn, x); mx = std::max(mx, x); av += x; cnt++; }
+                if (cnt) off += snprintf(line + off, sizeof line - off, " %s %.1f/%.1f/%.1f", names[s2], mn, av / cnt, mx);
+                if (s2 == 4) this_exit = mx;
+            }
+            fprintf(stderr, "%s | period %.1f us\n", line, this_exit - prev_exit);
+            prev_exit = this_exit;
+        }
+        d->dbg_chain_last = -1;
+    }
+#endif
     if (*status) {
         CU_TRY(cudaMemset(d->status, 0, sizeof(int32_t)));
         if (d->seg_counter) CU_TRY(cudaMemset(d->seg_counter, 0, d->counter_cap * sizeof(int32_t)));

@@ -748,9 +748,17 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             failed = __any_sync(0xffffffffu, failed);
         };
         int raw = claim_issue();  // this CTA's second item
-        int4 cur = fetch(cta);
-        publish(0, cur);
+        // The unit range of this CTA's first item follows from the launch's totals (the host cuts the
+        // same way, build_decode_plan), so the first copies leave without waiting for its record; the
+        // record itself (first segment, part index) is fetched meanwhile for the other warps.
+        int4 cur;
+        {
+            const long long rb = (long long)a.n_units * cta / a.n_ctas, re = (long long)a.n_units * (cta + 1) / a.n_ctas;
+            const long long len = re - rb;
+            cur = make_int4((int)rb, (int)(re - len * a.tail_pct / 100), 0, 0);
+        }
         int4 nxt = make_int4(-1, -1, 0, 0);
+        bool first_record = true;
         int j = 0, T = 0;  // items started, tile slots used (copies and the fillers between items)
 #pragma unroll 1
         while (!failed) {
@@ -783,6 +791,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     // needs stages of earlier items, whereas later rounds may need this item's own tiles
                     // consumed, and its consumers may already be waiting for the queue entry.
                     if (to_publish) {
+                        if (first_record) { publish(0, fetch(cta)); first_record = false; }
                         nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
                         publish(j + 1, nxt);
                         to_publish = false;
@@ -792,6 +801,7 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 if (j == 0 && base == 0 && lane == 0) CBKV_STAMP(2);
             }
             if (to_publish && !failed) {  // an item without tiles (the host never makes one)
+                if (first_record) { publish(0, fetch(cta)); first_record = false; }
                 nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
                 publish(j + 1, nxt);
             }
@@ -872,7 +882,6 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             if (lane == 0 && pend_raw == pend_np - 1) {
                 last = 1;
                 a.seg_counter[pend_seg] = 0;  // ready for the next launch
-                __threadfence();              // acquire the other parts
             }
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {
@@ -955,8 +964,9 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 settle();  // the previous cut piece's ticket has had a whole piece to come back
                 if (nparts > 1) {
                     if (lane == 0) {
-                        __threadfence();  // the warp's partial (ordered before by __syncwarp) becomes visible before the ticket
-                        pend_raw = atomicAdd(a.seg_counter + seg, 1);
+                        // release: the warp's partial (ordered before by __syncwarp) is visible before the ticket;
+                        // acquire: whoever draws the last ticket sees every other part's partial
+                        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(pend_raw) : "l"(a.seg_counter + seg) : "memory");
                     }
                     pend_seg = seg;
                     pend_np = nparts;

@@ -84,6 +84,7 @@ struct DecodeArgs {
     const ItemInfo* items;      // n_items work items in claim order; item c < n_ctas is CTA c's first
     const int32_t* unit_row;    // per unit: page * n_kv + kv head (the record the tile lives in), -1 = bad table entry
     int32_t n_segs, n_items, n_ctas;
+    int32_t n_units, tail_pct;  // with n_ctas: enough for CTA c to compute the unit range of its first item (tail_pct 0: one item per CTA)
     const void* q;
     void* out;
     const void* k_new;  // non-null: write the step's new row into its page and attend it (fused append)

@@ -206,6 +206,7 @@ extern "C" int32_t cbkv_decode_attention_static(const void* kv_pages, int64_t nu
     args.items = reinterpret_cast<const ItemInfo*>(S + kOffItems);
     args.unit_row = unit_row;
     args.n_segs = pl.n_segs; args.n_items = pl.n_items; args.n_ctas = pl.n_ctas;
+    args.n_units = pl.n_units; args.tail_pct = pl.levels > 1 ? split.tail_pct : 0;
     args.q = q; args.out = out; args.k_new = nullptr; args.v_new = nullptr; args.arena = nullptr;
     args.part_o = reinterpret_cast<float*>(S + kOffPartO);
     args.part_ml = reinterpret_cast<float*>(S + kOffPartMl);

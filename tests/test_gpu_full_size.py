@@ -245,3 +245,100 @@ def test_cfg4_chunk_rotation_preserves_norms_and_is_linear():
     kr = gk.view(np.float16).astype(np.float32)
     kx = k.view(batch, n_kv, chunk, d)[3, :, 80:96].float().cpu().numpy()
     assert np.allclose(kr[..., : d // 2] ** 2 + kr[..., d // 2:] ** 2, kx[..., : d // 2] ** 2 + kx[..., d // 2:] ** 2, rtol=6e-3, atol=6e-3)
+
+
+def causal_rows_f64(q_rows, k, v, scale, q_pos, window=None):
+    """q_rows [n, d] at absolute position q_pos; k/v [L, d] with L > q_pos: keys 0..q_pos are visible
+    (bottom-right aligned causal mask, kv.rs:247-251), with a window only (q_pos - w, q_pos] (kv.rs:252-257)."""
+    lo = 0 if window is None else max(0, q_pos - window + 1)
+    kk, vv = k[lo:q_pos + 1].astype(np.float64), v[lo:q_pos + 1].astype(np.float64)
+    s = (q_rows.astype(np.float64) @ kk.T) * scale
+    s -= s.max(-1, keepdims=True)
+    p = np.exp(s)
+    return (p / p.sum(-1, keepdims=True)) @ vv
+
+
+@pytest.mark.parametrize("chunk_kernel", [3, 2, 1])
+def test_cfg4_chunked_prefill_at_full_context(chunk_kernel):
+    """The cfg4 shape at its real length: Llama-3-8B geometry, prompts of 8192 tokens in 16 chunks of 512
+    (one layer, two prompts).  After chunks 0, 7 and 15 a handful of (prompt, kv head, query row) triples
+    are recomputed in float64 from host copies of K and V; the last chunk is repeated with a window."""
+    n_q, n_kv, d, batch, prompt, chunk = 32, 8, 128, 2, 8192, 512
+    rep, scale = n_q // n_kv, d ** -0.5
+    arena = KVArena(1, n_q, n_kv, d, prompt + 64, 16, batch * (prompt // 16 + 4), sliding_popn_refuses=False)
+    arena.set_free_list(np.random.default_rng(44).permutation(arena.num_pages))
+    arena.set_chunk_kernel(chunk_kernel)
+    seqs = [arena.new_seq() for _ in range(batch)]
+    gen = torch.Generator(device="cuda").manual_seed(0xC0B50004 + chunk_kernel)
+    K = np.zeros((batch, n_kv, prompt, d), np.float16)
+    V = np.zeros_like(K)
+    rng = np.random.default_rng(chunk_kernel)
+    ntok = batch * chunk
+
+    def check(c, q, out, window=None):
+        qh = q.cpu().numpy().reshape(batch, n_q, chunk, d)
+        oh = out.cpu().numpy().reshape(batch, n_q, chunk, d)
+        rows = [0, 1, 127, 128, 300, chunk - 1] + [int(x) for x in rng.integers(0, chunk, 3)]
+        for r in rows:
+            b, h = int(rng.integers(batch)), int(rng.integers(n_kv))
+            ref = causal_rows_f64(qh[b, h * rep:(h + 1) * rep, r], K[b, h], V[b, h], scale, c * chunk + r, window)
+            assert_attention_close(oh[b, h * rep:(h + 1) * rep, r], ref, f"chunk {c} prompt {b} kv head {h} row {r} window {window}")
+
+    for c in range(prompt // chunk):
+        q = torch.randn(ntok * n_q * d, device="cuda", generator=gen).half()
+        k = torch.randn(ntok * n_kv * d, device="cuda", generator=gen).half()
+        v = torch.randn(ntok * n_kv * d, device="cuda", generator=gen).half()
+        K[:, :, c * chunk:(c + 1) * chunk] = k.cpu().numpy().reshape(batch, n_kv, chunk, d)
+        V[:, :, c * chunk:(c + 1) * chunk] = v.cpu().numpy().reshape(batch, n_kv, chunk, d)
+        arena.begin_step(seqs, [chunk] * batch, [c * chunk] * batch)
+        out = arena.attention(0, q, k, v, scale)
+        if c in (0, 7, 15):
+            assert arena.device_status() == 0
+            check(c, q, out)
+    # the last chunk once more with a sliding window (keys (p - 1000, p]): same pages, paged attention only
+    for s in seqs:
+        assert s.popn(chunk) == chunk
+    arena.begin_step(seqs, [chunk] * batch)
+    arena.append(0, k, v)
+    out = arena.paged_attention(0, q, scale, 1000)
+    assert arena.device_status() == 0
+    check(prompt // chunk - 1, q, out, window=1000)
+    # pages of the last chunk hold exactly what was appended
+    tbl = seqs[1].block_table()
+    gk, gv = arena.export_page(0, int(tbl[-1]))
+    assert np.array_equal(gk, K[1, :, -16:].view(np.uint16)) and np.array_equal(gv, V[1, :, -16:].view(np.uint16))
+
+
+@pytest.mark.parametrize("chunk_kernel", [3, 2])
+def test_chunk_attention_beyond_the_staged_block_table(chunk_kernel):
+    """A context longer than the 2560 block-table entries the tensor-core chunk kernels stage in shared
+    memory (40960 tokens): the entries past them are read from global memory while the kernel runs."""
+    n_q, n_kv, d, ctx, chunk = 4, 1, 128, 41472, 512
+    scale = d ** -0.5
+    arena = KVArena(1, n_q, n_kv, d, ctx + chunk, 16, (ctx + chunk) // 16 + 8)
+    arena.set_free_list(np.random.default_rng(45).permutation(arena.num_pages))
+    arena.set_chunk_kernel(chunk_kernel)
+    seq = arena.new_seq()
+    gen = torch.Generator(device="cuda").manual_seed(45)
+    kf = torch.randn(ctx * n_kv * d, device="cuda", generator=gen).half()
+    vf = torch.randn(ctx * n_kv * d, device="cuda", generator=gen).half()
+    arena.begin_step([seq], [ctx])
+    arena.append(0, kf, vf)
+    q = torch.randn(chunk * n_q * d, device="cuda", generator=gen).half()
+    k = torch.randn(chunk * n_kv * d, device="cuda", generator=gen).half()
+    v = torch.randn(chunk * n_kv * d, device="cuda", generator=gen).half()
+    arena.begin_step([seq], [chunk], [ctx])
+    out = arena.attention(0, q, k, v, scale).cpu().numpy().reshape(n_q, chunk, d)
+    assert arena.device_status() == 0
+    K = np.concatenate([kf.cpu().numpy().reshape(ctx, d), k.cpu().numpy().reshape(chunk, d)])
+    V = np.concatenate([vf.cpu().numpy().reshape(ctx, d), v.cpu().numpy().reshape(chunk, d)])
+    qh = q.cpu().numpy().reshape(n_q, chunk, d)
+    for r in (0, 255, 256, chunk - 1):
+        assert_attention_close(out[:, r], causal_rows_f64(qh[:, r], K, V, scale, ctx + r), f"row {r}")
+    # the same chunk through a window that starts beyond the staged entries' reach as well
+    assert seq.popn(chunk) == chunk
+    arena.begin_step([seq], [chunk], [ctx])
+    out = arena.attention(0, q, k, v, scale, 41000).cpu().numpy().reshape(n_q, chunk, d)
+    assert arena.device_status() == 0
+    for r in (0, chunk - 1):
+        assert_attention_close(out[:, r], causal_rows_f64(qh[:, r], K, V, scale, ctx + r, 41000), f"window row {r}")

@@ -254,6 +254,11 @@ def test_decode_plan_covers_every_page_once(window, n_ctas, tail_pct, min_item):
     if J > 1:
         assert size[0].min() >= size[1:].max()
         assert np.all(size[1:-1].min(axis=1) + 1 >= size[2:].max(axis=1)) if J > 2 else True
+    # a CTA's first item is a function of the launch totals alone (the kernel computes it instead of reading it)
+    U, pct = pl["n_units"], (25 if tail_pct < 0 else tail_pct) if J > 1 else 0
+    for c in range(G):
+        rb, re = U * c // G, U * (c + 1) // G
+        assert items[c, 0] == rb and items[c, 1] == re - (re - rb) * pct // 100
     per_range = size.sum(axis=0)
     assert per_range.max() - per_range.min() <= 1  # balanced to one page before any claiming
     # parts: every segment knows how many items touch it, and every item its place among them
