@@ -13,7 +13,7 @@ SOURCES = ["manager.cpp", "sessions.cpp", "kernels.cu", "prefill_tc.cu", "rope.c
 HEADERS = ["manager.hpp", "kernels.hpp", os.path.join("..", "..", "include", "combs_kv.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "static", "-ldl",
 ]
 
 

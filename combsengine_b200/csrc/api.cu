@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <atomic>
 #include <algorithm>
@@ -24,6 +25,20 @@ using namespace cbkv;
 namespace {
 
 std::atomic<int64_t> g_launches{0};
+
+// NVTX range around the host side of an entry point (header-only NVTX: a no-op unless a profiler
+// that collects NVTX is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    NvtxRange(const char* name, int layer) {
+        char buf[48];
+        snprintf(buf, sizeof buf, "%s L%d", name, layer);
+        nvtxRangePushA(buf);
+    }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 #define CU_TRY(expr)                                                                     \
     do {                                                                                 \
@@ -677,6 +692,7 @@ int32_t cbkv_seq_fork_prefix(cbkv_seq* parent, int64_t n_tokens, cbkv_seq** out)
 int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t* new_tokens, const int64_t* pos,
                         int32_t n_seqs, void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_begin_step");
     Arena* a = reinterpret_cast<Arena*>(arena);
     if (!a) { set_error("null arena"); return CBKV_ERR_ARG; }
     // The device must be reachable before any state is advanced: there is no CPU path.
@@ -690,6 +706,7 @@ int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t*
 
 int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void* v, void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_append", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -705,6 +722,7 @@ int32_t cbkv_append(cbkv_arena* arena, int32_t layer, const void* k, const void*
 int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, void* out, double scale, int64_t window,
                              void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_paged_attention", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -720,6 +738,7 @@ int32_t cbkv_paged_attention(cbkv_arena* arena, int32_t layer, const void* q, vo
 int32_t cbkv_attention(cbkv_arena* arena, int32_t layer, const void* q, const void* k, const void* v, void* out,
                        double scale, int64_t window, void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_attention", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -874,6 +893,7 @@ static int32_t rope_scratch(Arena* a, cudaStream_t st, size_t bytes) {
 int32_t cbkv_rope_append(cbkv_arena* arena, int32_t layer, const cbkv_rope* rope, const cbkv_qk_norm* norm,
                          const void* q, const void* k, const void* v, void* q_out, void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_rope_append", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -897,6 +917,7 @@ int32_t cbkv_attention_rope(cbkv_arena* arena, int32_t layer, const cbkv_rope* r
                             const void* q, const void* k, const void* v, void* out, double scale, int64_t window,
                             void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_attention_rope", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
@@ -962,6 +983,7 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
 int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
                                   const void* v_host, void* out_host, double scale, int64_t window, void* stream) {
     return fenced([&]() -> int32_t {
+    NvtxRange nvtx_range("cbkv_attention_host_async", layer);
     Arena* a = reinterpret_cast<Arena*>(arena);
     int32_t rc = check_step(a, layer);
     if (rc) return rc;
