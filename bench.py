@@ -649,6 +649,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             wq = workload("cfg2", quant=True)
             also["int8"] = measure_decode(wq, wq.lengths(wq.batch), local_rank, args, 20, 5)
             also["cfg4_one_layer"] = prefill_record(args, local_rank, layers=1, passes=2, warm_passes=1)
+            also["prefill_head_dim_256_one_layer"] = prefill_record(args, local_rank, layers=1, passes=2, warm_passes=1, geometry=(8, 4, 256),
+                                                                    label="cfg3's gemma-3-4b-style geometry under the cfg4 schedule,")
             also["rope"] = rope_record(args, local_rank, cpu=False)
 
     cpu = None
@@ -694,14 +696,16 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
 
 def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, warm_passes: int = 1, quant: bool = False,
-                   chunk_kernel: int = 0) -> dict:
+                   chunk_kernel: int = 0, geometry=(32, 8, 128), label: str = "cfg4 llama-3-8b geometry") -> dict:
     """cfg4: chunked prefill into the paged cache, Llama-3-8B geometry (32 layers, 32/8/128),
     8 prompts of 8192 tokens in 512-token chunks; per chunk and layer: append + causal attention
-    over the paged prefix plus the chunk.  A step = one full pass over the 16 chunks."""
+    over the paged prefix plus the chunk.  A step = one full pass over the 16 chunks.  `geometry`
+    runs the same schedule at other head counts / head_dim (cfg3's 8/4/256)."""
     import torch
     from combsengine_b200 import KVArena
 
-    n_q, n_kv, d, batch, prompt, chunk = 32, 8, 128, 8, 8192, 512
+    n_q, n_kv, d = geometry
+    batch, prompt, chunk = 8, 8192, 512
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     arena = KVArena(layers, n_q, n_kv, d, prompt + 64, 16, batch * (prompt // 16 + 4), device=local_rank, quantize_kv=quant)
@@ -748,7 +752,7 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
     vh = np.tile(v.cpu().numpy().reshape(batch, n_kv, chunk, d).astype(np.float64), (1, 1, prompt // chunk, 1))
     oh = out.cpu().numpy().reshape(batch, n_q, chunk, d).astype(np.float64)
     worst = 0.0
-    for b, hq, r in ((0, 0, 0), (3, 17, 255), (7, 31, chunk - 1), (5, 9, 128)):
+    for b, hq, r in ((0, 0, 0), (3, 17 % n_q, 255), (7, n_q - 1, chunk - 1), (5, 9 % n_q, 128)):
         p_abs = prompt - chunk + r
         sc = (kh[b, hq // (n_q // n_kv), :p_abs + 1] @ qh[b, hq, r]) * scale
         pr = np.exp(sc - sc.max())
@@ -768,7 +772,7 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
         "metric": "chunked_prefill_attention_tokens_per_s", "value": batch * prompt / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": passes, "warmup": warm_passes, "ms_per_step": ms, "higher_is_better": True,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"cfg4 llama-3-8b geometry chunked prefill: {layers} layers, 32/8/128, 8 prompts x 8192 in 512-token "
+        "config": {"workload": f"{label} chunked prefill: {layers} layers, {n_q}/{n_kv}/{d}, 8 prompts x 8192 in 512-token "
                                "chunks, append + causal attention over paged prefix + chunk"
                                + (", int8 KV pages" if quant else ""),
                    "chunk_kernel": {0: "auto", 1: "mma.sync", 2: "tcgen05, one query tile per CTA",

@@ -1365,7 +1365,7 @@ int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
     if (mode == 3 && !(dev_of(a)->tc_ok && chunk_tc2_supported(a->cfg.head_dim))) {
         set_error("the two-tile tensor-core chunk kernel covers head_dim 128 with 16-token pages only"); return CBKV_ERR_ARG;
     }
-    if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64 and 128 with 16-token pages only"); return CBKV_ERR_ARG; }
+    if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64, 128 and 256 with 16-token pages only"); return CBKV_ERR_ARG; }
     dev_of(a)->chunk_mode = mode;
     return CBKV_OK;
     });

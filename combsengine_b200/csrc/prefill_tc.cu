@@ -15,7 +15,11 @@
 //   warps 2..5    softmax: one TMEM lane (row) per thread, P written to shared memory
 //                 in the K-major swizzled layout, O rescaled in TMEM when a row max moves
 //
-// Tensor memory: S0 [0,128), S1 [128,256), O [256, 256 + D) -> 512 columns allocated.
+// KV tiles hold KT tokens: 128 for head_dim 64 and 128; 64 for head_dim 256, where a 128-token tile of K
+// and V (128 KB) would not leave room for two stages next to the Q tile (S = Q K^T is then 128 x 64 and
+// O += P V one 128 x 256 MMA per 16 keys).
+//
+// Tensor memory: S0 [0,KT), S1 [128,128+KT), O [256, 256 + D) -> 512 columns allocated.
 // Shared memory: Q and P tiles of 128 rows stored as 64-column blocks of 128 rows x 128 bytes
 // (128-byte swizzle); two K/V stages, each D/64 blocks of 8 pages x 32 rows x 128 bytes in
 // the arena's row order [K 0-7][V 0-7][K 8-15][V 8-15], so K and V are both 8-row groups
@@ -180,10 +184,30 @@ constexpr int kTmemCols = 512;
 constexpr int kPageCap = 2560;   // block-table entries staged in shared memory (40960 tokens); longer ranges read the rest from global memory
 
 template <int D>
+struct TcKeys { static constexpr int value = D == 256 ? 64 : 128; };  // tokens per KV tile
+
+template <int D>
 constexpr int tc_smem_bytes() {
-    // Q + 2 K + 2 V tiles of 128 rows x D, P tile of 128 rows x 128 keys, barriers and flags; at least
-    // 120 KB so that two CTAs never share an SM (each allocates all 512 tensor-memory columns)
-    return (5 * 128 * D * 2 + 128 * 128 * 2 + 256 + kPageCap * 4) < 120 * 1024 ? 120 * 1024 : (5 * 128 * D * 2 + 128 * 128 * 2 + 256 + kPageCap * 4);
+    // Q tile of 128 rows x D, two stages of K and V tiles of KT tokens x D, P tile of 128 rows x KT keys, barriers
+    // and the staged block table; at least 120 KB so that two CTAs never share an SM (each allocates all 512
+    // tensor-memory columns)
+    constexpr int need = 128 * D * 2 + 2 * 2 * TcKeys<D>::value * D * 2 + 128 * TcKeys<D>::value * 2 + 256 + kPageCap * 4;
+    return need < 120 * 1024 ? 120 * 1024 : need;
+}
+
+// KT consecutive columns of this thread's lane
+template <int KT>
+__device__ __forceinline__ void tmem_ld_row(uint32_t taddr, uint32_t (&r)[KT]) {
+    if constexpr (KT == 128) {
+        tmem_ld128(taddr, r);
+    } else {
+        static_assert(KT == 64, "KV tiles of 64 or 128 tokens");
+        uint32_t lo[32], hi[32];
+        tmem_ld32(taddr, lo);
+        tmem_ld32(taddr + 32, hi);
+#pragma unroll
+        for (int e = 0; e < 32; e++) { r[e] = lo[e]; r[32 + e] = hi[e]; }
+    }
 }
 
 }  // namespace
@@ -194,12 +218,14 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
     constexpr uint32_t BLK = 128u * 128u;      // one 64-element column block of a tile: 128 rows x 128 bytes
     constexpr int XB = D / 64;                 // column blocks per row
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr uint32_t BLKKV = 8u * 4096u;     // one 64-column block of a K/V stage: 8 pages x 32 rows x 128 bytes
-    constexpr uint32_t STAGE = 2u * TILE;      // K and V of 128 tokens
+    constexpr int KT = TcKeys<D>::value;           // tokens per KV tile
+    constexpr int PPT = KT / 16;               // pages per KV tile
+    constexpr uint32_t BLKKV = PPT * 4096u;    // one 64-column block of a K/V stage: PPT pages x 32 rows x 128 bytes
+    constexpr uint32_t STAGE = 2u * KT * D * 2u;  // K and V of KT tokens
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TILE;           // 2 stages
-    uint8_t* sP = sKV + 2 * STAGE;      // 128 x 128 keys
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 128 * 128 * 2);
+    uint8_t* sP = sKV + 2 * STAGE;      // 128 rows x KT keys
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 128 * KT * 2);
     // barriers: kv_full[2], kv_empty[2], s_full[2], p_full, o_done
     const uint32_t b_kv_full = smem_u32(bars + 0), b_kv_empty = smem_u32(bars + 2), b_s_full = smem_u32(bars + 4);
     const uint32_t b_p_full = smem_u32(bars + 6), b_o_done = smem_u32(bars + 7);
@@ -229,7 +255,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
     const int q_min = sm.pos + r0, q_max = sm.pos + r_last;
     const int lo_key = a.window > 0 ? max(0, q_min - a.window + 1) : 0;
     const int p_lo = lo_key >> 4, p_hi = q_max >> 4;
-    const int n_tiles = (p_hi - p_lo + 1 + 7) >> 3;
+    const int n_tiles = (p_hi - p_lo + 1 + PPT - 1) / PPT;
     const int k0 = p_lo * 16;                               // absolute position of key 0 of tile 0
 
     if (tid == 0) {
@@ -284,10 +310,10 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
-            for (int bx = lane; bx < 8 * XB; bx += 32) {
+            for (int bx = lane; bx < PPT * XB; bx += 32) {
                 const int pg = bx / XB, x = bx - pg * XB;
                 // pages past the last visible one repeat it: finite data that the causal mask hides
-                const int idx = min(j * 8 + pg, p_hi - p_lo);
+                const int idx = min(j * PPT + pg, p_hi - p_lo);
                 int phys = idx < kPageCap ? s_pages[idx] : a.step.tables[sm.tbl_off + p_lo + idx];
                 if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
                 tma_load_2d(smem_u32(sKV + st * STAGE + x * BLKKV + pg * 4096), &tmap32, x * 64, (phys * Hkv + h) * 32, b_kv_full + st * 8);
@@ -298,7 +324,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t id_qk = instr_desc(BF16, 128, 128, false);
+            const uint32_t id_qk = instr_desc(BF16, 128, KT, false);
             const uint32_t id_pv = instr_desc(BF16, 128, D, true);
             // descriptors differ only in the start address field (bits 0-13, address >> 4)
             // K: 8-row groups 2048 bytes apart; V: the same groups 1024 bytes further, 64-wide d blocks BLKKV apart
@@ -335,7 +361,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
                 const int st = j & 1;
                 const uint64_t vst = (uint64_t)((st * STAGE) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {  // 16 keys per step = one page
+                for (int ks = 0; ks < PPT; ks++) {  // 16 keys per step = one page
                     // P: K-major, keys 16 ks.. inside key block ks / 4; V: MN-major, one page (4096 bytes) per step
                     umma(tO, dp + (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4), dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv,
                          (j > 0 || ks > 0));
@@ -369,15 +395,15 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             if (!ok) break;
             tc_fence_after();
             const uint32_t tS = tS0 + (j & 1) * 128 + lane_addr;
-            const int kbase = k0 + j * 128;
-            const bool need_mask = (kbase + 127 > q_min) || (a.window > 0 && kbase + a.window <= q_max);
-            uint32_t sv[128];
-            tmem_ld128(tS, sv);
+            const int kbase = k0 + j * KT;
+            const bool need_mask = (kbase + KT - 1 > q_min) || (a.window > 0 && kbase + a.window <= q_max);
+            uint32_t sv[KT];
+            tmem_ld_row<KT>(tS, sv);
             TC_ACC(c_ld);
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < 128; e++) {
+                for (int e = 0; e < KT; e++) {
                     const int kp = kbase + e;
                     if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) sv[e] = 0xff800000u;  // -inf
                 }
@@ -385,7 +411,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             {
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int e = 0; e < 128; e += 4) {
+                for (int e = 0; e < KT; e += 4) {
                     m0 = fmaxf(m0, __uint_as_float(sv[e])); m1 = fmaxf(m1, __uint_as_float(sv[e + 1]));
                     m2 = fmaxf(m2, __uint_as_float(sv[e + 2])); m3 = fmaxf(m3, __uint_as_float(sv[e + 3]));
                 }
@@ -400,9 +426,9 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
             float sum = 0.f, sum2 = 0.f;
-            uint32_t pk[64];
+            uint32_t pk[KT / 2];
 #pragma unroll
-            for (int e = 0; e < 128; e += 2) {
+            for (int e = 0; e < KT; e += 2) {
                 const float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), a.scale_log2, -m_use));
                 const float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2, -m_use));
                 if (e & 2) sum2 += p0 + p1; else sum += p0 + p1;  // two chains
@@ -419,7 +445,7 @@ __global__ void __launch_bounds__(kThreads) chunk_tc_kernel(const __grid_constan
             }
             TC_ACC(c_wo);
 #pragma unroll
-            for (int u = 0; u < 16; u++) {  // sixteen 16-byte pieces = 128 keys, K-major swizzled
+            for (int u = 0; u < KT / 8; u++) {  // 16-byte pieces of 8 keys, K-major swizzled
                 const uint32_t off = (u >> 3) * BLK + m * 128u + (((u & 7) ^ (m & 7)) << 4);
                 *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
             }
@@ -818,7 +844,7 @@ cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const ChunkArgs& a, bool 
     return bf16 ? launch_tc2<true>(map32, a, st) : launch_tc2<false>(map32, a, st);
 }
 
-bool chunk_tc_supported(int d) { return d == 64 || d == 128; }
+bool chunk_tc_supported(int d) { return d == 64 || d == 128 || d == 256; }
 
 cudaError_t chunk_tc_init() {
     cudaError_t e;
@@ -826,6 +852,8 @@ cudaError_t chunk_tc_init() {
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<64>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<128>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<256>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<256>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
     return cudaSuccess;
@@ -836,6 +864,7 @@ cudaError_t launch_chunk_tc(const CUtensorMap& map, const CUtensorMap& map32, co
     switch (a.geo.d) {
         case 64: return bf16 ? launch_tc<64, true>(map, map32, a, st) : launch_tc<64, false>(map, map32, a, st);
         case 128: return bf16 ? launch_tc<128, true>(map, map32, a, st) : launch_tc<128, false>(map, map32, a, st);
+        case 256: return bf16 ? launch_tc<256, true>(map, map32, a, st) : launch_tc<256, false>(map, map32, a, st);
         default: return cudaErrorInvalidValue;
     }
 }

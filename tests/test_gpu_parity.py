@@ -88,6 +88,7 @@ def test_cfg4_llama_chunked_prefill(chunk_kernel):
 
 
 @pytest.mark.parametrize("geom", [(28, 4, 128, 2), (9, 3, 64, 2), (8, 8, 128, 2), (16, 2, 64, 2),
+                                  (8, 4, 256, 2), (16, 2, 256, 2), (4, 4, 256, 2),
                                   (28, 4, 128, 3), (8, 8, 128, 3), (16, 2, 128, 3)])
 def test_tensor_core_chunk_kernel_shapes_windows_and_ragged_chunks(geom):
     # tcgen05 kernels forced: q-head groups of 7, 3, 1 and 8; windows; chunks that do not fill a tile
