@@ -742,6 +742,8 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / passes
     assert arena.device_status() == 0
+    if args.measure:  # measurement build: per-role cycle counters of the last launch (CBKV_DEBUG=8), printed to stderr
+        arena.profile_read()
     # Outside the timed region: the last chunk of one more pass, a few rows recomputed in float64.  Every
     # chunk appends the same k, v, so a prompt's cached K is its chunk of k repeated 16 times.
     one_pass(pop=False)
