@@ -105,7 +105,7 @@ CFG2_TEXT = ("cfg2 qwen2.5-7b geometry batched decode: 28 layers, 28/4/128, batc
 
 def workload(name: str, layers: int = 0, quant: bool = False) -> Workload:
     if name == "cfg3":  # Gemma-3-4B-style: 5 local (w = 1024) : 1 global, batch 16 at 8192 tokens
-        w = Workload("cfg3", 34, 8, 4, 256, 16, 8192, 8192, 16 * 520, 0xC0B50003,
+        w = Workload("cfg3", 34, 8, 4, 256, 16, 8192, 8192, 16 * 640, 0xC0B50003,
                      "cfg3 gemma-3-4b-style decode: 34 layers (5 local w=1024 : 1 global), 8/4/256, batch 16 per GPU, "
                      "ctx 8192, windows over paged KV",
                      windows=[None if (i + 1) % 6 == 0 else 1024 for i in range(34)])
