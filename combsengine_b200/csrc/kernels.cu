@@ -48,6 +48,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// Non-blocking look at a barrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
 // Bounded wait: gives up after `limit_ns` of wall time and returns false (the caller
 // records it in the status word and stops consuming; nothing spins forever).
 __device__ __forceinline__ uint64_t global_ns() {
@@ -757,14 +767,17 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
             const long long len = re - rb;
             cur = make_int4((int)rb, (int)(re - len * a.tail_pct / 100), 0, 0);
         }
+        // the record and the first rows travel together; the other warps get the record the moment it is there
+        const int4 rec0 = fetch(cta);
+        int row_first = lane < cur.y - cur.x ? __ldcg(a.unit_row + cur.x + lane) : 0;
+        publish(0, rec0);
         int4 nxt = make_int4(-1, -1, 0, 0);
-        bool first_record = true;
         int j = 0, T = 0;  // items started, tile slots used (copies and the fillers between items)
 #pragma unroll 1
         while (!failed) {
             const int ub = cur.x, ntl = cur.y - cur.x;
             bool to_publish = true;
-            int row_next = lane < ntl ? __ldcg(a.unit_row + ub + lane) : 0;
+            int row_next = j == 0 ? row_first : (lane < ntl ? __ldcg(a.unit_row + ub + lane) : 0);
 #pragma unroll 1
             for (int base = 0; base < ntl && !failed; base += 32) {
                 const int row = row_next;
@@ -791,7 +804,6 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                     // needs stages of earlier items, whereas later rounds may need this item's own tiles
                     // consumed, and its consumers may already be waiting for the queue entry.
                     if (to_publish) {
-                        if (first_record) { publish(0, fetch(cta)); first_record = false; }
                         nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
                         publish(j + 1, nxt);
                         to_publish = false;
@@ -801,7 +813,6 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
                 if (j == 0 && base == 0 && lane == 0) CBKV_STAMP(2);
             }
             if (to_publish && !failed) {  // an item without tiles (the host never makes one)
-                if (first_record) { publish(0, fetch(cta)); first_record = false; }
                 nxt = fetch(__shfl_sync(0xffffffffu, raw, 0));
                 publish(j + 1, nxt);
             }
@@ -857,6 +868,19 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(qempty0 + s * 8);
         return out.x >= 0;
+    };
+
+    // the same without waiting: 1 = entry read (out valid, possibly the end marker), 0 = not published yet
+    auto peek_item = [&](int j, int4& out) -> bool {
+        const int s = j & (QN - 1);
+        int ok = 0;
+        if (lane == 0) ok = (int)mbar_test_wait(qfull0 + s * 8, (j / QN) & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
+        out = lds128(qitems0 + s * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(qempty0 + s * 8);
+        return true;
     };
 
     const int n_rep = a.geo.n_rep;
@@ -1037,15 +1061,19 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         // what comes next (the item's next segment, or the first piece of the next item): its
         // metadata and queries arrive while this piece is processed
         int4 nit = it;
-        bool nhave = true;
+        bool nhave = true, nknown = true;
         int nseg = seg + 1;
         if (!more) {
-            nhave = get_item(k + 1, nit);
+            // The next item's queue entry is looked at without waiting: the producer runs a ring ahead, so
+            // it is nearly always there; if not, it is waited for after this piece's tiles (a consumer
+            // never waits for the queue while tiles it has to consume are outstanding).
+            nknown = !failed && peek_item(k + 1, nit);
+            nhave = nknown && nit.x >= 0;
             nseg = nit.z;
         }
         Piece nxt = cur;
         uint32_t qf_next[1][D / 16][2];
-        if (nhave) {
+        if (nknown && nhave) {
             nxt = load_piece(a, nseg);
             if constexpr (Q8) load_q_frags_q8<D>(a, nxt, g, t, qf_next);
             else load_q_frags<D>(a, nxt, g, t, qf_next);
@@ -1163,6 +1191,15 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(cfull0 + buf * 8);
         kk++;
+        if (!nknown) {  // the entry was not there when the piece began: wait for it now
+            nhave = get_item(k + 1, nit);
+            if (nhave) {
+                nseg = nit.z;
+                nxt = load_piece(a, nseg);
+                if constexpr (Q8) load_q_frags_q8<D>(a, nxt, g, t, qf_next);
+                else load_q_frags<D>(a, nxt, g, t, qf_next);
+            }
+        }
         if (!nhave) break;
         if (more) {
             pb = pe;
