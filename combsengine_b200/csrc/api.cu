@@ -1291,11 +1291,12 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         const int n = -d->dbg_ctas;
         std::vector<unsigned long long> h((size_t)n * 16);
         cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
-        const char* names[11] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue", "softmax wait_s",
-                                 "softmax ld+max", "softmax exp+store", "softmax wait_o", "softmax rescale+arrive", "softmax total"};
+        const char* names[12] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue (QK)", "softmax wait_s",
+                                 "softmax ld+max", "softmax exp+store", "softmax wait_o", "softmax rescale+arrive", "softmax total",
+                                 "mma issue (PV, two-tile kernel)"};
         double tiles = 0;
         for (int c = 0; c < n; c++) tiles += (double)h[(size_t)c * 16 + 15];
-        for (int s2 = 0; s2 < 11; s2++) {
+        for (int s2 = 0; s2 < 12; s2++) {
             double sum = 0;
             for (int c = 0; c < n; c++) sum += (double)h[(size_t)c * 16 + s2];
             fprintf(stderr, "[cbkv tc] %-26s %9.0f cycles per KV tile (mean over %d CTAs, %.1f tiles each)\n", names[s2], sum / tiles, n, tiles / n);

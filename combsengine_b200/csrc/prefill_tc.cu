@@ -531,14 +531,21 @@ static cudaError_t launch_tc(const CUtensorMap& map, const CUtensorMap& map32, c
 //
 //   warp 0        TMA producer (as above)
 //   warp 1        MMA issuer:  QK_A, QK_B, then per K/V tile  PV_A, QK_A', PV_B, QK_B'
-//   warps 2..5    softmax of tile A        warps 6..9   softmax of tile B
+//   warps 2..9    softmax of tile A        warps 10..17  softmax of tile B
+//
+// A tile's softmax is the longest link of the chain QK -> softmax -> PV, and that chain, not the tensor pipe,
+// set the pace with one thread per row.  Two threads share a row now: the warps of a tile come in pairs that
+// may touch the same quarter of the tensor-memory lanes; one takes keys 0-63 of the tile, the other keys
+// 64-127 (and, when the row maximum moves, the matching half of the O columns).  They exchange their half-row
+// maxima through shared memory once per tile and their half-row sums once at the end.
 //
 // Tensor memory: S_A [0,128), S_B [128,256), O_A [256,384), O_B [384,512).
-constexpr int kThreads2 = 320;
+constexpr int kThreads2 = 576;
 
 template <int D>
 constexpr int tc2_smem_bytes() {
-    return 2 * 128 * D * 2 /* Q_A, Q_B */ + 2 * 2 * 128 * D * 2 /* two K/V stages */ + 256 + kPageCap * 4;
+    return 2 * 128 * D * 2 /* Q_A, Q_B */ + 2 * 2 * 128 * D * 2 /* two K/V stages */ + 256 + kPageCap * 4 +
+           2 * 2 * 128 * 2 * 4 /* half-row maxima of both tiles, double-buffered */ + 64 /* the pairs' failure flags */;
 }
 
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -567,6 +574,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* failed = reinterpret_cast<volatile int*>(bars + 11);
     int* s_pages = reinterpret_cast<int*>(bars + 16);
+    float* s_xch = reinterpret_cast<float*>(s_pages + kPageCap);  // [2 buffers][2 tiles][128 rows][2 halves]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
@@ -594,9 +602,10 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
     if (tid == 0) {
         for (int i = 0; i < 2; i++) {
             mbar_init(b_kv_full + i * 8, 1); mbar_init(b_kv_empty + i * 8, 1); mbar_init(b_s_full + i * 8, 1);
-            mbar_init(b_p_full + i * 8, 128); mbar_init(b_o_done + i * 8, 1);
+            mbar_init(b_p_full + i * 8, 256); mbar_init(b_o_done + i * 8, 1);
         }
         *failed = 0;
+        for (int i = 0; i < 8; i++) reinterpret_cast<int*>(s_xch + 2 * 2 * 128 * 2)[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap32) : "memory");
     }
@@ -675,7 +684,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                     umma_ts(tmem + 256 + X * 128, tmem + X * 128 + ks * 8, dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv, (j > 0 || ks > 0));
                 umma_commit(b_o_done + X * 8);
             };
-            long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0;
+            long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0, c_pv = 0;
             bool ok = mbar_wait_bounded(b_kv_full, 0);
             if (ok) { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
             for (int j = 0; ok && j < n_tiles; j++) {
@@ -685,8 +694,8 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(0, j);
+                TC_ACC(c_pv);
                 if (j + 1 < n_tiles) {
-                    TC_ACC(c_iss);
                     ok = mbar_wait_bounded(b_kv_full + ((j + 1) & 1) * 8, ((j + 1) >> 1) & 1);
                     TC_ACC(c_wkv);
                     if (!ok) break;
@@ -699,16 +708,19 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(1, j);
+                TC_ACC(c_pv);
                 umma_commit(b_kv_empty + (j & 1) * 8);  // every read of this stage has been issued before
                 if (j + 1 < n_tiles) issue_qk(1, j + 1);
             }
             if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
-            TC_DUMP(a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss;);
+            (void)c_pv;
+            TC_DUMP(a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss;
+                    a.dbg_buf[(size_t)blockIdx.x * 16 + 11] = c_pv;);
         }
     } else {
-        // ------------------------------------------------------------ softmax + epilogue of tile X
-        const int X = (warp - 2) >> 2;
-        const int lane_base = (warp & 3) * 32;
+        // ------------------------------------------------------------ softmax + epilogue of tile X, half H of the keys
+        const int X = (warp - 2) >> 3, H = ((warp - 2) >> 2) & 1;
+        const int lane_base = (warp & 3) * 32;  // the quarter of the tensor-memory lanes this warp may touch
         const int m = lane_base + lane;
         const int rep = m / TPT, r = r0 + X * TPT + (m - rep * TPT);
         const bool row_ok = rep < n_rep && r < sm.snew;
@@ -716,7 +728,12 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
         const int qx_min = sm.pos + min(r0 + X * TPT, sm.snew - 1), qx_max = sm.pos + min(r0 + (X + 1) * TPT, sm.snew) - 1;
         const uint32_t lane_addr = (uint32_t)lane_base << 16;
         const uint32_t tS = tmem + X * 128 + lane_addr, tO = tmem + 256 + X * 128 + lane_addr;
-        float m_ref = -INFINITY, l_run = 0.f;
+        const int pair_bar = 1 + X * 4 + (warp & 3);  // named barrier of the two warps that share this quarter of tile X
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+        // A named barrier has no time limit, so the two warps of a pair must leave the loop in the same
+        // iteration: whichever sees a wait run out says so here before the pair's barrier, both read it after.
+        volatile int* pair_failed = reinterpret_cast<volatile int*>(s_xch + 2 * 2 * 128 * 2) + X * 4 + (warp & 3);
+        float m_ref = -INFINITY, l_run = 0.f;  // l_run: this half's share of the row sum
         bool ok = true;
         long long tprev = TC_NOW(), c_ws = 0, c_ld = 0, c_exp = 0, c_wo = 0, c_st = 0;
         const long long tstart = tprev;
@@ -725,16 +742,16 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             ok = mbar_wait_bounded(b_s_full + X * 8, j & 1) && !*failed;
             ok = __all_sync(0xffffffffu, ok);
             TC_ACC(c_ws);
-            if (!ok) break;
+            if (!ok && lane == 0) *pair_failed = 1;  // the loads below then read stale columns: harmless, nothing is kept
             tc_fence_after();
-            const int kbase = k0 + j * 128;
-            const bool need_mask = (kbase + 127 > qx_min) || (a.window > 0 && kbase + a.window <= max(qx_max, qx_min));
-            // the whole row of S in registers: maximum, exponentials, packed P back over the S columns
-            uint32_t sv[128];
-            tmem_ld128(tS, sv);
+            const int kbase = k0 + j * 128 + H * 64;
+            const bool need_mask = (kbase + 63 > qx_min) || (a.window > 0 && kbase + a.window <= max(qx_max, qx_min));
+            // this half of the row of S in registers: maximum, exponentials, packed P back over the S columns
+            uint32_t sv[64];
+            tmem_ld_row<64>(tS + H * 64, sv);
             if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < 128; e++) {
+                for (int e = 0; e < 64; e++) {
                     const int kp = kbase + e;
                     if (!(kp <= q_pos && (a.window <= 0 || kp + a.window > q_pos))) sv[e] = 0xff800000u;  // -inf
                 }
@@ -743,32 +760,40 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             {
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int e = 0; e < 128; e += 4) {
+                for (int e = 0; e < 64; e += 4) {
                     m0 = fmaxf(m0, __uint_as_float(sv[e])); m1 = fmaxf(m1, __uint_as_float(sv[e + 1]));
                     m2 = fmaxf(m2, __uint_as_float(sv[e + 2])); m3 = fmaxf(m3, __uint_as_float(sv[e + 3]));
                 }
-                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * a.scale_log2;
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
+            // the other half's maximum (double-buffered by tile parity: the partner may still be reading the
+            // previous tile's entry when this one is written only if it were two tiles behind, which the
+            // barrier of the tile in between rules out)
+            float* xrow = s_xch + (((j & 1) * 2 + X) * 128 + m) * 2;
+            xrow[H] = mx;
+            pair_sync();  // also: both warps have their S columns in registers, so P may overwrite them
+            mx = fmaxf(mx, xrow[H ^ 1]) * a.scale_log2;
+            if (*pair_failed) { ok = false; break; }  // both warps of the pair, in the same iteration
             TC_ACC(c_ld);
             float alpha = 1.f;
-            if (mx > m_ref + 8.f || m_ref == -INFINITY) {
+            if (mx > m_ref + 8.f || m_ref == -INFINITY) {  // both halves see the same mx: the same decision
                 alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
                 m_ref = mx;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
             float sum = 0.f, sum2 = 0.f;
 #pragma unroll
-            for (int e = 0; e < 128; e += 2) {
+            for (int e = 0; e < 64; e += 2) {
                 const float p0 = ex2_approx(fmaf(__uint_as_float(sv[e]), a.scale_log2, -m_use));
                 const float p1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2, -m_use));
                 if (e & 2) sum2 += p0 + p1; else sum += p0 + p1;
                 sv[e >> 1] = pack2<BF16>(p0, p1);  // P pair e/2 reuses a register whose score is already consumed
             }
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {  // keys 64 H .. 64 H + 63 are packed columns 32 H .. 32 H + 31 of P
                 asm volatile(
                     "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                    ::"r"(tS + c * 16), "r"(sv[c * 16 + 0]), "r"(sv[c * 16 + 1]), "r"(sv[c * 16 + 2]), "r"(sv[c * 16 + 3]), "r"(sv[c * 16 + 4]),
+                    ::"r"(tS + H * 32 + c * 16), "r"(sv[c * 16 + 0]), "r"(sv[c * 16 + 1]), "r"(sv[c * 16 + 2]), "r"(sv[c * 16 + 3]), "r"(sv[c * 16 + 4]),
                       "r"(sv[c * 16 + 5]), "r"(sv[c * 16 + 6]), "r"(sv[c * 16 + 7]), "r"(sv[c * 16 + 8]), "r"(sv[c * 16 + 9]), "r"(sv[c * 16 + 10]),
                       "r"(sv[c * 16 + 11]), "r"(sv[c * 16 + 12]), "r"(sv[c * 16 + 13]), "r"(sv[c * 16 + 14]), "r"(sv[c * 16 + 15]) : "memory");
             }
@@ -776,13 +801,16 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             l_run = l_run * alpha + (sum + sum2);
             TC_ACC(c_exp);
             // S_X being full means P V_X of the previous tile has completed (the tensor pipe runs in
-            // order), so O_X may be rescaled now
+            // order), so O_X may be rescaled now: this warp takes the O columns 64 H .. 64 H + 63
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                uint32_t ov[128];
-                tmem_ld128(tO, ov);
+#pragma unroll 1
+                for (int c = 0; c < 2; c++) {
+                    uint32_t ov[32];
+                    tmem_ld32(tO + H * 64 + c * 32, ov);
 #pragma unroll
-                for (int e = 0; e < 128; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
-                tmem_st128(tO, ov);
+                    for (int e = 0; e < 32; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+                    tmem_st32(tO + H * 64 + c * 32, ov);
+                }
             }
             tc_fence_before();
             mbar_arrive(b_p_full + X * 8);
@@ -795,13 +823,19 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
         (void)tstart; (void)c_wo;
         if (ok) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
         ok = __all_sync(0xffffffffu, ok);
+        // the row sum is the two halves' sums (exchanged whether or not the wait succeeded: the pair must
+        // meet at its barrier the same number of times)
+        float* xrow = s_xch + ((n_tiles & 1) * 2 + X) * 256 + m * 2;
+        xrow[H] = l_run;
+        pair_sync();
+        const float l_row = l_run + xrow[H ^ 1];
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / l_run;
+            const float inv = 1.f / l_row;
             uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) +
                              ((size_t)sm.tok_off * a.geo.n_q + (size_t)(h * n_rep + (row_ok ? rep : 0)) * sm.snew + (row_ok ? r : 0)) * D;
 #pragma unroll 1
-            for (int c = 0; c < D / 32; c++) {
+            for (int c = 2 * H; c < 2 * H + 2; c++) {  // this warp writes the output columns 64 H .. 64 H + 63
                 uint32_t v[32];
                 tmem_ld32(tO + c * 32, v);
                 if (row_ok) {
