@@ -879,6 +879,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--quantize-kv", action="store_true", help="int8 KV pages (the reference's CacheConfig::quantize_kv)")
+    ap.add_argument("--head-dim-256", action="store_true", help="cfg4 only: run the schedule at cfg3's geometry (8/4/256)")
     ap.add_argument("--measure", action="store_true", help="load the measurement build (timers, CBKV_DEBUG switches)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: run fewer layers than the configuration has (small ncu case)")
     args = ap.parse_args()
@@ -890,9 +891,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.config == "cfg4":
         if rank == 0:
+            geo = dict(geometry=(8, 4, 256), label="cfg3's gemma-3-4b-style geometry under the cfg4 schedule,") if args.head_dim_256 else {}
             print(json.dumps(prefill_record(args, local_rank, layers=args.layers or 32, passes=max(1, args.steps // 16),
                                             warm_passes=max(1, args.warmup // 8), quant=bool(args.quantize_kv),
-                                            chunk_kernel=args.chunk_kernel)), flush=True)
+                                            chunk_kernel=args.chunk_kernel, **geo)), flush=True)
         return
     if args.config == "rope":
         if rank == 0:
