@@ -778,7 +778,8 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
                                "chunks, append + causal attention over paged prefix + chunk"
                                + (", int8 KV pages" if quant else ""),
                    "chunk_kernel": {0: "auto", 1: "mma.sync", 2: "tcgen05, one query tile per CTA",
-                                    3: "tcgen05, two query tiles per CTA"}[chunk_kernel]},
+                                    3: "tcgen05, two query tiles per CTA",
+                                    4: "tcgen05, two query tiles per CTA, int8 records converted in the kernel"}[chunk_kernel]},
         "roofline": {"bound": "tensor", "achieved": tfl, "peak": peak, "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None,
                      "algorithmic_flops_per_pass": flops, "peak_source": "cuBLAS bf16 burst, " + src},
         "spot_check": {"rows": 4, "max_abs_err_vs_float64": worst, "tolerance": ("5e-2" if quant else "2e-3") + " + 1e-2 |ref|"},
@@ -867,7 +868,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync, 2 = tcgen05 one tile per CTA, 3 = tcgen05 two tiles per CTA")
+    ap.add_argument("--chunk-kernel", type=int, default=0, help="cfg4 only: 1 = mma.sync, 2 = tcgen05 one tile per CTA, 3 = tcgen05 two tiles per CTA, 4 = as 3 with int8 records converted in the kernel")
     ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "rope"],
                     help="cfg2 is the headline workload; the others on request (short runs of them ride in the default line's `also`)")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="tuning: decode CTAs per SM (0 = default)")

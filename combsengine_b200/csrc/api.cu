@@ -105,7 +105,7 @@ struct DeviceState {
     ChunkPlan chunk_host;
     const int32_t* chunk_item_begin = nullptr;
     bool tc_ok = false;       // the tcgen05 chunk kernel covers this geometry
-    int chunk_mode = 0;       // 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel
+    int chunk_mode = 0;       // cbkv_set_chunk_kernel: 0 = choose, 1 = mma.sync, 2 = tcgen05 one tile, 3 = two tiles, 4 = two tiles, int8 records converted in the kernel
     bool tile_plan_ok = false;
     int tile_plan_tokens = 0;  // tokens per work item the tile plan was built for
     ChunkPlan tile_host;
@@ -242,6 +242,19 @@ int32_t materialize(Arena* a, int layer, cudaStream_t st) {
                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 records) failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
+            if (a->cfg.head_dim == 128) {
+                // the two-tile chunk kernel fetches K and V of a record separately: rows 0-15 K values, 16-31 V
+                // values, row 32 K scales, row 33 V scales
+                cuuint32_t box_values[2] = {128, 16}, box_scales[2] = {128, 1};
+                r = encode_fn()(&L.map_k16, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, L.base, dims, strides, box_values, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r == CUDA_SUCCESS)
+                    r = encode_fn()(&L.map_sc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, L.base, dims, strides, box_scales, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 half-records) failed: " + std::to_string((int)r)); return CBKV_ERR_CUDA; }
+            }
         }
         return CBKV_OK;
     }
@@ -500,12 +513,20 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
     if (w != 0 && w < 2) { set_error("sliding window must be >= 2, got " + std::to_string(w)); return CBKV_ERR_ARG; }
     LayerArena& L = d->layers[(size_t)layer];
     const float scale_log2 = (float)(scale * 1.4426950408889634);
-    // int8 pages: decode steps stream the records through the decode kernel; everything else (chunks,
-    // shapes outside the fast path) de-quantises on the fly in the generic kernel
+    // tensor-core chunk kernels: worth it once the step has enough new tokens to fill 128-row tiles
+    // (their softmax takes row maxima before scaling, which needs a positive scale)
+    const bool tc_able = d->fast && d->tc_ok && scale > 0 && !a->step_is_decode;
+    const bool use_tc2 = tc_able && chunk_tc2_supported(a->cfg.head_dim) &&
+                         (d->chunk_mode == 3 || d->chunk_mode == 4 || (d->chunk_mode == 0 && a->step_tokens >= 128));
+    const bool use_tc = tc_able && !use_tc2 && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
+    // int8 pages: decode steps stream the records through the decode kernel; the chunk kernels read a float
+    // copy made per layer and step (mode 4: the two-tile kernel converts the records itself, slower so far);
+    // shapes outside the fast path de-quantise on the fly in the generic kernel
+    const bool q8_direct = L.quant && use_tc2 && d->chunk_mode == 4;
     LayerArena* KV = &L;  // where the chunk kernels read K/V from
-    if (L.quant && d->fast && !a->step_is_decode && !(debug_flags() & 16)) {
-        // chunks over an int8 layer: de-quantise the pages of the step's sequences into the scratch layer
-        // (kv_dequantize, kv.rs:771-780) and run the float chunk kernels over that
+    if (L.quant && d->fast && !a->step_is_decode && !q8_direct && !(debug_flags() & 16)) {
+        // de-quantise the pages of the step's sequences into the scratch layer (kv_dequantize,
+        // kv.rs:771-780) and run the float chunk kernels over that
         if (!d->qscratch.base) {
             int32_t rc = alloc_float_layer(a, &d->qscratch, st);
             if (rc) return rc;
@@ -514,7 +535,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         CU_TRY(launch_dequant_pages(d->step.tables, (int)a->step_tables.size(), g, L.base, d->qscratch.base, d->status, bf16, st));
         g_launches++;
         KV = &d->qscratch;
-    } else if (L.quant && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
+    } else if (L.quant && !q8_direct && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
         GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
         ProfScope ps(d, st);
         CU_TRY(launch_generic_quant(args, bf16, st));
@@ -561,12 +582,6 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         d->last_kv_writer = k_fused ? layer : -1;
         return CBKV_OK;
     }
-    // tensor-core chunk kernels: worth it once the step has enough new tokens to fill 128-row tiles
-    // (their softmax takes row maxima before scaling, which needs a positive scale)
-    const bool tc_able = d->fast && d->tc_ok && scale > 0;
-    const bool use_tc2 = tc_able && chunk_tc2_supported(a->cfg.head_dim) &&
-                         (d->chunk_mode == 3 || (d->chunk_mode == 0 && a->step_tokens >= 128));
-    const bool use_tc = tc_able && !use_tc2 && (d->chunk_mode == 2 || (d->chunk_mode == 0 && a->step_tokens >= 64));
     if (use_tc || use_tc2) {
         const int rs = rep_slots_of(a->n_rep());
         int32_t rc = get_tile_plan(a, (use_tc2 ? 2 : 1) * (128 / rs), st);
@@ -574,6 +589,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         ChunkArgs args{};
         args.step = d->step; args.geo = geom(a); args.item_begin = d->tile_item_begin; args.n_items = d->tile_host.n_items;
         args.q = q; args.out = out; args.status = d->status; args.window = (int32_t)w; args.scale_log2 = scale_log2; args.rep_slots = rs;
+        args.q8_arena = q8_direct ? L.base : nullptr;
 #ifdef CBKV_MEASURE
         if (debug_flags() & 8) {  // per-role cycle counters of the first 4096 CTAs
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
@@ -582,7 +598,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         }
 #endif
         ProfScope ps(d, st);
-        if (use_tc2) CU_TRY(launch_chunk_tc2(KV->map_kv, args, bf16, st));
+        if (use_tc2) CU_TRY(q8_direct ? launch_chunk_tc2(L.map_k16, L.map_sc, args, bf16, st) : launch_chunk_tc2(KV->map_kv, KV->map_kv, args, bf16, st));
         else CU_TRY(launch_chunk_tc(KV->map_k16, KV->map_kv, args, bf16, st));
         g_launches++;
         d->last_kv_writer = -1;
@@ -1291,12 +1307,12 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
         const int n = -d->dbg_ctas;
         std::vector<unsigned long long> h((size_t)n * 16);
         cudaMemcpy(h.data(), d->dbg_buf, h.size() * 8, cudaMemcpyDeviceToHost);
-        const char* names[12] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue (QK)", "softmax wait_s",
+        const char* names[15] = {"producer wait_empty", "producer issue", "mma wait_kv", "mma wait_p", "mma issue (QK)", "softmax wait_s",
                                  "softmax ld+max", "softmax exp+store", "softmax wait_o", "softmax rescale+arrive", "softmax total",
-                                 "mma issue (PV, two-tile kernel)"};
+                                 "mma issue (PV, two-tile kernel)", "int8 loader: convert", "int8 loader: warp meets", "int8 loader: next copy"};
         double tiles = 0;
         for (int c = 0; c < n; c++) tiles += (double)h[(size_t)c * 16 + 15];
-        for (int s2 = 0; s2 < 12; s2++) {
+        for (int s2 = 0; s2 < 15; s2++) {
             double sum = 0;
             for (int c = 0; c < n; c++) sum += (double)h[(size_t)c * 16 + s2];
             fprintf(stderr, "[cbkv tc] %-26s %9.0f cycles per KV tile (mean over %d CTAs, %.1f tiles each)\n", names[s2], sum / tiles, n, tiles / n);
@@ -1360,10 +1376,10 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
 int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode) {
     return fenced([&]() -> int32_t {
     Arena* a = reinterpret_cast<Arena*>(arena);
-    if (!a || mode < 0 || mode > 3) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    if (!a || mode < 0 || mode > 4) { set_error("bad argument"); return CBKV_ERR_ARG; }
     int32_t rc = ensure_device(a);
     if (rc) return rc;
-    if (mode == 3 && !(dev_of(a)->tc_ok && chunk_tc2_supported(a->cfg.head_dim))) {
+    if (mode >= 3 && !(dev_of(a)->tc_ok && chunk_tc2_supported(a->cfg.head_dim))) {
         set_error("the two-tile tensor-core chunk kernel covers head_dim 128 with 16-token pages only"); return CBKV_ERR_ARG;
     }
     if (mode == 2 && !dev_of(a)->tc_ok) { set_error("the tensor-core chunk kernel covers head_dim 64, 128 and 256 with 16-token pages only"); return CBKV_ERR_ARG; }

@@ -27,6 +27,7 @@
 #include <algorithm>
 
 #include "kernels.hpp"
+#include "q8_unpack.cuh"
 
 namespace cbkv {
 
@@ -250,36 +251,7 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     asm volatile("ld.shared.b16 %0, [%1];" : "=h"(v) : "r"(addr));
     return v;
 }
-// Byte -> number.  Every byte of a record is b = q + 128.  f16: a byte under the exponent byte 0x64
-// reads as 1024 + b, and subtracting 1152 leaves q.  bf16 has one mantissa bit less than a byte is
-// wide, so there the bytes are first made two's complement (one XOR per word): the low seven bits
-// under 0x43 read as 128 + (b & 127), the sign bit under 0x43 reads as 128 or 256, and their
-// difference is q.  Both subtractions are exact.
-template <bool BF16> __device__ __forceinline__ uint32_t q8_fix(uint32_t w) { return BF16 ? (w ^ 0x80808080u) : w; }
-// two bytes of `src` (selected by `sel`, which also places the exponent bytes) -> two numbers q
-template <bool BF16>
-__device__ __forceinline__ uint32_t q8_pair(uint32_t src, uint32_t sel) {
-    uint32_t v = __byte_perm(src, BF16 ? 0x43434343u : 0x64646464u, sel);
-    if constexpr (BF16) {
-        uint32_t lo = v & 0xff7fff7fu, hi = v & 0xff80ff80u;
-        __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&lo), *reinterpret_cast<__nv_bfloat162*>(&hi));
-        return *reinterpret_cast<uint32_t*>(&r);
-    } else {
-        const uint32_t bias = 0x64806480u;  // 1152, 1152
-        __half2 r = __hsub2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&bias));
-        return *reinterpret_cast<uint32_t*>(&r);
-    }
-}
-template <bool BF16>
-__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
-    if constexpr (BF16) {
-        __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-        return *reinterpret_cast<uint32_t*>(&r);
-    } else {
-        __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-        return *reinterpret_cast<uint32_t*>(&r);
-    }
-}
+// Byte -> number conversions (q8_fix, q8_pair, mul2): q8_unpack.cuh.
 template <bool BF16>
 __device__ __forceinline__ float2 up2(uint32_t v) {
     if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
@@ -290,8 +262,6 @@ __device__ __forceinline__ float fast_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-constexpr uint32_t SEL_LO = 0x5140u;  // bytes 0 and 1 of the source, each under an exponent byte
-constexpr uint32_t SEL_HI = 0x7362u;  // bytes 2 and 3
 
 // One 16-token quantised tile against the 8 query columns of the kv group (decode), in two steps:
 // q8_load copies this thread's share of the record from shared memory to registers, after which the

@@ -61,9 +61,12 @@ CBKV_HD inline size_t qrec_scale_off(int is_v, int slot, int group, int page_siz
 
 struct LayerArena {
     void* base = nullptr;
-    bool quant = false;  // base holds quantised records, no tensor maps
-    CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle
-    CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile)
+    bool quant = false;  // base holds quantised records
+    CUtensorMap map_kv;  // 2-D view [rows = pages*n_kv*32][d], box 32 rows x 64 elems, 128B swizzle;
+                         // quantised: bytes in 128-byte rows, one box = one record
+    CUtensorMap map_k16; // same view, box 16 rows x 64 elems (one K or one V tile);
+                         // quantised, head_dim 128: box = the 16 rows of a record's K values or of its V values
+    CUtensorMap map_sc;  // quantised, head_dim 128: box = one row, a record's K scales or its V scales
 };
 
 struct StepDev {
@@ -121,6 +124,7 @@ struct ChunkArgs {
     int32_t window;
     float scale_log2;
     int32_t rep_slots;  // tcgen05 kernel: q heads per kv head rounded up to a power of two (rows per token in a tile)
+    const void* q8_arena;  // two-tile tcgen05 kernel: non-null = the layer's int8 records, read and converted by the kernel itself
 #ifdef CBKV_MEASURE
     unsigned long long* dbg_buf;  // per-CTA cycle counters of the tcgen05 kernel
 #endif
@@ -195,7 +199,8 @@ cudaError_t chunk_tc_init();
 cudaError_t launch_chunk_tc(const CUtensorMap& map16, const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st);
 // two query tiles per CTA, P in tensor memory (head_dim 128)
 bool chunk_tc2_supported(int d);
-cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st);
+// int8 layer (a.q8_arena non-null): `map32` = the layer's map_k16, `map_sc` = its map_sc; float layer: map_sc is not used
+cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const CUtensorMap& map_sc, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t kernels_init();  // raises the dynamic shared memory limits once per process
 
 }  // namespace cbkv

@@ -15,6 +15,7 @@
 #include <algorithm>
 
 #include "kernels.hpp"
+#include "q8_unpack.cuh"
 
 namespace cbkv {
 
@@ -116,26 +117,38 @@ __global__ void __launch_bounds__(256) dequant_pages_kernel(const int32_t* table
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int D = geo.d, P = geo.page_size, Hkv = geo.n_kv;
+    const int D = geo.d, P = geo.page_size, Hkv = geo.n_kv, G = D / 32;
     const size_t rec = qrec_bytes(P, D);
+    const int k_chunks = P * D / 16, sw = qrec_swizzled(D) ? 1 : 0;
+    const bool tiled = geo.tiled != 0;
     for (int64_t it = warp0; it < (int64_t)n_entries * Hkv; it += nwarps) {
         const int e = (int)(it / Hkv), h = (int)(it - (int64_t)e * Hkv);
         const int phys = tables[e];
         if (phys < 0 || phys >= geo.num_pages) { if (lane == 0) atomicOr(status, ST_BAD_PAGE); continue; }
         const uint8_t* recp = arena + ((size_t)phys * Hkv + h) * rec;
+        const uint16_t* ksc = reinterpret_cast<const uint16_t*>(recp + (size_t)2 * P * D);
+        const uint32_t* vsc = reinterpret_cast<const uint32_t*>(ksc + P * G);  // group-major: one word = two neighbouring tokens
         uint16_t* dst = scratch + ((size_t)phys * Hkv + h) * 2 * P * D;
-        for (int r = 0; r < 2 * P; r++) {
-            const int is_v = r >= P, slot = is_v ? r - P : r;
-            uint16_t* drow = dst + (size_t)page_row(is_v, slot, P, geo.tiled != 0) * D;
-            for (int c = lane; c < D / 4; c += 32) {
-                const float sc = q_up<BF16>(*reinterpret_cast<const uint16_t*>(recp + qrec_scale_off(is_v, slot, c >> 3, P, D)));
-                uint16_t o[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int qi = (int)recp[qrec_value_off(is_v, slot, 4 * c + i, P, D)] - 128;
-                    o[i] = q_down<BF16>(__fmul_rn((float)qi, sc));
-                }
-                *reinterpret_cast<uint2*>(drow + 4 * c) = make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
+        // a lane takes 16-byte pieces of the record as they lie (coalesced) and works out which values they hold
+        for (int c = lane; c < 2 * k_chunks; c += 32) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(recp) + c);
+            if (c < k_chunks) {  // K: 16 consecutive d of one token, inside one 32-value group (qrec_value_off)
+                const int off = c * 16, slot = off / D, pos = off - slot * D;
+                const int grp = (pos >> 5) ^ qrec_swz(slot, D), j0 = grp * 32 + (pos & 31);
+                const uint32_t s1 = ksc[slot * G + grp];
+                uint4 lo, hi;
+                q8_unpack_k16<BF16>(raw, s1 | (s1 << 16), lo, hi);
+                uint4* out = reinterpret_cast<uint4*>(dst + (size_t)page_row(0, slot, P, tiled) * D + j0);
+                out[0] = lo; out[1] = hi;
+            } else {             // V: 8 consecutive d of a token pair, interleaved per d
+                const int off = (c - k_chunks) * 16, pair = off / (2 * D), rem = off - pair * 2 * D;
+                const int grp = (rem >> 6) ^ (sw * (pair & 1));
+                const int chunk = ((rem & 63) >> 3) ^ (sw * 4 * ((pair >> 1) & 1));
+                const int j0 = grp * 32 + chunk * 4;
+                uint4 even, odd;
+                q8_unpack_v8x2<BF16>(raw, vsc[(grp * P + 2 * pair) >> 1], even, odd);
+                *reinterpret_cast<uint4*>(dst + (size_t)page_row(1, 2 * pair, P, tiled) * D + j0) = even;
+                *reinterpret_cast<uint4*>(dst + (size_t)page_row(1, 2 * pair + 1, P, tiled) * D + j0) = odd;
             }
         }
     }

@@ -30,6 +30,7 @@
 #include <algorithm>
 
 #include "kernels.hpp"
+#include "q8_unpack.cuh"
 
 namespace cbkv {
 
@@ -556,8 +557,30 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <int D, bool BF16>
-__global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_constant__ CUtensorMap tmap32, const ChunkArgs a) {
+// Q8: the layer holds int8 records (kernels.hpp, qrec_*) and the kernel converts them itself
+// (cbkv_set_chunk_kernel mode 4; by default int8 layers go through a float copy, which is faster so far).
+// Two warps after the softmax warps take the TMA producer's place, one for K and one for V.  Each keeps a
+// ring of raw half-records (a record's K bytes and K scales, or its V bytes and V scales: two boxes of
+// the layer's byte tensor maps) in flight, turns a landed half-record into q * scale in registers
+// (q8_unpack.cuh: kv_dequantize, kv.rs:319-358), stores that where the tensor pipe reads it, and refills
+// the slot itself.  Shared memory is cut differently from the float kernel: K is double-buffered as there
+// (the scores of the next tile are issued a tile ahead), V has one buffer (P.V of a tile is the last thing
+// that reads it), and the 32 KB this frees plus the tail of the allocation hold 8 K and 14 V half-records.
+// Measured on 8 prompts x 8192 tokens: 2.4 times the float-copy route's time.  The V buffer can only be
+// refilled between the last P.V of a tile and the first of the next, and one warp needs about 1400 cycles
+// per half-record there (wait, convert, refill), eight times per tile; 640 threads at 96 registers leave no
+// room for more converting warps, and 227 KB no room for a second V buffer beside the raw rings.
+constexpr int kLoaders2 = 2;
+constexpr int kThreads2Q8 = kThreads2 + kLoaders2 * 32;
+constexpr int kRawK = 8, kRawV = 14;       // half-records per ring
+constexpr int kRawVInStage = 7;            // V slots that fit behind the K ring in the freed stage quarter
+template <int D>
+constexpr int tc2_half_rec() { return 16 * D + 16 * (D / 32) * 2; }  // values + scales of K or of V
+template <int D>
+constexpr int tc2_smem_bytes_q8() { return tc2_smem_bytes<D>() + 64 + (kRawV - kRawVInStage) * tc2_half_rec<D>() + (kRawK + kRawV + 2) * 8; }
+
+template <int D, bool BF16, bool Q8>
+__global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel(const __grid_constant__ CUtensorMap tmap32, const __grid_constant__ CUtensorMap tmap_sc, const ChunkArgs a) {
     static_assert(D == 128, "two-tile kernel: head_dim 128");
     constexpr uint32_t TILE = 128u * D * 2u;   // one Q tile
     constexpr uint32_t BLK = 128u * 128u;      // 64-column block of a Q tile
@@ -575,6 +598,20 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
     volatile int* failed = reinterpret_cast<volatile int*>(bars + 11);
     int* s_pages = reinterpret_cast<int*>(bars + 16);
     float* s_xch = reinterpret_cast<float*>(s_pages + kPageCap);  // [2 buffers][2 tiles][128 rows][2 halves]
+    // Q8 layout of the stage area: K buffers [0, 64 KB), V buffer [64, 96 KB), raw K ring and the first raw V
+    // slots [96, 128 KB); the other raw V slots and the Q8 barriers follow the exchange area.  A K or V buffer
+    // is [64-column block][page][8-token group][8 rows of 128 bytes], 128-byte swizzle.
+    constexpr uint32_t REC = 2u * 16u * D + 2u * 16u * (D / 32) * 2u;  // an int8 record
+    constexpr uint32_t HALF = 16u * D + 16u * (D / 32) * 2u;              // a record's K or V values with their scales
+    static_assert(HALF == (uint32_t)(REC / 2), "half a record");
+    constexpr uint32_t QBUF = 128u * D * 2u, QBLK = QBUF / 2;          // one K or V buffer, one 64-column block of it
+    static_assert(!Q8 || kRawK * HALF + kRawVInStage * HALF <= 2 * STAGE - 3 * QBUF, "raw rings in the freed quarter");
+    uint8_t* sRawK = sKV + 3 * QBUF;
+    uint8_t* sRawV0 = sRawK + kRawK * HALF;
+    uint8_t* sRawV1 = reinterpret_cast<uint8_t*>(s_xch + 2 * 2 * 128 * 2) + 128;  // 128-byte aligned, as every slot is
+    const uint32_t b_q8 = smem_u32(sRawV1 + (kRawV - kRawVInStage) * HALF);
+    const uint32_t b_v_full = b_q8, b_v_empty = b_q8 + 8, b_rawk = b_q8 + 16, b_rawv = b_rawk + kRawK * 8;
+    (void)sRawK; (void)sRawV0; (void)sRawV1; (void)b_v_full; (void)b_v_empty; (void)b_rawk; (void)b_rawv; (void)REC;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
@@ -604,20 +641,25 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             mbar_init(b_kv_full + i * 8, 1); mbar_init(b_kv_empty + i * 8, 1); mbar_init(b_s_full + i * 8, 1);
             mbar_init(b_p_full + i * 8, 256); mbar_init(b_o_done + i * 8, 1);
         }
+        if constexpr (Q8) {  // kv_full / kv_empty above are K's here
+            mbar_init(b_v_full, 1); mbar_init(b_v_empty, 1);
+            for (int i = 0; i < kRawK + kRawV; i++) mbar_init(b_rawk + i * 8, 1);
+        }
         *failed = 0;
         for (int i = 0; i < 8; i++) reinterpret_cast<int*>(s_xch + 2 * 2 * 128 * 2)[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap32) : "memory");
+        if constexpr (Q8) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_sc) : "memory");
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i <= p_hi - p_lo && i < kPageCap; i += kThreads2) s_pages[i] = a.step.tables[sm.tbl_off + p_lo + i];
+    for (int i = tid; i <= p_hi - p_lo && i < kPageCap; i += (int)blockDim.x) s_pages[i] = a.step.tables[sm.tbl_off + p_lo + i];
     // ---- Q tiles: row m of tile X is q head (m / TPT) at token r0 + X TPT + m % TPT
     {
         const uint16_t* qbase = reinterpret_cast<const uint16_t*>(a.q) + (size_t)sm.tok_off * a.geo.n_q * D;
-        for (int c = tid; c < 256 * (D / 8); c += kThreads2) {
+        for (int c = tid; c < 256 * (D / 8); c += (int)blockDim.x) {
             const int mm = c / (D / 8), j = c - mm * (D / 8);
             const int X = mm >> 7, m = mm & 127;
             const int rep = m / TPT, r = r0 + X * TPT + (m - rep * TPT);
@@ -634,7 +676,117 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
+    if (Q8 && warp >= 18) {
+        // ------------------------------------------------------------ int8 layer: warp 18 feeds K, warp 19 feeds V
+        const bool is_v = warp == 19;
+        const int n_slots = is_v ? kRawV : kRawK;
+        const uint32_t b_raw = is_v ? b_rawv : b_rawk;
+        auto slot_ptr = [&](int sl) -> uint8_t* {
+            if (!is_v) return sRawK + sl * HALF;
+            return sl < kRawVInStage ? sRawV0 + sl * HALF : sRawV1 + (sl - kRawVInStage) * HALF;
+        };
+        const int n_recs = 8 * n_tiles;
+        // lane 0: the half-record of page n of the CTA's range into its slot (values, then scales behind them).
+        // Two boxes of the layer's byte tensor maps (128-byte rows, REC / 128 rows per record: K values, V values,
+        // one row of K scales, one of V scales); plain bulk copies of the same bytes cost the issuing thread about
+        // a thousand cycles per record, tensor-map copies a few dozen.
+        auto issue = [&](int n, int sl) {
+            const int idx = min(n, p_hi - p_lo);  // pages past the end repeat the last one (masked)
+            int phys = idx < kPageCap ? s_pages[idx] : a.step.tables[sm.tbl_off + p_lo + idx];
+            if (phys < 0 || phys >= a.geo.num_pages) { atomicOr(a.status, ST_BAD_PAGE); phys = 0; }
+            const int row0 = (phys * Hkv + h) * (int)(REC / 128u);
+            const uint32_t dst = smem_u32(slot_ptr(sl)), bar = b_raw + sl * 8;
+            mbar_expect_tx(bar, HALF);
+            tma_load_2d(dst, &tmap32, 0, row0 + (is_v ? 16 : 0), bar);
+            tma_load_2d(dst + 16u * D, &tmap_sc, 0, row0 + 32 + (is_v ? 1 : 0), bar);
+        };
+        // Lane l takes the 16-byte pieces l, l + 32, l + 64, l + 96 of a half-record's 2048 value bytes.
+        // K: 16 consecutive d of token l / 8 + 4 i, one scale group.  V: 8 consecutive d of token pair
+        // l / 16 + 2 i.  Both permutations of qrec_value_off repeat every eight tokens, so piece i + 2 lands
+        // one 8-token group (1024 bytes) after piece i, and pieces i = 0, 1 differ by four rows.
+        uint32_t src_sc, d0[2], d1[2];  // scale offset of piece 0; where the piece's two 16-byte results go (i even, i odd)
+        if (!is_v) {
+            const int s0 = lane >> 3, grp = ((lane & 7) >> 1) ^ (s0 & 3), j0 = grp * 32 + (lane & 1) * 16, cc = (j0 & 63) >> 3;
+            src_sc = 16u * D + (uint32_t)(s0 * (D / 32) + grp) * 2u;  // + 4 i tokens = + 4 i (D / 32) * 2 bytes
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int row = s0 + 4 * e;
+                const uint32_t base = (uint32_t)(j0 >> 6) * QBLK + (uint32_t)row * 128u;
+                d0[e] = base + (uint32_t)((cc ^ row) << 4); d1[e] = base + (uint32_t)(((cc + 1) ^ row) << 4);
+            }
+        } else {
+            const int p0 = lane >> 4, grp = ((lane & 15) >> 2) ^ (p0 & 1);
+            src_sc = 16u * D + (uint32_t)(grp * 8 + p0) * 4u;          // + 2 i pairs = + 8 i bytes
+#pragma unroll
+            for (int e = 0; e < 2; e++) {  // pair p0 + 2 i: (pair >> 1) & 1 = i & 1
+                const int chunk = (2 * (lane & 3)) ^ (4 * e), j0 = grp * 32 + chunk * 4, cc = (j0 & 63) >> 3;
+                const int t0 = 2 * p0 + 4 * e, t1 = t0 + 1;            // rows inside the 8-token group
+                const uint32_t base = (uint32_t)(j0 >> 6) * QBLK;
+                d0[e] = base + (uint32_t)t0 * 128u + (uint32_t)((cc ^ t0) << 4); d1[e] = base + (uint32_t)t1 * 128u + (uint32_t)((cc ^ t1) << 4);
+            }
+        }
+        int issued = 0;
+        if (lane == 0)
+            for (; issued < n_slots && issued < n_recs; issued++) issue(issued, issued);
+        issued = __shfl_sync(0xffffffffu, issued, 0);
+        bool ok = true;
+        int n = 0, sl = 0, ph = 0;  // record, its slot, the slot's phase
+        long long tprev = TC_NOW(), c_wait = 0, c_issue = 0, c_conv = 0, c_meet = 0;
+#pragma unroll 1
+        for (; n < n_recs; n++) {
+            const int j = n >> 3, pg = n & 7;
+            if (lane == 0) {
+                if (pg == 0) {  // the buffer this tile goes to must have been read to the end
+                    if (!is_v && j >= 2 && !mbar_wait_bounded(b_kv_empty + (j & 1) * 8, ((j >> 1) - 1) & 1)) ok = false;
+                    if (is_v && j >= 1 && !mbar_wait_bounded(b_v_empty, (j - 1) & 1)) ok = false;
+                }
+                if (ok && !mbar_wait_bounded(b_raw + sl * 8, ph)) ok = false;
+                if (*failed) ok = false;
+                if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
+                TC_ACC(c_wait);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            const uint8_t* rp = slot_ptr(sl);
+            uint8_t* out = sKV + (is_v ? 2 * QBUF : (uint32_t)(j & 1) * QBUF) + (uint32_t)pg * 2048u;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(rp + lane * 16 + i * 512);
+                uint8_t* o = out + (i >> 1) * 1024;
+                uint4 x, y;
+                if (!is_v) {
+                    const uint32_t sc = *reinterpret_cast<const uint16_t*>(rp + src_sc + i * (4 * (D / 32) * 2));
+                    q8_unpack_k16<BF16>(raw, sc | (sc << 16), x, y);
+                } else {
+                    const uint32_t sc = *reinterpret_cast<const uint32_t*>(rp + src_sc + i * 8);
+                    q8_unpack_v8x2<BF16>(raw, sc, x, y);
+                }
+                *reinterpret_cast<uint4*>(o + d0[i & 1]) = x;
+                *reinterpret_cast<uint4*>(o + d1[i & 1]) = y;
+            }
+            // A finished tile goes to the tensor pipe's proxy.  The slot's next copy needs no fence: every lane's
+            // loads from the slot have returned their values (the stores above used them) before the warp meets.
+            if (lane == 0) TC_ACC(c_conv);
+            if (pg == 7) fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                TC_ACC(c_meet);
+                if (issued < n_recs) issue(issued, sl);
+                if (pg == 7) mbar_arrive(is_v ? b_v_full : b_kv_full + (j & 1) * 8);
+                TC_ACC(c_issue);
+            }
+            if (issued < n_recs) issued++;
+            if (++sl == n_slots) { sl = 0; ph ^= 1; }
+        }
+        // never leave with a copy in flight: the records n .. issued - 1 have been asked for and not taken
+        if (lane == 0)
+            for (; n < issued; n++) {
+                if (!mbar_wait_bounded(b_raw + sl * 8, ph)) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
+                if (++sl == n_slots) { sl = 0; ph ^= 1; }
+            }
+        TC_DUMP(if (tid == 18 * 32) { unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16; b[0] = c_wait; b[1] = c_issue + c_conv + c_meet; b[12] = c_conv; b[13] = c_meet; b[14] = c_issue; b[15] = n_tiles; });
+        (void)c_wait; (void)c_issue; (void)c_conv; (void)c_meet; (void)tprev;
+    } else if (!Q8 && warp == 0) {
         // ------------------------------------------------------------ TMA producer
         bool ok = true;
         long long tprev = TC_NOW(), c_wait = 0, c_issue = 0;
@@ -665,23 +817,27 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
         if (lane == 0) {
             const uint32_t id_qk = instr_desc(BF16, 128, 128, false);
             const uint32_t id_pv = instr_desc(BF16, 128, D, true);
-            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sKV), 16, 2048);
-            const uint64_t dv = smem_desc(smem_u32(sKV) + 1024, BLKKV, 2048);
+            // float layer: a stage holds pages as they lie in device memory (K and V rows of a page interleaved in
+            // groups of eight); int8 layer: the loader warps lay K and V out separately (see the shared memory map)
+            constexpr uint32_t KBUF = Q8 ? QBUF : STAGE, KBLK = Q8 ? QBLK : BLKKV, GRP = Q8 ? 1024u : 2048u, VPAGE = Q8 ? 2048u : 4096u;
+            const uint64_t dq = smem_desc(smem_u32(sQ), 16, 1024), dk = smem_desc(smem_u32(sKV), 16, GRP);
+            const uint64_t dv = smem_desc(smem_u32(sKV) + (Q8 ? 2 * QBUF : 1024u), KBLK, GRP);
             auto issue_qk = [&](int X, int j) {
-                const uint64_t kst = (uint64_t)(((j & 1) * STAGE) >> 4), qst = (uint64_t)((X * TILE) >> 4);
+                const uint64_t kst = (uint64_t)(((j & 1) * KBUF) >> 4), qst = (uint64_t)((X * TILE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ks++) {
                     const uint64_t qoff = (uint64_t)(((ks >> 2) * BLK + (ks & 3) * 32) >> 4);
-                    const uint64_t koff = (uint64_t)(((ks >> 2) * BLKKV + (ks & 3) * 32) >> 4);
+                    const uint64_t koff = (uint64_t)(((ks >> 2) * KBLK + (ks & 3) * 32) >> 4);
                     umma(tmem + X * 128, dq + qst + qoff, dk + kst + koff, id_qk, ks > 0);
                 }
                 umma_commit(b_s_full + X * 8);
+                if (Q8 && X == 1) umma_commit(b_kv_empty + (j & 1) * 8);  // both tiles' scores of this K buffer have been issued
             };
             auto issue_pv = [&](int X, int j) {
-                const uint64_t vst = (uint64_t)(((j & 1) * STAGE) >> 4);
+                const uint64_t vst = Q8 ? 0ull : (uint64_t)(((j & 1) * STAGE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // 16 keys = one page per step; P: 8 packed columns per step
-                    umma_ts(tmem + 256 + X * 128, tmem + X * 128 + ks * 8, dv + vst + (uint64_t)((ks * 4096) >> 4), id_pv, (j > 0 || ks > 0));
+                    umma_ts(tmem + 256 + X * 128, tmem + X * 128 + ks * 8, dv + vst + (uint64_t)((ks * VPAGE) >> 4), id_pv, (j > 0 || ks > 0));
                 umma_commit(b_o_done + X * 8);
             };
             long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0, c_pv = 0;
@@ -691,6 +847,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                 TC_ACC(c_iss);
                 ok = mbar_wait_bounded(b_p_full, j & 1) && !*failed;
                 TC_ACC(c_wp);
+                if (Q8 && ok) { ok = mbar_wait_bounded(b_v_full, j & 1); TC_ACC(c_wkv); }
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(0, j);
@@ -709,7 +866,8 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
                 tc_fence_after();
                 issue_pv(1, j);
                 TC_ACC(c_pv);
-                umma_commit(b_kv_empty + (j & 1) * 8);  // every read of this stage has been issued before
+                // every read of this stage (int8 layer: of the V buffer) has been issued before
+                umma_commit(Q8 ? b_v_empty : b_kv_empty + (j & 1) * 8);
                 if (j + 1 < n_tiles) issue_qk(1, j + 1);
             }
             if (!ok) { *failed = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); }
@@ -717,7 +875,7 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
             TC_DUMP(a.dbg_buf[(size_t)blockIdx.x * 16 + 2] = c_wkv; a.dbg_buf[(size_t)blockIdx.x * 16 + 3] = c_wp; a.dbg_buf[(size_t)blockIdx.x * 16 + 4] = c_iss;
                     a.dbg_buf[(size_t)blockIdx.x * 16 + 11] = c_pv;);
         }
-    } else {
+    } else if (warp >= 2 && warp < 18) {
         // ------------------------------------------------------------ softmax + epilogue of tile X, half H of the keys
         const int X = (warp - 2) >> 3, H = ((warp - 2) >> 2) & 1;
         const int lane_base = (warp & 3) * 32;  // the quarter of the tensor-memory lanes this warp may touch
@@ -864,18 +1022,19 @@ __global__ void __launch_bounds__(kThreads2) chunk_tc2_kernel(const __grid_const
 }
 
 template <bool BF16>
-static cudaError_t launch_tc2(const CUtensorMap& map32, const ChunkArgs& a, cudaStream_t st) {
+static cudaError_t launch_tc2(const CUtensorMap& map32, const CUtensorMap& map_sc, const ChunkArgs& a, cudaStream_t st) {
     if (a.n_items <= 0) return cudaSuccess;
-    chunk_tc2_kernel<128, BF16><<<a.n_items, kThreads2, tc2_smem_bytes<128>(), st>>>(map32, a);
+    if (a.q8_arena) chunk_tc2_kernel<128, BF16, true><<<a.n_items, kThreads2Q8, tc2_smem_bytes_q8<128>(), st>>>(map32, map_sc, a);
+    else chunk_tc2_kernel<128, BF16, false><<<a.n_items, kThreads2, tc2_smem_bytes<128>(), st>>>(map32, map_sc, a);
     return cudaGetLastError();
 }
 
 bool chunk_tc2_supported(int d) { return d == 128; }
 
 // Two query tiles per CTA (head_dim 128): the work list has one item per pair of tiles.
-cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const ChunkArgs& a, bool bf16, cudaStream_t st) {
+cudaError_t launch_chunk_tc2(const CUtensorMap& map32, const CUtensorMap& map_sc, const ChunkArgs& a, bool bf16, cudaStream_t st) {
     if (a.geo.d != 128) return cudaErrorInvalidValue;
-    return bf16 ? launch_tc2<true>(map32, a, st) : launch_tc2<false>(map32, a, st);
+    return bf16 ? launch_tc2<true>(map32, map_sc, a, st) : launch_tc2<false>(map32, map_sc, a, st);
 }
 
 bool chunk_tc_supported(int d) { return d == 64 || d == 128 || d == 256; }
@@ -888,8 +1047,10 @@ cudaError_t chunk_tc_init() {
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<128>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<256>())) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(chunk_tc_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<256>())) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes_q8<128>())) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(chunk_tc2_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2_smem_bytes_q8<128>())) != cudaSuccess) return e;
     return cudaSuccess;
 }
 

@@ -309,7 +309,9 @@ class KVArena:
 
     def set_chunk_kernel(self, mode: int) -> None:
         """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM kernel (one query tile per
-        CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128)."""
+        CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128); int8 layers are read
+        through a float copy made per layer and step, except in mode 4 = as 3 with the int8 records
+        converted inside the kernel (slower so far)."""
         check(self._lib.cbkv_set_chunk_kernel(self._h, mode))
 
     def set_decode_split(self, tail_pct: int = -1, min_item: int = -1, max_levels: int = -1) -> None:

@@ -331,8 +331,11 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
 
 /* Which kernel runs a step that is not pure decode: 0 = the library chooses (tcgen05
  * tiles once the step has at least 64 new tokens), 1 = the mma.sync kernel, 2 = the
- * tcgen05/TMEM kernel with one 128-row query tile per CTA (head_dim 64 or 128), 3 = the
- * tcgen05/TMEM kernel with two query tiles per CTA and P in tensor memory (head_dim 128). */
+ * tcgen05/TMEM kernel with one 128-row query tile per CTA (head_dim 64, 128 or 256), 3 = the
+ * tcgen05/TMEM kernel with two query tiles per CTA and P in tensor memory (head_dim 128).
+ * Over int8 layers these kernels read a float copy of the step's pages made per layer and
+ * step; 4 = as 3, but the kernel fetches the int8 records and converts them itself (no
+ * float copy; slower so far, kept for measurement). */
 int32_t cbkv_set_chunk_kernel(cbkv_arena* arena, int32_t mode);
 
 /* ---- test hooks (host only, no device is touched) --------------------------- */

@@ -192,6 +192,25 @@ def test_chunks_over_int8_layers_run_on_the_tensor_core_kernels(n_q, n_kv, d, ch
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n_q", [32, 28])
+def test_two_tile_kernel_converts_int8_records_itself(n_q):
+    # chunk kernel mode 4: no float copy, the tcgen05 kernel fetches the half-records of every page and
+    # converts them in registers; same tolerance against the oracle as the default route, and the same
+    # result as that route to within float rounding of the output
+    outs = []
+    for mode in (4, 0):
+        p = Pair(2, n_q, 4, 128, 4096, num_pages=400, seed=41, shuffle_free_list=True, quantize_kv=True, chunk_kernel=mode)
+        a, b, c = p.new_seq(), p.new_seq(), p.new_seq()
+        p.step([a, b, c], [700, 130, 257])                  # several K/V tiles per CTA, ragged last pages
+        p.step([a, b], [1, 1])
+        outs.append(p.step([a, c], [256, 300], window=500))  # a second chunk over the cached prefix, with a window
+        p.step([a, b, c], [1, 1, 1])
+        p.assert_state_equal(pages="used")
+    if outs[0] is not None:
+        np.testing.assert_allclose(np.asarray(outs[0], np.float32), np.asarray(outs[1], np.float32), atol=2e-3, rtol=1e-2)
+
+
+@pytest.mark.gpu
 def test_int8_pages_with_prefix_sharing_and_churn():
     # shared prefix pages (refcounted), decode with the quantising append inside the kernel, rollback to the
     # prefix and replacement: private pages only are ever written, packed records stay bit-exact
