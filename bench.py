@@ -263,6 +263,8 @@ class DecodeRun:
         self.arena.set_free_list(np.random.default_rng(w.seed + 7 + seed_salt).permutation(w.arena_pages))
         if args.ctas_per_sm or args.stages or args.consumers or args.no_overlap or args.max_ctas:
             self.arena.set_decode_tuning(args.ctas_per_sm, args.stages, args.consumers, args.max_ctas, not args.no_overlap)
+        if args.host_copies:
+            self.arena.set_host_route(False)
         if args.split:
             self.arena.set_decode_split(*[int(x) for x in args.split.split(",")])
         self.gen = torch.Generator(device=self.dev).manual_seed(w.seed + seed_salt)
@@ -876,6 +878,7 @@ def main():
     ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8, 12)")
     ap.add_argument("--max-ctas", type=int, default=0, help="tuning: upper bound on the CTAs of a decode launch")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
+    ap.add_argument("--host-copies", action="store_true", help="e2e leg: events and copies around every kernel instead of the flag / pinned-output route")
     ap.add_argument("--split", default="", help="tuning: tail_pct,min_item,max_levels of the decode work split (min_item 0 = static split)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")

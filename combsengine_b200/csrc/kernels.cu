@@ -1016,6 +1016,21 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     int seg = have ? it.z : 0, pb = have ? it.x : 0;
     Piece cur = load_piece(a, seg);
     pdl_wait();  // q, k_new and v_new come from earlier work in the stream
+    if (a.in_flag != nullptr) {
+        // ... or from copies on another stream, which end by writing this launch's number behind the data:
+        // one lane looks until it is there (bounded like every wait; a copy engine makes progress whatever
+        // this kernel does), the warp meets, and only then are the inputs read
+        if (lane == 0) {
+            const uint64_t t0 = global_ns(), lim = (uint64_t)a.wait_us * 1000ull;
+            uint32_t seen;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.in_flag) : "memory");
+                if ((int32_t)(seen - a.in_seq) >= 0) break;
+                if (global_ns() - t0 > lim) { atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
+            }
+        }
+        __syncwarp();
+    }
     uint32_t qf[1][D / 16][2];
     if constexpr (Q8) load_q_frags_q8<D>(a, cur, g, t, qf);
     else load_q_frags<D>(a, cur, g, t, qf);

@@ -106,6 +106,8 @@ struct DecodeArgs {
     int32_t comb_bufs;  // 1 or 2 merge buffers
     int32_t kv_dep;     // 1: earlier work in the stream wrote this layer's pages or unit_row: the producer waits for it
     uint32_t wait_us;   // limit of every bounded wait on a tile, microseconds
+    const uint32_t* in_flag;  // non-null: q, k_new, v_new arrive by copies on another stream, which writes in_seq here after them
+    uint32_t in_seq;
     int32_t fault_tile; // test hook: the copy of this tile of CTA 0 is never issued (-1 = none), so its consumer's wait runs out
 #ifdef CBKV_MEASURE
     unsigned long long* dbg_buf;  // per-CTA timestamps

@@ -307,6 +307,11 @@ class KVArena:
         check(self._lib.cbkv_set_decode_tuning(self._h, ctas_per_sm, stages, consumers, max_ctas,
                                                1 if overlap_launches else 0))
 
+    def set_host_route(self, direct: bool) -> None:
+        """attention_host_async on decode steps: True (default) = no stream operation between the kernels (they
+        wait for their inputs' flag and write the pinned output themselves), False = events and copies."""
+        check(self._lib.cbkv_set_host_route(self._h, 1 if direct else 0))
+
     def set_chunk_kernel(self, mode: int) -> None:
         """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM kernel (one query tile per
         CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128); int8 layers are read

@@ -201,6 +201,43 @@ def test_host_buffer_entry_point_matches_device_one():
         assert torch.equal(o, r)
 
 
+@pytest.mark.parametrize("direct", [True, False])
+def test_host_buffer_pipeline_over_many_layers_and_steps(direct):
+    # Decode steps over 5 layers through attention_host_async, 9 steps without a host_sync in between: 45 calls
+    # in flight over the 32 input slots of the direct route (the kernels wait for their inputs' flag and
+    # write the pinned outputs themselves) or the 4 staging slots of the copy route; pageable outputs take
+    # the copy route whatever the setting.  Every output must equal the device entry point's.
+    layers, n_q, n_kv, d = 5, 28, 4, 128
+    p = Pair(layers, n_q, n_kv, d, 2048, num_pages=400, seed=23, shuffle_free_list=True)
+    seqs = [p.new_seq() for _ in range(3)]
+    p.step(seqs, [300, 17, 130], check=False)
+    g = p.g
+    g.set_host_route(direct)
+    gs = [s[0] for s in seqs]
+    n = len(gs)
+    steps = 9
+    mk = lambda heads, pinned: (torch.randn(n * heads * d).half().pin_memory() if pinned else torch.randn(n * heads * d).half())
+    qs = [[mk(n_q, True) for _ in range(layers)] for _ in range(steps)]
+    ks = [[mk(n_kv, True) for _ in range(layers)] for _ in range(steps)]
+    vs = [[mk(n_kv, True) for _ in range(layers)] for _ in range(steps)]
+    outs = [[(torch.empty(n * n_q * d).half().pin_memory() if (t + l) % 7 else torch.empty(n * n_q * d).half())
+             for l in range(layers)] for t in range(steps)]
+    for t in range(steps):
+        g.begin_step(gs, [1] * n)
+        for l in range(layers):
+            g.attention_host_async(l, qs[t][l], ks[t][l], vs[t][l], outs[t][l], 0.09)
+    g.host_sync()
+    assert g.device_status() == 0
+    for s_ in gs:
+        assert s_.popn(steps) == steps
+    for t in range(steps):
+        g.begin_step(gs, [1] * n)
+        for l in range(layers):
+            ref = g.attention(l, qs[t][l].cuda(), ks[t][l].cuda(), vs[t][l].cuda(), 0.09).cpu()
+            assert torch.equal(outs[t][l], ref), (t, l)
+    assert g.device_status() == 0
+
+
 def test_one_long_sequence_is_cut_into_many_parts():
     # a single 20 000-token sequence: every (kv head) segment is split over dozens of CTAs, so the
     # ticket merge runs with far more than eight partials
