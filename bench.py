@@ -878,7 +878,7 @@ def main():
     ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8, 12)")
     ap.add_argument("--max-ctas", type=int, default=0, help="tuning: upper bound on the CTAs of a decode launch")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
-    ap.add_argument("--host-copies", action="store_true", help="e2e leg: events and copies around every kernel instead of the flag / pinned-output route")
+    ap.add_argument("--host-copies", action="store_true", help="e2e leg: the compute stream waits for the input copies before every kernel instead of the kernels reading a flag")
     ap.add_argument("--split", default="", help="tuning: tail_pct,min_item,max_levels of the decode work split (min_item 0 = static split)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other configurations")

@@ -135,25 +135,16 @@ struct DeviceState {
         cudaEvent_t in_done = nullptr, k_done = nullptr, out_done = nullptr;
         bool used = false;
     };
-    IoSlot io_slots[4];
+    static constexpr int kIoSlots = 32;
+    IoSlot io_slots[kIoSlots];
     int io_cur = 0;
     cudaStream_t h2d = nullptr, d2h = nullptr;
-    // Decode steps with a device-visible output buffer skip every stream operation between the kernels (an
-    // event wait or record there ends the overlap of consecutive launches): the kernel writes its output to
-    // the caller's pinned buffer itself and learns that its inputs have arrived from a number the copy
-    // stream writes behind them (DecodeArgs::in_flag).
-    static constexpr int kInSlots = 32;
-    struct InSlot {
-        uint8_t* dev = nullptr;
-        size_t cap = 0;
-        uint64_t used_seq = 0;  // the launch that last read it
-    };
-    InSlot in_slots[kInSlots];
+    // Decode steps do not make the compute stream wait for the input copies' event (a wait between two
+    // kernels ends the overlap of consecutive launches; an event record does not): the kernel itself waits for
+    // a number that the copy stream writes behind its inputs (DecodeArgs::in_flag).
     uint32_t* in_flags = nullptr;      // device, one per slot
     uint32_t* in_seq_host = nullptr;   // pinned, the source of each slot's flag copy
-    uint64_t in_seq = 0, in_mark_seq = 0, in_done_seq = 0;  // launches enqueued / covered by in_mark / known complete
-    cudaEvent_t in_mark = nullptr;
-    cudaStream_t in_stream = nullptr;  // the compute stream of the launches not yet synchronised
+    uint32_t in_seq = 0;
     const uint32_t* next_in_flag = nullptr;  // handed to the next decode launch
     uint32_t next_in_seq = 0;
 #ifdef CBKV_MEASURE
@@ -683,10 +674,8 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
             if (sl.in_done) { cudaEventDestroy(sl.in_done); cudaEventDestroy(sl.k_done); cudaEventDestroy(sl.out_done); }
         }
         if (d->h2d) { cudaStreamDestroy(d->h2d); cudaStreamDestroy(d->d2h); }
-        for (auto& sl : d->in_slots) if (sl.dev) cudaFree(sl.dev);
         if (d->in_flags) cudaFree(d->in_flags);
         if (d->in_seq_host) cudaFreeHost(d->in_seq_host);
-        if (d->in_mark) cudaEventDestroy(d->in_mark);
         for (auto& p : d->prof) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
         delete d;
     }
@@ -740,13 +729,6 @@ int32_t cbkv_begin_step(cbkv_arena* arena, cbkv_seq* const* seqs, const int64_t*
     if (rc) return rc;
     rc = begin_step(a, reinterpret_cast<Seq* const*>(seqs), new_tokens, pos, n_seqs);
     if (rc) return rc;
-    DeviceState* d = dev_of(a);
-    if (d->in_mark && d->in_seq > d->in_mark_seq) {
-        // a step boundary separates the launches anyway (the step's tables are uploaded between them), so
-        // this is the free place to mark how far the host-buffer launches have got
-        CU_TRY(cudaEventRecord(d->in_mark, d->in_stream));
-        d->in_mark_seq = d->in_seq;
-    }
     return upload_step(a, static_cast<cudaStream_t>(stream));
     });
 }
@@ -1046,67 +1028,10 @@ int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* 
     const size_t qb = (size_t)a->step_tokens * a->cfg.n_q_heads * a->cfg.head_dim * 2;
     const size_t kb = (size_t)a->step_tokens * a->cfg.n_kv_heads * a->cfg.head_dim * 2;
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-    if (d->fast && a->step_is_decode && d->host_direct) {
-        cudaPointerAttributes attr{};
-        void* out_dev = nullptr;
-        if (cudaPointerGetAttributes(&attr, out_host) == cudaSuccess && attr.type == cudaMemoryTypeHost) out_dev = attr.devicePointer;
-        else cudaGetLastError();
-        if (out_dev) {
-            if (!d->in_flags) {
-                CU_TRY(cudaMalloc(&d->in_flags, DeviceState::kInSlots * sizeof(uint32_t)));
-                CU_TRY(cudaMemset(d->in_flags, 0, DeviceState::kInSlots * sizeof(uint32_t)));
-                CU_TRY(cudaMallocHost(&d->in_seq_host, DeviceState::kInSlots * sizeof(uint32_t)));
-                CU_TRY(cudaEventCreateWithFlags(&d->in_mark, cudaEventDisableTiming));
-            }
-            if (d->in_stream && d->in_stream != st && d->in_done_seq < d->in_seq) {  // the caller changed streams: finish the old one first
-                CU_TRY(cudaStreamSynchronize(d->in_stream));
-                d->in_done_seq = d->in_mark_seq = d->in_seq;
-            }
-            const uint64_t seq = ++d->in_seq;
-            const int si = (int)(seq % DeviceState::kInSlots);
-            DeviceState::InSlot& sl = d->in_slots[si];
-            if (sl.used_seq > d->in_done_seq) {  // the launch that last read this slot may not be over
-                if (d->in_mark_seq < sl.used_seq) {  // no mark covers it yet: one now, after everything enqueued so far
-                    CU_TRY(cudaEventRecord(d->in_mark, st));
-                    d->in_mark_seq = seq - 1;
-                }
-                CU_TRY(cudaEventSynchronize(d->in_mark));
-                d->in_done_seq = d->in_mark_seq;
-            }
-#ifdef CBKV_MEASURE
-            static const bool exp_out_dev = getenv("CBKV_EXP_OUT_DEV") != nullptr;  // timing experiment: the output stays on the device
-            const size_t need = up(qb) + 2 * up(kb) + (exp_out_dev ? up(qb) : 0);
-#else
-            const size_t need = up(qb) + 2 * up(kb);
-#endif
-            if (need > sl.cap) {
-                if (sl.dev) CU_TRY(cudaFree(sl.dev));
-                sl.cap = need * 2;
-                CU_TRY(cudaMalloc(&sl.dev, sl.cap));
-            }
-            uint8_t* qd = sl.dev;
-            uint8_t* kd = qd + up(qb);
-            uint8_t* vd = kd + up(kb);
-#ifdef CBKV_MEASURE
-            if (exp_out_dev) out_dev = vd + up(kb);
-#endif
-            CU_TRY(cudaMemcpyAsync(qd, q_host, qb, cudaMemcpyHostToDevice, d->h2d));
-            CU_TRY(cudaMemcpyAsync(kd, k_host, kb, cudaMemcpyHostToDevice, d->h2d));
-            CU_TRY(cudaMemcpyAsync(vd, v_host, kb, cudaMemcpyHostToDevice, d->h2d));
-            d->in_seq_host[si] = (uint32_t)seq;  // stable until the slot comes round again, long after this copy
-            CU_TRY(cudaMemcpyAsync(d->in_flags + si, d->in_seq_host + si, sizeof(uint32_t), cudaMemcpyHostToDevice, d->h2d));
-            d->next_in_flag = d->in_flags + si;
-            d->next_in_seq = (uint32_t)seq;
-            rc = cbkv_attention(arena, layer, qd, kd, vd, out_dev, scale, window, stream);
-            d->next_in_flag = nullptr;
-            sl.used_seq = seq;
-            d->in_stream = st;
-            return rc;
-        }
-    }
     const size_t need = 2 * up(qb) + 2 * up(kb);
-    DeviceState::IoSlot& sl = d->io_slots[d->io_cur];
-    d->io_cur = (d->io_cur + 1) % 4;
+    const int si = d->io_cur;
+    DeviceState::IoSlot& sl = d->io_slots[si];
+    d->io_cur = (d->io_cur + 1) % DeviceState::kIoSlots;
     if (!sl.in_done) {
         CU_TRY(cudaEventCreateWithFlags(&sl.in_done, cudaEventDisableTiming));
         CU_TRY(cudaEventCreateWithFlags(&sl.k_done, cudaEventDisableTiming));
@@ -1125,9 +1050,24 @@ int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* 
     CU_TRY(cudaMemcpyAsync(qd, q_host, qb, cudaMemcpyHostToDevice, d->h2d));
     CU_TRY(cudaMemcpyAsync(kd, k_host, kb, cudaMemcpyHostToDevice, d->h2d));
     CU_TRY(cudaMemcpyAsync(vd, v_host, kb, cudaMemcpyHostToDevice, d->h2d));
-    CU_TRY(cudaEventRecord(sl.in_done, d->h2d));
-    CU_TRY(cudaStreamWaitEvent(st, sl.in_done, 0));
+    if (d->fast && a->step_is_decode && d->host_direct) {
+        // the decode kernel waits for this number itself (bounded), after its wait for the previous launch
+        if (!d->in_flags) {
+            CU_TRY(cudaMalloc(&d->in_flags, DeviceState::kIoSlots * sizeof(uint32_t)));
+            CU_TRY(cudaMemset(d->in_flags, 0, DeviceState::kIoSlots * sizeof(uint32_t)));
+            CU_TRY(cudaMallocHost(&d->in_seq_host, DeviceState::kIoSlots * sizeof(uint32_t)));
+        }
+        const uint32_t seq = ++d->in_seq;
+        d->in_seq_host[si] = seq;  // stable until the slot comes round again, by when this copy is long done
+        CU_TRY(cudaMemcpyAsync(d->in_flags + si, d->in_seq_host + si, sizeof(uint32_t), cudaMemcpyHostToDevice, d->h2d));
+        d->next_in_flag = d->in_flags + si;
+        d->next_in_seq = seq;
+    } else {
+        CU_TRY(cudaEventRecord(sl.in_done, d->h2d));
+        CU_TRY(cudaStreamWaitEvent(st, sl.in_done, 0));
+    }
     rc = cbkv_attention(arena, layer, qd, kd, vd, od, scale, window, stream);
+    d->next_in_flag = nullptr;
     if (rc) return rc;
     CU_TRY(cudaEventRecord(sl.k_done, st));
     CU_TRY(cudaStreamWaitEvent(d->d2h, sl.k_done, 0));
@@ -1147,10 +1087,6 @@ int32_t cbkv_host_sync(cbkv_arena* arena) {
     CU_TRY(cudaSetDevice(d->device));
     for (auto& sl : d->io_slots)
         if (sl.used) CU_TRY(cudaEventSynchronize(sl.out_done));
-    if (d->in_done_seq < d->in_seq) {  // launches that write the caller's buffers themselves
-        CU_TRY(cudaStreamSynchronize(d->in_stream));
-        d->in_done_seq = d->in_mark_seq = d->in_seq;
-    }
     return CBKV_OK;
     });
 }

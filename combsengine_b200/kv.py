@@ -308,8 +308,8 @@ class KVArena:
                                                1 if overlap_launches else 0))
 
     def set_host_route(self, direct: bool) -> None:
-        """attention_host_async on decode steps: True (default) = no stream operation between the kernels (they
-        wait for their inputs' flag and write the pinned output themselves), False = events and copies."""
+        """attention_host_async on decode steps: True (default) = the kernel waits for a flag written behind its
+        inputs, False = the compute stream waits for the input copies' event before every kernel."""
         check(self._lib.cbkv_set_host_route(self._h, 1 if direct else 0))
 
     def set_chunk_kernel(self, mode: int) -> None:

@@ -148,12 +148,11 @@ int32_t cbkv_attention_host(cbkv_arena* arena, int32_t layer, const void* q_host
                             const void* v_host, void* out_host, double scale, int64_t window, void* stream);
 /* The same call without the wait: the copies run on the library's own copy streams
  * so that layer l+1's inputs and layer l's output move while a kernel runs; `out_host`
- * is valid after cbkv_host_sync.  Needs pinned buffers to overlap.  On a decode step whose
- * `out_host` is pinned, nothing is put on `stream` between the kernels of consecutive layers
- * (an event there would end their overlap): the kernel writes `out_host` itself and waits for
- * a number that the copy stream writes behind its inputs; 32 calls can be in flight.
- * Otherwise the output comes back by a copy on a second stream, with up to four calls in
- * flight. */
+ * is valid after cbkv_host_sync.  Needs pinned buffers to overlap; 32 calls can be in flight,
+ * a 33rd waits for the oldest.  On a decode step `stream` is not made to wait for the input
+ * copies (a wait between two kernels would end the overlap of consecutive layers' launches):
+ * the kernel itself waits, with the usual limit, for a number that the copy stream writes
+ * behind its inputs. */
 int32_t cbkv_attention_host_async(cbkv_arena* arena, int32_t layer, const void* q_host, const void* k_host,
                                   const void* v_host, void* out_host, double scale, int64_t window, void* stream);
 int32_t cbkv_host_sync(cbkv_arena* arena);
@@ -333,9 +332,8 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
 int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t stages, int32_t consumers,
                                int32_t max_ctas, int32_t overlap_launches);
 
-/* cbkv_attention_host_async on decode steps: 1 (default) = the kernels read their inputs' arrival
- * from a flag and write pinned output buffers themselves, 0 = events and copies around every
- * kernel (what other steps and pageable buffers use). */
+/* cbkv_attention_host_async on decode steps: 1 (default) = the kernel reads its inputs' arrival from a
+ * flag, 0 = `stream` waits for the input copies' event before every kernel (what other steps use). */
 int32_t cbkv_set_host_route(cbkv_arena* arena, int32_t direct);
 
 /* Which kernel runs a step that is not pure decode: 0 = the library chooses (tcgen05

@@ -204,9 +204,9 @@ def test_host_buffer_entry_point_matches_device_one():
 @pytest.mark.parametrize("direct", [True, False])
 def test_host_buffer_pipeline_over_many_layers_and_steps(direct):
     # Decode steps over 5 layers through attention_host_async, 9 steps without a host_sync in between: 45 calls
-    # in flight over the 32 input slots of the direct route (the kernels wait for their inputs' flag and
-    # write the pinned outputs themselves) or the 4 staging slots of the copy route; pageable outputs take
-    # the copy route whatever the setting.  Every output must equal the device entry point's.
+    # over the 32 rotating slots, the kernels waiting for their inputs' flag (direct) or the stream waiting for
+    # the input copies' event; pinned and pageable outputs mixed.  Every output must equal the device entry
+    # point's.
     layers, n_q, n_kv, d = 5, 28, 4, 128
     p = Pair(layers, n_q, n_kv, d, 2048, num_pages=400, seed=23, shuffle_free_list=True)
     seqs = [p.new_seq() for _ in range(3)]
