@@ -714,6 +714,8 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
     arena.set_free_list(np.random.default_rng(0xC0B50004).permutation(arena.num_pages))
     if chunk_kernel:
         arena.set_chunk_kernel(chunk_kernel)
+    if args.chunk_split:
+        arena.set_chunk_split(args.chunk_split)
     seqs = [arena.new_seq() for _ in range(batch)]
     gen = torch.Generator(device=dev).manual_seed(0xC0B50004)
     ntok = batch * chunk
@@ -877,6 +879,7 @@ def main():
     ap.add_argument("--stages", type=int, default=0, help="tuning: TMA ring stages (0 = default)")
     ap.add_argument("--consumers", type=int, default=0, help="tuning: consumer warps per decode CTA (4, 6, 8, 12)")
     ap.add_argument("--max-ctas", type=int, default=0, help="tuning: upper bound on the CTAs of a decode launch")
+    ap.add_argument("--chunk-split", type=int, default=0, help="cfg4 only: most K/V slices per item of a launch's last wave (1 = never cut; default: the library's 4)")
     ap.add_argument("--no-overlap", action="store_true", help="tuning: no programmatic dependent launch")
     ap.add_argument("--host-copies", action="store_true", help="e2e leg: the compute stream waits for the input copies before every kernel instead of the kernels reading a flag")
     ap.add_argument("--split", default="", help="tuning: tail_pct,min_item,max_levels of the decode work split (min_item 0 = static split)")

@@ -178,6 +178,7 @@ extern "C" {
     pub fn cbkv_profile_read(arena: *mut cbkv_arena, total_ms: *mut f64, launches: *mut i64) -> i32;
     pub fn cbkv_set_decode_tuning(arena: *mut cbkv_arena, ctas_per_sm: i32, stages: i32, consumers: i32, max_ctas: i32, overlap_launches: i32) -> i32;
     pub fn cbkv_set_host_route(arena: *mut cbkv_arena, direct: i32) -> i32;
+    pub fn cbkv_set_chunk_split(arena: *mut cbkv_arena, max_parts: i32) -> i32;
     pub fn cbkv_set_chunk_kernel(arena: *mut cbkv_arena, mode: i32) -> i32;
     pub fn cbkv_set_decode_split(arena: *mut cbkv_arena, tail_pct: i32, min_item: i32, max_levels: i32) -> i32;
 

@@ -96,6 +96,7 @@ PROTOTYPES = {
     "cbkv_set_decode_tuning": (I32, [P, I32, I32, I32, I32, I32]),
     "cbkv_set_chunk_kernel": (I32, [P, I32]),
     "cbkv_set_host_route": (I32, [P, I32]),
+    "cbkv_set_chunk_split": (I32, [P, I32]),
     "cbkv_debug_begin_step_host": (I32, [P, C.POINTER(P), C.POINTER(I64), C.POINTER(I64), I32]),
     "cbkv_debug_decode_plan": (I64, [P, I64, I32, I32, I32, C.POINTER(I32), I64]),
     "cbkv_set_decode_split": (I32, [P, I32, I32, I32]),

@@ -119,6 +119,12 @@ struct DeviceState {
     int decode_ctas_per_sm = 0, decode_stages = 0, decode_consumers = 0, decode_max_ctas = 0;
     bool pdl = true;
     bool host_direct = true;  // cbkv_set_host_route
+    // two-tile chunk kernel: slices of the items of a launch's last, mostly empty wave (ChunkArgs::split_*)
+    int chunk_split = 4;               // most slices per item, 1 = never cut (cbkv_set_chunk_split)
+    float* split_o = nullptr;
+    float2* split_ml = nullptr;
+    int32_t* split_counter = nullptr;
+    int split_cap = 0;                 // slices the buffers hold
     int last_kv_writer = -1;  // layer whose pages the most recent launch wrote (-1: none since the last upload)
     // host-buffer entry point staging
     uint8_t* io = nullptr;
@@ -348,6 +354,7 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->unit_rows_used = 0;
     // tickets and claim counters start every step at zero, whatever an earlier launch that gave up left behind
     if (d->seg_counter) CU_TRY(cudaMemsetAsync(d->seg_counter, 0, d->counter_cap * sizeof(int32_t), st));
+    if (d->split_counter) CU_TRY(cudaMemsetAsync(d->split_counter, 0, (size_t)d->split_cap * sizeof(int32_t), st));
     if (d->work_counters) CU_TRY(cudaMemsetAsync(d->work_counters, 0, 4 * sizeof(int32_t), st));
     if (a->step_meta.empty()) {  // an empty step: nothing to upload, nothing will launch
         d->uploaded_step = a->step_id;
@@ -601,11 +608,38 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.step = d->step; args.geo = geom(a); args.item_begin = d->tile_item_begin; args.n_items = d->tile_host.n_items;
         args.q = q; args.out = out; args.status = d->status; args.window = (int32_t)w; args.scale_log2 = scale_log2; args.rep_slots = rs;
         args.q8_arena = q8_direct ? L.base : nullptr;
+        if (use_tc2 && d->chunk_split > 1) {
+            // The grid runs one CTA per SM at a time.  When the last wave would fill at most half of the SMs, its
+            // items are cut along K/V so that the wave is full and ends sooner (the slices are merged by whichever
+            // CTA of an item finishes last).  Only worth it when every slice still has a few K/V tiles.
+            const int n_items = d->tile_host.n_items, rem = n_items % d->sm_count;
+            int parts = rem > 0 ? std::min(d->chunk_split, d->sm_count / rem) : 1;
+            int64_t min_keys = INT64_MAX;
+            for (const auto& m : a->step_meta) {
+                const int64_t keys = w > 0 ? std::min<int64_t>(w, (int64_t)m.pos + m.snew) : (int64_t)m.pos + m.snew;
+                min_keys = std::min(min_keys, keys);
+            }
+            while (parts > 1 && min_keys < (int64_t)parts * 8 * 128) parts--;  // measured: below 8 tiles per slice the merge costs more than the wave saves
+            if (parts > 1) {
+                const int slices = rem * parts;
+                if (slices > d->split_cap) {
+                    CU_TRY(cudaStreamSynchronize(st));
+                    if (d->split_o) { cudaFree(d->split_o); cudaFree(d->split_ml); cudaFree(d->split_counter); }
+                    d->split_cap = std::max(slices, d->sm_count);
+                    CU_TRY(cudaMalloc(&d->split_o, (size_t)d->split_cap * 2 * 128 * 128 * sizeof(float)));
+                    CU_TRY(cudaMalloc(&d->split_ml, (size_t)d->split_cap * 2 * 128 * sizeof(float2)));
+                    CU_TRY(cudaMalloc(&d->split_counter, (size_t)d->split_cap * sizeof(int32_t)));
+                    CU_TRY(cudaMemsetAsync(d->split_counter, 0, (size_t)d->split_cap * sizeof(int32_t), st));
+                }
+                args.split_first = n_items - rem; args.split_parts = parts;
+                args.split_o = d->split_o; args.split_ml = d->split_ml; args.split_counter = d->split_counter;
+            }
+        }
 #ifdef CBKV_MEASURE
         if (debug_flags() & 8) {  // per-role cycle counters of the first 4096 CTAs
             if (!d->dbg_buf) { CU_TRY(cudaMalloc(&d->dbg_buf, 4096 * 16 * sizeof(unsigned long long))); }
             CU_TRY(cudaMemsetAsync(d->dbg_buf, 0, 4096 * 16 * sizeof(unsigned long long), st));
-            if (d->tile_host.n_items <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
+            if (d->tile_host.n_items + d->sm_count * 4 <= 4096) { args.dbg_buf = d->dbg_buf; d->dbg_ctas = -d->tile_host.n_items; }
         }
 #endif
         ProfScope ps(d, st);
@@ -674,6 +708,7 @@ int32_t cbkv_arena_destroy(cbkv_arena* arena) {
             if (sl.in_done) { cudaEventDestroy(sl.in_done); cudaEventDestroy(sl.k_done); cudaEventDestroy(sl.out_done); }
         }
         if (d->h2d) { cudaStreamDestroy(d->h2d); cudaStreamDestroy(d->d2h); }
+        if (d->split_o) { cudaFree(d->split_o); cudaFree(d->split_ml); cudaFree(d->split_counter); }
         if (d->in_flags) cudaFree(d->in_flags);
         if (d->in_seq_host) cudaFreeHost(d->in_seq_host);
         for (auto& p : d->prof) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
@@ -1409,6 +1444,17 @@ int32_t cbkv_set_host_route(cbkv_arena* arena, int32_t direct) {
     int32_t rc = ensure_device(a);
     if (rc) return rc;
     dev_of(a)->host_direct = direct != 0;
+    return CBKV_OK;
+    });
+}
+
+int32_t cbkv_set_chunk_split(cbkv_arena* arena, int32_t max_parts) {
+    return fenced([&]() -> int32_t {
+    Arena* a = reinterpret_cast<Arena*>(arena);
+    if (!a || max_parts < 1 || max_parts > 8) { set_error("bad argument"); return CBKV_ERR_ARG; }
+    int32_t rc = ensure_device(a);
+    if (rc) return rc;
+    dev_of(a)->chunk_split = max_parts;
     return CBKV_OK;
     });
 }

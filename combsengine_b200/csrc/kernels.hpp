@@ -127,6 +127,15 @@ struct ChunkArgs {
     float scale_log2;
     int32_t rep_slots;  // tcgen05 kernel: q heads per kv head rounded up to a power of two (rows per token in a tile)
     const void* q8_arena;  // two-tile tcgen05 kernel: non-null = the layer's int8 records, read and converted by the kernel itself
+    // two-tile tcgen05 kernel: the items from split_first on are cut along K/V into split_parts CTAs each (the
+    // last wave of a launch would otherwise leave most SMs idle); each writes its un-normalised rows and their
+    // (reference exponent, sum) to split_o / split_ml and draws a ticket from split_counter, the last one
+    // merges.  split_parts <= 1: no item is cut.  n_items counts items, the grid has
+    // split_first + (n_items - split_first) * split_parts CTAs.
+    int32_t split_first, split_parts;
+    float* split_o;         // float4 [(item - split_first) * split_parts + part][tile 2][column group 32][row 128]
+    float2* split_ml;       // [(item - split_first) * split_parts + part][tile 2][row 128]
+    int32_t* split_counter; // per cut item, zero between launches
 #ifdef CBKV_MEASURE
     unsigned long long* dbg_buf;  // per-CTA cycle counters of the tcgen05 kernel
 #endif

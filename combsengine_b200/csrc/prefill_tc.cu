@@ -64,10 +64,13 @@ __device__ __forceinline__ uint64_t global_ns() {
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns = 200000000ull) {
     for (int i = 0; i < 64; i++)
         if (mbar_try_wait(bar, parity)) return true;
+    // the timer is slow to read, and a read in flight would hold up the return: look at it once per 64 polls
     const uint64_t t0 = global_ns();
-    while (!mbar_try_wait(bar, parity))
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
         if (global_ns() - t0 > limit_ns) return false;
-    return true;
+    }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
@@ -618,7 +621,10 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
         if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
         return;
     }
-    const int item = blockIdx.x;
+    // CTAs past split_first share items: `parts` of them per item, each with a slice of the item's K/V tiles
+    const int parts = (a.split_parts > 1 && (int)blockIdx.x >= a.split_first) ? a.split_parts : 1;
+    const int item = parts > 1 ? a.split_first + ((int)blockIdx.x - a.split_first) / parts : (int)blockIdx.x;
+    const int part = parts > 1 ? ((int)blockIdx.x - a.split_first) % parts : 0;
     int lo = 0, hi = a.step.n_seqs - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -632,8 +638,15 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
     const int r0 = qt * 2 * TPT;                                  // first new token of tile A
     const int q_first = sm.pos + r0, q_last = sm.pos + min(r0 + 2 * TPT, sm.snew) - 1;
     const int lo_key = a.window > 0 ? max(0, q_first - a.window + 1) : 0;
-    const int p_lo = lo_key >> 4, p_hi = q_last >> 4;
-    const int n_tiles = (p_hi - p_lo + 1 + 7) >> 3;
+    int p_lo = lo_key >> 4, p_hi = q_last >> 4;
+    int n_tiles = (p_hi - p_lo + 1 + 7) >> 3;
+    if (parts > 1) {  // this CTA's slice of the tiles (possibly empty: it then hands over rows with sum 0)
+        const int per = (n_tiles + parts - 1) / parts;
+        const int t0 = min(n_tiles, part * per), t1 = min(n_tiles, t0 + per);
+        if (t1 < n_tiles) p_hi = p_lo + 8 * t1 - 1;  // inner slices end on a tile boundary: every page is real
+        p_lo += 8 * t0;
+        n_tiles = t1 - t0;
+    }
     const int k0 = p_lo * 16;
 
     if (tid == 0) {
@@ -841,8 +854,8 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
                 umma_commit(b_o_done + X * 8);
             };
             long long tprev = TC_NOW(), c_wkv = 0, c_wp = 0, c_iss = 0, c_pv = 0;
-            bool ok = mbar_wait_bounded(b_kv_full, 0);
-            if (ok) { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
+            bool ok = n_tiles == 0 || mbar_wait_bounded(b_kv_full, 0);  // an empty slice of a cut item: nothing to issue
+            if (ok && n_tiles > 0) { tc_fence_after(); issue_qk(0, 0); issue_qk(1, 0); }
             for (int j = 0; ok && j < n_tiles; j++) {
                 TC_ACC(c_iss);
                 ok = mbar_wait_bounded(b_p_full, j & 1) && !*failed;
@@ -979,7 +992,7 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
             b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = TC_NOW() - tstart;
         });
         (void)tstart; (void)c_wo;
-        if (ok) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
+        if (ok && n_tiles > 0) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
         ok = __all_sync(0xffffffffu, ok);
         // the row sum is the two halves' sums (exchanged whether or not the wait succeeded: the pair must
         // meet at its barrier the same number of times)
@@ -987,30 +1000,100 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
         xrow[H] = l_run;
         pair_sync();
         const float l_row = l_run + xrow[H ^ 1];
-        if (ok) {
-            tc_fence_after();
-            const float inv = 1.f / l_row;
-            uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) +
-                             ((size_t)sm.tok_off * a.geo.n_q + (size_t)(h * n_rep + (row_ok ? rep : 0)) * sm.snew + (row_ok ? r : 0)) * D;
-#pragma unroll 1
-            for (int c = 2 * H; c < 2 * H + 2; c++) {  // this warp writes the output columns 64 H .. 64 H + 63
-                uint32_t v[32];
-                tmem_ld32(tO + c * 32, v);
-                if (row_ok) {
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        uint4 w;
-                        w.x = pack2<BF16>(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
-                        w.y = pack2<BF16>(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
-                        w.z = pack2<BF16>(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
-                        w.w = pack2<BF16>(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
-                    }
-                }
-            }
-        } else if (lane == 0) {
+        if (!ok && lane == 0) {
             *failed = 1;
             atomicOr(a.status, ST_WAIT_TIMEOUT);
+        }
+        uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) +
+                         ((size_t)sm.tok_off * a.geo.n_q + (size_t)(h * n_rep + (row_ok ? rep : 0)) * sm.snew + (row_ok ? r : 0)) * D;
+        auto store_row = [&](int c, const float (&v)[32], float inv) {  // 32 output columns from c * 32
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                uint4 w;
+                w.x = pack2<BF16>(v[u * 8 + 0] * inv, v[u * 8 + 1] * inv);
+                w.y = pack2<BF16>(v[u * 8 + 2] * inv, v[u * 8 + 3] * inv);
+                w.z = pack2<BF16>(v[u * 8 + 4] * inv, v[u * 8 + 5] * inv);
+                w.w = pack2<BF16>(v[u * 8 + 6] * inv, v[u * 8 + 7] * inv);
+                *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+            }
+        };
+        if (parts == 1) {
+            if (ok) {
+                tc_fence_after();
+                const float inv = 1.f / l_row;
+#pragma unroll 1
+                for (int c = 2 * H; c < 2 * H + 2; c++) {  // this warp writes the output columns 64 H .. 64 H + 63
+                    uint32_t v[32];
+                    tmem_ld32(tO + c * 32, v);
+                    float f[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) f[e] = __uint_as_float(v[e]);
+                    if (row_ok) store_row(c, f, inv);
+                }
+            }
+        } else {
+            // ---- a slice of a cut item: un-normalised rows and their (reference exponent, sum) go to memory, the
+            // CTA draws a ticket, and the CTA that draws the item's last one adds the slices up.  No CTA waits
+            // for another; every softmax warp passes both barriers whatever happened to its waits.
+            const int cut = item - a.split_first;
+            // rows are the fast index of the partial rows in memory (split_o as float4 [slice][tile][32 column
+            // groups][128 rows]): a warp's 32 rows make one contiguous 512-byte access
+            const size_t mine = ((size_t)(cut * parts + part) * 2 + X) * 128 + m;
+            float4* my_o = reinterpret_cast<float4*>(a.split_o) + ((size_t)(cut * parts + part) * 2 + X) * 32 * 128 + m;
+            if (ok) {
+                if (n_tiles > 0) {
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 2 * H; c < 2 * H + 2; c++) {
+                        uint32_t v[32];
+                        tmem_ld32(tO + c * 32, v);
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            my_o[(size_t)(c * 8 + u) * 128] = make_float4(__uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
+                                                                          __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+                    }
+                }
+                if (H == 0) a.split_ml[mine] = make_float2(n_tiles > 0 ? m_ref : -INFINITY, n_tiles > 0 ? l_row : 0.f);
+            }
+            __threadfence();
+            asm volatile("bar.sync 9, 512;" ::: "memory");
+            int* s_ticket = reinterpret_cast<int*>(const_cast<int*>(failed)) + 1;
+            if (tid == 64) {
+                const int tk = atomicAdd(a.split_counter + cut, 1);
+                if (tk == parts - 1) a.split_counter[cut] = 0;  // ready for the next launch
+                *s_ticket = tk;
+            }
+            asm volatile("bar.sync 9, 512;" ::: "memory");
+            if (*s_ticket == parts - 1 && ok && !*failed && row_ok) {
+                __threadfence();
+                const size_t base = ((size_t)cut * parts * 2 + X) * 128 + m;  // slice p: + p * 256
+                float mx = -INFINITY;
+                for (int p = 0; p < parts; p++) mx = fmaxf(mx, __ldcg(&a.split_ml[base + (size_t)p * 256].x));
+                float wsum = 0.f;
+                for (int p = 0; p < parts; p++) {
+                    const float2 ml = __ldcg(&a.split_ml[base + (size_t)p * 256]);
+                    if (ml.x != -INFINITY) wsum += ml.y * exp2f(ml.x - mx);
+                }
+                const float inv = 1.f / wsum;
+#pragma unroll 1
+                for (int c = 2 * H; c < 2 * H + 2; c++) {
+                    float acc[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) acc[e] = 0.f;
+                    for (int p = 0; p < parts; p++) {
+                        const float mp = __ldcg(&a.split_ml[base + (size_t)p * 256].x);
+                        if (mp == -INFINITY) continue;  // an empty slice, or rows it never saw: its rows were not written
+                        const float w = exp2f(mp - mx);
+                        const float4* src = reinterpret_cast<const float4*>(a.split_o) + ((size_t)(cut * parts + p) * 2 + X) * 32 * 128 + m;
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            const float4 t = __ldcg(src + (size_t)(c * 8 + u) * 128);
+                            acc[u * 4] += w * t.x; acc[u * 4 + 1] += w * t.y; acc[u * 4 + 2] += w * t.z; acc[u * 4 + 3] += w * t.w;
+                        }
+                    }
+                    store_row(c, acc, inv);
+                }
+            }
         }
     }
     tc_fence_before();
@@ -1024,8 +1107,9 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
 template <bool BF16>
 static cudaError_t launch_tc2(const CUtensorMap& map32, const CUtensorMap& map_sc, const ChunkArgs& a, cudaStream_t st) {
     if (a.n_items <= 0) return cudaSuccess;
-    if (a.q8_arena) chunk_tc2_kernel<128, BF16, true><<<a.n_items, kThreads2Q8, tc2_smem_bytes_q8<128>(), st>>>(map32, map_sc, a);
-    else chunk_tc2_kernel<128, BF16, false><<<a.n_items, kThreads2, tc2_smem_bytes<128>(), st>>>(map32, map_sc, a);
+    const int grid = a.split_parts > 1 ? a.split_first + (a.n_items - a.split_first) * a.split_parts : a.n_items;
+    if (a.q8_arena) chunk_tc2_kernel<128, BF16, true><<<grid, kThreads2Q8, tc2_smem_bytes_q8<128>(), st>>>(map32, map_sc, a);
+    else chunk_tc2_kernel<128, BF16, false><<<grid, kThreads2, tc2_smem_bytes<128>(), st>>>(map32, map_sc, a);
     return cudaGetLastError();
 }
 

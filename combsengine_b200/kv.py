@@ -312,6 +312,10 @@ class KVArena:
         inputs, False = the compute stream waits for the input copies' event before every kernel."""
         check(self._lib.cbkv_set_host_route(self._h, 1 if direct else 0))
 
+    def set_chunk_split(self, max_parts: int) -> None:
+        """Two-tile chunk kernel: most K/V slices per item of a launch's last, mostly empty wave (1 = never cut)."""
+        check(self._lib.cbkv_set_chunk_split(self._h, max_parts))
+
     def set_chunk_kernel(self, mode: int) -> None:
         """0 = library's choice, 1 = mma.sync chunk kernel, 2 = tcgen05/TMEM kernel (one query tile per
         CTA), 3 = tcgen05/TMEM kernel with two query tiles per CTA (head_dim 128); int8 layers are read

@@ -336,6 +336,11 @@ int32_t cbkv_set_decode_tuning(cbkv_arena* arena, int32_t ctas_per_sm, int32_t s
  * flag, 0 = `stream` waits for the input copies' event before every kernel (what other steps use). */
 int32_t cbkv_set_host_route(cbkv_arena* arena, int32_t direct);
 
+/* Two-tile tcgen05 chunk kernel: when the last wave of a launch (one CTA per SM at a time) would fill at
+ * most half of the SMs, its items are cut along K/V into up to `max_parts` CTAs each, whose partial rows
+ * the last finisher adds up.  1 = never cut; default 4. */
+int32_t cbkv_set_chunk_split(cbkv_arena* arena, int32_t max_parts);
+
 /* Which kernel runs a step that is not pure decode: 0 = the library chooses (tcgen05
  * tiles once the step has at least 64 new tokens), 1 = the mma.sync kernel, 2 = the
  * tcgen05/TMEM kernel with one 128-row query tile per CTA (head_dim 64, 128 or 256), 3 = the

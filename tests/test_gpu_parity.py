@@ -238,6 +238,26 @@ def test_host_buffer_pipeline_over_many_layers_and_steps(direct):
     assert g.device_status() == 0
 
 
+@pytest.mark.parametrize("n_q,n_kv,chunk,window", [(32, 8, 512, None), (28, 4, 256, None), (28, 4, 256, 2500)])
+def test_chunk_items_of_a_short_last_wave_are_cut_along_kv(n_q, n_kv, chunk, window):
+    # One prompt in chunks: 64 (or 32) work items per launch on 148 SMs, so the two-tile kernel cuts every
+    # item into 2 (or 4) K/V slices once the context is long enough, and the last slice to finish merges
+    # them.  Checked against the oracle at every chunk; then again with the cutting switched off, which must
+    # give the same numbers to within the rounding of a different summation order.
+    outs = []
+    for max_parts in (4, 1):
+        p = Pair(1, n_q, n_kv, 128, 8192, num_pages=400, seed=77, shuffle_free_list=True)
+        p.g.set_chunk_split(max_parts)
+        s_ = p.new_seq()
+        last = None
+        for _ in range(4608 // chunk):
+            last = p.step([s_], [chunk], window=window)
+        outs.append(np.asarray(last[0], np.float32))
+        p.assert_state_equal(pages="used")
+        assert p.g.device_status() == 0
+    np.testing.assert_allclose(outs[0], outs[1], atol=2e-3, rtol=1e-2)
+
+
 def test_one_long_sequence_is_cut_into_many_parts():
     # a single 20 000-token sequence: every (kv head) segment is split over dozens of CTAs, so the
     # ticket merge runs with far more than eight partials
