@@ -339,6 +339,7 @@ class DecodeRun:
         torch = self.torch
         for _ in range(warmup):
             fn()
+        self.rollback(warmup)
         out, t0 = [], None
         for _ in range(repeats):
             if barrier:
@@ -360,7 +361,18 @@ class DecodeRun:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
             out.append(ms)
+            self.rollback(steps)  # outside the timed region: every loop starts from the configured contexts
         return out, t0, time.time()
+
+    def rollback(self, n):
+        """Drop the n tokens the last n steps appended (popn, kv.rs:807-835), so that the contexts do not drift
+        away from the configured ones over hundreds of steps."""
+        if n <= 0:
+            return
+        self.torch.cuda.synchronize()
+        for s in self.seqs:
+            if s.popn(n) != n:
+                raise RuntimeError("popn refused a rollback between timed loops")
 
     def kernel_level(self, steps):
         """CUDA events around every launch over `steps` more steps (this forbids the overlap of consecutive
@@ -370,6 +382,7 @@ class DecodeRun:
             self.step_device()
         kms, kn = self.arena.profile_read()
         self.arena.profile_enable(False)
+        self.rollback(steps)
         return kms / kn * 1e3
 
     def close(self):
@@ -388,11 +401,11 @@ def measure_decode(w: Workload, lens: np.ndarray, local_rank: int, args, steps: 
     (ms,), _, _ = run.timed(run.step_device, steps, warmup)
     launches = _launch_count() - launches0
     assert run.arena.device_status() == 0, f"kernel status word set ({w.name})"
-    lens_mid = run.lens + 1 + warmup + steps // 2
+    lens_mid = run.lens + 1 + steps // 2  # contexts at the middle of a timed loop (the loops are rolled back)
     bytes_step = w.bytes_per_step(lens_mid)
     ksteps = min(steps, 10)
     us = run.kernel_level(ksteps)
-    bytes_launch = w.bytes_per_step(run.lens + 1 + warmup + steps + ksteps // 2) / w.layers
+    bytes_launch = w.bytes_per_step(run.lens + 1 + ksteps // 2) / w.layers
     peak, _, src = peaks()
     ms_step = ms / steps
     out = {
@@ -603,8 +616,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     assert run.arena.device_status() == 0, "kernel status word set"
     n_total = w.batch * world
     value = n_total * args.steps / (ms * 1e-3)
-    done_steps = args.warmup + args.steps * repeats
-    bytes_rank = w.bytes_per_step(run.lens + 1 + args.warmup + args.steps * repeats // 2)  # contexts at the middle of the timed loops
+    bytes_rank = w.bytes_per_step(run.lens + 1 + args.steps // 2)  # contexts at the middle of a timed loop (every loop is rolled back)
     if world > 1:  # every rank's own bytes: their sum for the job's GB/s, min and max to show the balance
         t = torch.tensor([bytes_rank], device=dev, dtype=torch.float64)
         allb = [torch.zeros_like(t) for _ in range(world)]
@@ -616,7 +628,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     # roofline of the decode kernel: CUDA events around every launch, same steps again
     us = run.kernel_level(args.steps)
-    bytes_launch = w.bytes_per_step(run.lens + 1 + done_steps + args.steps // 2) / w.layers  # mean over the layers of a step
+    bytes_launch = w.bytes_per_step(run.lens + 1 + args.steps // 2) / w.layers  # mean over the layers of a step
     achieved = bytes_launch / (us * 1e-6) / 1e9
 
     # end to end: host buffers in, host buffers out, every layer
@@ -673,7 +685,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                    "l2": f"inputs larger than L2 (about {bytes_rank / 1e9:.1f} GB of KV read per step and GPU)",
                    "sharding": "one seeded population of 32 x N sequences, assigned to ranks by page count (LPT); no collective in the path",
                    "timing": (f"median of {repeats} timed loops of {args.steps} steps" if repeats > 1
-                              else f"one timed loop of {args.steps} steps")},
+                              else f"one timed loop of {args.steps} steps") +
+                             "; the appended tokens are dropped again (popn) after the warm-up and after every loop, outside the"
+                             " timed region, so every loop runs the configured contexts"},
         "repeats": repeats, "ms_per_step_all_repeats": [t / args.steps for t in times],
         "hbm_gbs": bytes_job / (ms_step * 1e-3) / 1e9,
         "hbm_frac_of_8tbs": bytes_job / world / (ms_step * 1e-3) / 8e12,
