@@ -1321,7 +1321,45 @@ int32_t cbkv_device_status(cbkv_arena* arena, void* stream, int32_t* status) {
                 if (s2 == 4) this_exit = mx;
             }
             fprintf(stderr, "%s | period %.1f us\n", line, this_exit - prev_exit);
+            {   // the same times by quarter of the CTA index (CTAs are dispatched in index order as SMs come free)
+                char q[256]; int qo = snprintf(q, sizeof q, "[cbkv chain]   by index quarter, entry / exit:");
+                for (int part = 0; part < 4; part++) {
+                    double en = 0, ex = 0; int cnt = 0;
+                    for (int c = n * part / 4; c < n * (part + 1) / 4; c++) {
+                        const unsigned long long e0 = h[((size_t)l * 512 + c) * 16 + 0], e1 = h[((size_t)l * 512 + c) * 16 + 6];
+                        if (!e0 || !e1) continue;
+                        en += (double)(e0 - t0) * 1e-3; ex += (double)(e1 - t0) * 1e-3; cnt++;
+                    }
+                    if (cnt) qo += snprintf(q + qo, sizeof q - qo, "  %.1f / %.1f", en / cnt, ex / cnt);
+                }
+                fprintf(stderr, "%s\n", q);
+            }
             prev_exit = this_exit;
+        }
+        {   // is a CTA's streaming time a property of the SM it ran on?  per SM: mean and spread over the eight launches
+            std::map<int, std::vector<double>> by_sm;
+            for (int l = 0; l < 8; l++)
+                for (int c = 0; c < n; c++) {
+                    const unsigned long long* r = &h[((size_t)l * 512 + c) * 16];
+                    if (r[4] && r[7]) by_sm[(int)r[11]].push_back((double)(r[7] - r[4]) * 1e-3);
+                }
+            std::vector<std::pair<double, int>> order;
+            double within = 0; int nw = 0;
+            for (auto& kv : by_sm) {
+                double m = 0; for (double x : kv.second) m += x; m /= kv.second.size();
+                for (double x : kv.second) { within += (x - m) * (x - m); nw++; }
+                order.push_back({m, kv.first});
+            }
+            std::sort(order.begin(), order.end());
+            double gm = 0; for (auto& o : order) gm += o.first; gm /= std::max<size_t>(1, order.size());
+            double between = 0; for (auto& o : order) between += (o.first - gm) * (o.first - gm);
+            fprintf(stderr, "[cbkv chain] streaming time per SM (first tile -> last copy issued): mean %.2f us, std between SMs %.2f, std within an SM %.2f\n",
+                    gm, std::sqrt(between / std::max<size_t>(1, order.size())), std::sqrt(within / std::max(1, nw)));
+            char line[1024]; int off = snprintf(line, sizeof line, "[cbkv chain] fastest SMs:");
+            for (size_t i = 0; i < std::min<size_t>(10, order.size()); i++) off += snprintf(line + off, sizeof line - off, " %d:%.1f", order[i].second, order[i].first);
+            off += snprintf(line + off, sizeof line - off, " | slowest:");
+            for (size_t i = order.size() > 10 ? order.size() - 10 : 0; i < order.size(); i++) off += snprintf(line + off, sizeof line - off, " %d:%.1f", order[i].second, order[i].first);
+            fprintf(stderr, "%s\n", line);
         }
         d->dbg_chain_last = -1;
     }
