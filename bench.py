@@ -337,9 +337,23 @@ class DecodeRun:
         """Device time of `steps` calls of fn after `warmup` untimed ones, bracketed by a barrier and a synchronise on
         both sides, maximum over ranks.  repeats > 1: the timed loop runs that many times; all times are returned."""
         torch = self.torch
-        for _ in range(warmup):
-            fn()
-        self.rollback(warmup)
+        # a loop longer than the arena has room for drops its tokens part-way (popn is host bookkeeping: nothing is
+        # enqueued, and the stream keeps later appends behind earlier reads of the freed pages)
+        room = self.room()
+        done = 0
+
+        def run(n):
+            nonlocal done
+            for _ in range(n):
+                if done >= room:
+                    self.rollback(done, sync=False)
+                    done = 0
+                fn()
+                done += 1
+
+        run(warmup)
+        self.rollback(done)
+        done = 0
         out, t0 = [], None
         for _ in range(repeats):
             if barrier:
@@ -348,8 +362,7 @@ class DecodeRun:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0 = t0 or time.time()
             e0.record(self.stream)
-            for _ in range(steps):
-                fn()
+            run(steps)
             e1.record(self.stream)
             if barrier:
                 barrier()
@@ -361,15 +374,22 @@ class DecodeRun:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
             out.append(ms)
-            self.rollback(steps)  # outside the timed region: every loop starts from the configured contexts
+            self.rollback(done)  # outside the timed region: every loop starts from the configured contexts
+            done = 0
         return out, t0, time.time()
 
-    def rollback(self, n):
+    def room(self):
+        """Steps between two rollbacks inside a long timed loop: at most 64, so that the contexts stay within 64
+        tokens of the configured ones whatever --steps is, and never more than the arena has pages for."""
+        return min(64, max(16, (self.arena.num_free_pages() // max(1, len(self.seqs)) - 2) * 16))
+
+    def rollback(self, n, sync=True):
         """Drop the n tokens the last n steps appended (popn, kv.rs:807-835), so that the contexts do not drift
         away from the configured ones over hundreds of steps."""
         if n <= 0:
             return
-        self.torch.cuda.synchronize()
+        if sync:
+            self.torch.cuda.synchronize()
         for s in self.seqs:
             if s.popn(n) != n:
                 raise RuntimeError("popn refused a rollback between timed loops")
@@ -377,6 +397,7 @@ class DecodeRun:
     def kernel_level(self, steps):
         """CUDA events around every launch over `steps` more steps (this forbids the overlap of consecutive
         launches, so the mean is the launch's duration when it runs alone); microseconds per launch."""
+        steps = min(steps, 64, self.room())
         self.arena.profile_enable(True)
         for _ in range(steps):
             self.step_device()
@@ -401,11 +422,11 @@ def measure_decode(w: Workload, lens: np.ndarray, local_rank: int, args, steps: 
     (ms,), _, _ = run.timed(run.step_device, steps, warmup)
     launches = _launch_count() - launches0
     assert run.arena.device_status() == 0, f"kernel status word set ({w.name})"
-    lens_mid = run.lens + 1 + steps // 2  # contexts at the middle of a timed loop (the loops are rolled back)
+    lens_mid = run.lens + 1 + min(steps, run.room()) // 2  # contexts at the middle of a timed loop (the loops are rolled back)
     bytes_step = w.bytes_per_step(lens_mid)
     ksteps = min(steps, 10)
     us = run.kernel_level(ksteps)
-    bytes_launch = w.bytes_per_step(run.lens + 1 + ksteps // 2) / w.layers
+    bytes_launch = w.bytes_per_step(run.lens + 1 + min(ksteps, 64, run.room()) // 2) / w.layers
     peak, _, src = peaks()
     ms_step = ms / steps
     out = {
@@ -616,7 +637,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     assert run.arena.device_status() == 0, "kernel status word set"
     n_total = w.batch * world
     value = n_total * args.steps / (ms * 1e-3)
-    bytes_rank = w.bytes_per_step(run.lens + 1 + args.steps // 2)  # contexts at the middle of a timed loop (every loop is rolled back)
+    bytes_rank = w.bytes_per_step(run.lens + 1 + min(args.steps, run.room()) // 2)  # contexts at the middle of a timed loop (every loop is rolled back)
     if world > 1:  # every rank's own bytes: their sum for the job's GB/s, min and max to show the balance
         t = torch.tensor([bytes_rank], device=dev, dtype=torch.float64)
         allb = [torch.zeros_like(t) for _ in range(world)]
@@ -628,7 +649,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     # roofline of the decode kernel: CUDA events around every launch, same steps again
     us = run.kernel_level(args.steps)
-    bytes_launch = w.bytes_per_step(run.lens + 1 + args.steps // 2) / w.layers  # mean over the layers of a step
+    bytes_launch = w.bytes_per_step(run.lens + 1 + min(args.steps, 64, run.room()) // 2) / w.layers  # mean over the layers of a step
     achieved = bytes_launch / (us * 1e-6) / 1e9
 
     # end to end: host buffers in, host buffers out, every layer
@@ -686,8 +707,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                    "sharding": "one seeded population of 32 x N sequences, assigned to ranks by page count (LPT); no collective in the path",
                    "timing": (f"median of {repeats} timed loops of {args.steps} steps" if repeats > 1
                               else f"one timed loop of {args.steps} steps") +
-                             "; the appended tokens are dropped again (popn) after the warm-up and after every loop, outside the"
-                             " timed region, so every loop runs the configured contexts"},
+                             "; the appended tokens are dropped again (popn: host bookkeeping, nothing enqueued) after the"
+                             " warm-up, after every loop and every 64 steps of a longer loop, so the contexts stay within 64"
+                             " tokens of the configured ones"},
         "repeats": repeats, "ms_per_step_all_repeats": [t / args.steps for t in times],
         "hbm_gbs": bytes_job / (ms_step * 1e-3) / 1e9,
         "hbm_frac_of_8tbs": bytes_job / world / (ms_step * 1e-3) / 8e12,
