@@ -109,6 +109,10 @@ def workload(name: str, layers: int = 0, quant: bool = False) -> Workload:
                      "cfg3 gemma-3-4b-style decode: 34 layers (5 local w=1024 : 1 global), 8/4/256, batch 16 per GPU, "
                      "ctx 8192, windows over paged KV",
                      windows=[None if (i + 1) % 6 == 0 else 1024 for i in range(34)])
+    elif name == "cfg1":  # the reference's own small case: one sequence, one layer; a step is bound by launch latency
+        w = Workload("cfg1", 1, 9, 3, 64, 1, 512, 512, 64, 0xC0B50001,
+                     "cfg1 smollm2-135m geometry: 1 layer, 9/3/64, one sequence, 512-token prefix, 64-page arena, append + "
+                     "decode attention per step (0.4 MB per step: the time of a step is launch latency)")
     elif name == "cfg5":  # one GPU's shard of the churn workload: 64 sequences sharing a 1024-token prefix
         w = Workload("cfg5", 28, 28, 4, 128, 64, 128, 32768, 40960, 0xC0B50005,
                      "cfg5 qwen2.5-7b geometry serving shard: 64 sequences per GPU sharing a 1024-token prefix by page "
@@ -679,6 +683,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         also["cfg5_churn"] = measure_churn(w5, lens5, _partition(lens5 + w5.prefix, world), rank, world, local_rank, args, barrier)
         if world == 1:
             w3 = workload("cfg3")
+            w1 = workload("cfg1")
+            also["cfg1"] = measure_decode(w1, np.array([512]), local_rank, args, 60, 10)
+            also["cfg1"]["us_per_step"] = also["cfg1"]["ms_per_step"] * 1e3
             also["cfg3"] = measure_decode(w3, w3.lengths(w3.batch), local_rank, args, 20, 5)
             also["cfg5_shard"] = measure_decode(w5, lens5, local_rank, args, 10, 4)
             wq = workload("cfg2", quant=True)
