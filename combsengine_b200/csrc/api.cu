@@ -119,6 +119,7 @@ struct DeviceState {
     int decode_ctas_per_sm = 0, decode_stages = 0, decode_consumers = 0, decode_max_ctas = 0;
     bool pdl = true;
     bool host_direct = true;  // cbkv_set_host_route
+    bool zero_pending = false; // the step's first unit-table kernel still has to zero the decode kernels' counters
     // two-tile chunk kernel: slices of the items of a launch's last, mostly empty wave (ChunkArgs::split_*)
     int chunk_split = 4;               // most slices per item, 1 = never cut (cbkv_set_chunk_split)
     float* split_o = nullptr;
@@ -352,10 +353,10 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     d->step = StepDev{};
     d->last_kv_writer = -1;  // the upload is a full stream dependency
     d->unit_rows_used = 0;
-    // tickets and claim counters start every step at zero, whatever an earlier launch that gave up left behind
-    if (d->seg_counter) CU_TRY(cudaMemsetAsync(d->seg_counter, 0, d->counter_cap * sizeof(int32_t), st));
-    if (d->split_counter) CU_TRY(cudaMemsetAsync(d->split_counter, 0, (size_t)d->split_cap * sizeof(int32_t), st));
-    if (d->work_counters) CU_TRY(cudaMemsetAsync(d->work_counters, 0, 4 * sizeof(int32_t), st));
+    // tickets and claim counters start every step at zero, whatever an earlier launch that gave up left behind:
+    // the decode kernels' by the step's first unit-table kernel (get_decode_plan), the chunk kernel's here
+    d->zero_pending = true;
+    if (d->split_counter && !a->step_is_decode) CU_TRY(cudaMemsetAsync(d->split_counter, 0, (size_t)d->split_cap * sizeof(int32_t), st));
     if (a->step_meta.empty()) {  // an empty step: nothing to upload, nothing will launch
         d->uploaded_step = a->step_id;
         return CBKV_OK;
@@ -441,7 +442,10 @@ int32_t get_decode_plan(Arena* a, int64_t window, bool quant, cudaStream_t st, D
     pd.unit_row_off = d->unit_rows_used;
     d->unit_rows_used = need;
     CU_TRY(launch_resolve_units(pd.segs, pd.host.n_segs, d->step.tables, a->cfg.n_kv_heads, (int)a->num_pages,
-                                d->unit_rows + pd.unit_row_off, pd.host.n_units, d->status, st));
+                                d->unit_rows + pd.unit_row_off, pd.host.n_units, d->status, st,
+                                d->zero_pending ? d->seg_counter : nullptr, (int)d->counter_cap,
+                                d->zero_pending ? d->work_counters : nullptr, 4));
+    d->zero_pending = false;
     g_launches++;
     pd.fresh = true;
     auto ins = d->decode_plans.emplace(key, std::move(pd));

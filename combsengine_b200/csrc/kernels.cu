@@ -634,7 +634,12 @@ __device__ __forceinline__ void merge_parts(const DecodeArgs& a, int base, int n
 // Record index (page * n_kv + kv head) of every unit of a decode plan, once per step and
 // window: the decode launches of all layers read it instead of chasing the block tables.
 __global__ void resolve_units_kernel(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
-                                     int32_t* unit_row, int n_units, int32_t* status) {
+                                     int32_t* unit_row, int n_units, int32_t* status,
+                                     int32_t* zero_a, int n_a, int32_t* zero_b, int n_b) {
+    // the step's first launch of this kernel also puts the tickets and claim counters back to zero (whatever a
+    // launch that gave up left behind): one stream operation per step instead of three
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_a; i += gridDim.x * blockDim.x) zero_a[i] = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_b; i += gridDim.x * blockDim.x) zero_b[i] = 0;
     for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < n_units; u += gridDim.x * blockDim.x) {
         int lo = 0, hi = n_segs - 1;  // last segment whose first unit is <= u (an empty segment shares its successor's)
         while (lo < hi) {
@@ -1580,10 +1585,13 @@ cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, 
 }
 
 cudaError_t launch_resolve_units(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
-                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st) {
-    if (n_units <= 0) return cudaSuccess;
-    const int blocks = std::min((n_units + 255) / 256, 148 * 4);
-    resolve_units_kernel<<<blocks, 256, 0, st>>>(segs, n_segs, tables, n_kv, num_pages, unit_row, n_units, status);
+                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st,
+                                 int32_t* zero_a, int n_a, int32_t* zero_b, int n_b) {
+    if (!zero_a) n_a = 0;
+    if (!zero_b) n_b = 0;
+    if (n_units <= 0 && n_a <= 0 && n_b <= 0) return cudaSuccess;
+    const int blocks = std::max(1, std::min((std::max(n_units, n_a) + 255) / 256, 148 * 4));
+    resolve_units_kernel<<<blocks, 256, 0, st>>>(segs, n_segs, tables, n_kv, num_pages, unit_row, n_units, status, zero_a, n_a, zero_b, n_b);
     return cudaGetLastError();
 }
 

@@ -192,9 +192,11 @@ cudaError_t launch_decode(const CUtensorMap& map, const DecodeArgs& a, int n_cta
                           bool q8 = false);  // q8: the layer holds int8 records, `map` is the byte view with one record per box
 cudaError_t launch_chunk(const CUtensorMap& map, const ChunkArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_generic(const GenericArgs& a, bool bf16, cudaStream_t st);
-// unit_row of a decode plan from its segments and the step's block tables (once per step and window)
+// unit_row of a decode plan from its segments and the step's block tables (once per step and window);
+// zero_a / zero_b (may be null): counters the same launch sets to zero
 cudaError_t launch_resolve_units(const SegInfo* segs, int n_segs, const int32_t* tables, int n_kv, int num_pages,
-                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st);
+                                 int32_t* unit_row, int n_units, int32_t* status, cudaStream_t st,
+                                 int32_t* zero_a = nullptr, int n_a = 0, int32_t* zero_b = nullptr, int n_b = 0);
 cudaError_t launch_init_quant(void* arena, size_t n_records, int page_size, int d, cudaStream_t st);
 cudaError_t launch_append_quant(const AppendArgs& a, bool bf16, cudaStream_t st);
 cudaError_t launch_dequant_pages(const int32_t* tables, int n_entries, const GeomDev& geo, const void* arena, void* scratch,
