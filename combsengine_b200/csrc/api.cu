@@ -1423,6 +1423,12 @@ int32_t cbkv_profile_read(cbkv_arena* arena, double* total_ms, int64_t* launches
             for (int c = 0; c < n; c++) sum += (double)h[(size_t)c * 16 + s2];
             fprintf(stderr, "[cbkv tc] %-26s %9.0f cycles per KV tile (mean over %d CTAs, %.1f tiles each)\n", names[s2], sum / tiles, n, tiles / n);
         }
+        if (h[12] == 0x7c2) {  // float layers of the two-tile kernel: what a CTA spends outside its tiles
+            double pro = 0, epi = 0, loop = 0;
+            for (int c = 0; c < n; c++) { pro += (double)h[(size_t)c * 16 + 13]; epi += (double)h[(size_t)c * 16 + 14]; loop += (double)h[(size_t)c * 16 + 10]; }
+            fprintf(stderr, "[cbkv tc] per CTA: %.0f cycles from entry to the softmax loop, %.0f in the loop, %.0f from the loop's end to the output written\n",
+                    pro / n, loop / n, epi / n);
+        }
     }
     if ((debug_flags() & 4) && d->dbg_buf && d->dbg_ctas > 0 && d->dbg_ctas <= 4096) {
         std::vector<unsigned long long> h((size_t)d->dbg_ctas * 16);

@@ -616,6 +616,8 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
     const uint32_t b_v_full = b_q8, b_v_empty = b_q8 + 8, b_rawk = b_q8 + 16, b_rawv = b_rawk + kRawK * 8;
     (void)sRawK; (void)sRawV0; (void)sRawV1; (void)b_v_full; (void)b_v_empty; (void)b_rawk; (void)b_rawv; (void)REC;
 
+    const long long t_entry = TC_NOW();
+    (void)t_entry;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if ((smem_u32(smem) & 1023u) != 0) {
         if (tid == 0) atomicOr(a.status, ST_SMEM_ALIGN);
@@ -990,8 +992,10 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
         TC_DUMP(if (tid == 64) {
             unsigned long long* b = a.dbg_buf + (size_t)blockIdx.x * 16;
             b[5] = c_ws; b[6] = c_ld; b[7] = c_exp; b[8] = c_wo; b[9] = c_st; b[10] = TC_NOW() - tstart;
+            if (!Q8) { b[12] = 0x7c2; b[13] = tstart - t_entry; }  // float layer: cycles in front of the softmax loop
         });
-        (void)tstart; (void)c_wo;
+        const long long t_loop_end = TC_NOW();
+        (void)tstart; (void)c_wo; (void)t_loop_end;
         if (ok && n_tiles > 0) ok = mbar_wait_bounded(b_o_done + X * 8, (n_tiles - 1) & 1) && !*failed;
         ok = __all_sync(0xffffffffu, ok);
         // the row sum is the two halves' sums (exchanged whether or not the wait succeeded: the pair must
@@ -1095,6 +1099,7 @@ __global__ void __launch_bounds__(Q8 ? kThreads2Q8 : kThreads2) chunk_tc2_kernel
                 }
             }
         }
+        TC_DUMP(if (tid == 64 && !Q8) { a.dbg_buf[(size_t)blockIdx.x * 16 + 14] = TC_NOW() - t_loop_end; });
     }
     tc_fence_before();
     __syncthreads();
