@@ -126,6 +126,15 @@ def workload(name: str, layers: int = 0, quant: bool = False) -> Workload:
     return w
 
 
+def peak_sustained():
+    """Dense bf16 TFLOP/s of a seconds-long cuBLAS loop under the power cap (MEASURED_PEAKS.json), or None."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        v = json.load(open(path)).get("bf16_tflops_sustained")
+        return float(v) if v else None
+    return 1400.0  # the fallback's sustained figure
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -778,15 +787,21 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
             for s in seqs:
                 s.popn(prompt)
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(warm_passes):
         one_pass()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
     e0.record(stream)
     for _ in range(passes):
         one_pass()
     e1.record(stream)
     torch.cuda.synchronize()
+    t1 = time.time()
+    clocks = sampler.summary(t0, t1)
+    sampler.stop()
     ms = e0.elapsed_time(e1) / passes
     assert arena.device_status() == 0
     if args.measure:  # measurement build: per-role cycle counters of the last launch (CBKV_DEBUG=8), printed to stderr
@@ -816,7 +831,12 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
     pairs = prompt * (prompt + 1) // 2
     flops = 4.0 * n_q * d * pairs * layers * batch  # QK^T and PV over the causal pairs only
     _, peak, src = peaks()
+    sustained = peak_sustained()
     tfl = flops / (ms * 1e-3) / 1e12
+    # The denominator: the burst figure for a short run, the sustained one (a seconds-long cuBLAS loop under the
+    # power cap) when this run is itself long or was seen to hit the power cap.
+    long_run = ms * passes >= 500.0 or "sw_power_cap" in (clocks.get("reasons") or [])
+    use = sustained if (long_run and sustained) else peak
     return {
         "metric": "chunked_prefill_attention_tokens_per_s", "value": batch * prompt / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": passes, "warmup": warm_passes, "ms_per_step": ms, "higher_is_better": True,
@@ -827,8 +847,11 @@ def prefill_record(args, local_rank: int, layers: int = 32, passes: int = 1, war
                    "chunk_kernel": {0: "auto", 1: "mma.sync", 2: "tcgen05, one query tile per CTA",
                                     3: "tcgen05, two query tiles per CTA",
                                     4: "tcgen05, two query tiles per CTA, int8 records converted in the kernel"}[chunk_kernel]},
-        "roofline": {"bound": "tensor", "achieved": tfl, "peak": peak, "unit": "TFLOP/s", "frac": tfl / peak, "traffic": None,
-                     "algorithmic_flops_per_pass": flops, "peak_source": "cuBLAS bf16 burst, " + src},
+        "roofline": {"bound": "tensor", "achieved": tfl, "peak": use, "unit": "TFLOP/s", "frac": tfl / use, "traffic": None,
+                     "algorithmic_flops_per_pass": flops,
+                     "peak_source": ("cuBLAS bf16 sustained under the power cap, " if use is not peak else "cuBLAS bf16 burst, ") + src,
+                     "frac_of_burst_peak": tfl / peak, "frac_of_sustained_peak": (tfl / sustained) if sustained else None},
+        "clocks": clocks,
         "spot_check": {"rows": 4, "max_abs_err_vs_float64": worst, "tolerance": ("5e-2" if quant else "2e-3") + " + 1e-2 |ref|"},
     }
 
