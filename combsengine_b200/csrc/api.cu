@@ -71,6 +71,8 @@ struct StepSlot {
     uint8_t* host = nullptr;  // pinned
     uint8_t* dev = nullptr;
     size_t cap = 0, used = 0;
+    size_t flushed = 0;       // bytes of `host` already on their way to `dev` (slot_upload only fills the pinned mirror;
+                              // flush_uploads sends everything new in one copy, right before the kernel that needs it)
     cudaEvent_t ev = nullptr;
     bool pending = false;
 };
@@ -331,11 +333,21 @@ int32_t slot_upload(DeviceState* d, const void* src, size_t bytes, cudaStream_t 
         s.host = nh; s.dev = nd; s.cap = ncap;
     }
     memcpy(s.host + off, src, bytes);
-    CU_TRY(cudaMemcpyAsync(s.dev + off, s.host + off, bytes, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaEventRecord(s.ev, st));
-    s.pending = true;
     s.used = off + bytes;
     *dev_out = s.dev + off;
+    return CBKV_OK;
+}
+
+// Everything slot_upload has put into the current step slot since the last call goes to the device in one
+// copy (a decode step uploads the sequences' records, the block tables and the work split: three pieces, one
+// copy).  Called in front of every launch that reads the slot.
+int32_t flush_uploads(DeviceState* d, cudaStream_t st) {
+    StepSlot& s = d->slots[d->cur];
+    if (s.flushed >= s.used) return CBKV_OK;
+    CU_TRY(cudaMemcpyAsync(s.dev + s.flushed, s.host + s.flushed, s.used - s.flushed, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaEventRecord(s.ev, st));
+    s.pending = true;
+    s.flushed = s.used;
     return CBKV_OK;
 }
 
@@ -345,6 +357,7 @@ int32_t upload_step(Arena* a, cudaStream_t st) {
     StepSlot& s = d->slots[d->cur];
     if (s.pending) { CU_TRY(cudaEventSynchronize(s.ev)); s.pending = false; }
     s.used = 0;
+    s.flushed = 0;
     d->decode_plans.clear();
     d->chunk_plan_ok = false;
     d->chunk_item_begin = nullptr;
@@ -441,6 +454,7 @@ int32_t get_decode_plan(Arena* a, int64_t window, bool quant, cudaStream_t st, D
     }
     pd.unit_row_off = d->unit_rows_used;
     d->unit_rows_used = need;
+    { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
     CU_TRY(launch_resolve_units(pd.segs, pd.host.n_segs, d->step.tables, a->cfg.n_kv_heads, (int)a->num_pages,
                                 d->unit_rows + pd.unit_row_off, pd.host.n_units, d->status, st,
                                 d->zero_pending ? d->seg_counter : nullptr, (int)d->counter_cap,
@@ -513,6 +527,7 @@ int32_t check_step(Arena* a, int32_t layer) {
 
 int32_t run_append(Arena* a, int layer, const void* k, const void* v, cudaStream_t st) {
     DeviceState* d = dev_of(a);
+    { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
     AppendArgs args{d->step, geom(a), k, v, d->layers[(size_t)layer].base, d->status};
     if (d->layers[(size_t)layer].quant) {
         args.geo.tiled = 0;
@@ -553,12 +568,14 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
             if (rc) return rc;
         }
         GeomDev g = geom(a);
+        { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
         CU_TRY(launch_dequant_pages(d->step.tables, (int)a->step_tables.size(), g, L.base, d->qscratch.base, d->status, bf16, st));
         g_launches++;
         KV = &d->qscratch;
     } else if (L.quant && !q8_direct && !(d->fast && a->step_is_decode && !(debug_flags() & 16))) {
         GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
         ProfScope ps(d, st);
+        { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
         CU_TRY(launch_generic_quant(args, bf16, st));
         g_launches++;
         return CBKV_OK;
@@ -599,6 +616,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         }
 #endif
         ProfScope ps(d, st);
+        { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
         CU_TRY(launch_decode(L.map_kv, args, pd->host.n_ctas, dc.consumers, dc.smem_bytes, d->pdl, bf16, st, L.quant));
         g_launches++;
         d->last_kv_writer = k_fused ? layer : -1;
@@ -647,6 +665,7 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         }
 #endif
         ProfScope ps(d, st);
+        { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
         if (use_tc2) CU_TRY(q8_direct ? launch_chunk_tc2(L.map_k16, L.map_sc, args, bf16, st) : launch_chunk_tc2(KV->map_kv, KV->map_kv, args, bf16, st));
         else CU_TRY(launch_chunk_tc(KV->map_k16, KV->map_kv, args, bf16, st));
         g_launches++;
@@ -660,12 +679,14 @@ int32_t run_attention(Arena* a, int layer, const void* q, const void* k_fused, c
         args.step = d->step; args.geo = geom(a); args.item_begin = d->chunk_item_begin; args.n_items = d->chunk_host.n_items;
         args.q = q; args.out = out; args.status = d->status; args.window = (int32_t)w; args.scale_log2 = scale_log2;
         ProfScope ps(d, st);
+        { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
         CU_TRY(launch_chunk(KV->map_kv, args, bf16, st));
         g_launches++;
         return CBKV_OK;
     }
     GenericArgs args{d->step, geom(a), q, out, L.base, d->status, (int32_t)w, (float)scale};
     ProfScope ps(d, st);
+    { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
     CU_TRY(launch_generic(args, bf16, st));
     g_launches++;
     return CBKV_OK;
@@ -939,6 +960,7 @@ static int32_t run_rope_append(Arena* a, int layer, const Rope* r, const cbkv_qk
     args.eps = norm ? (float)norm->eps : 0.f;
     args.gemma = norm ? norm->gemma : 0;
     args.status = d->status;
+    { int32_t frc = flush_uploads(d, st); if (frc) return frc; }
     CU_TRY(launch_rope_append(args, a->cfg.dtype == CBKV_BF16, st));
     g_launches++;
     if (!k_out) d->last_kv_writer = layer;
