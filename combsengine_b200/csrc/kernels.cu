@@ -1020,6 +1020,12 @@ __global__ void __launch_bounds__((C + 2) * 32) decode_kernel(const __grid_const
     bool have = get_item(0, it);  // plan and block tables were uploaded by a copy: always visible
     int seg = have ? it.z : 0, pb = have ? it.x : 0;
     Piece cur = load_piece(a, seg);
+    if (have && g < a.geo.n_rep && t < (D * 2 + 127) / 128) {
+        // ask for the first piece's q rows in L2 while the previous launch is still finishing (a request, not a
+        // read: L2 is where that launch or a copy engine writes them, so nothing stale can be seen later)
+        const char* qp = reinterpret_cast<const char*>(a.q) + ((size_t)cur.tok_off * a.geo.n_q + (size_t)cur.h * a.geo.n_rep + g) * D * 2 + t * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(qp));
+    }
     pdl_wait();  // q, k_new and v_new come from earlier work in the stream
     if (a.in_flag != nullptr) {
         // ... or from copies on another stream, which end by writing this launch's number behind the data:
