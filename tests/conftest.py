@@ -16,3 +16,11 @@ def pytest_configure(config):
 def _built_oracle():
     import oracle
     oracle.build()
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _built_library():
+    # a fresh checkout has no libcombskv.so (built artefacts are not tracked): compile it once, where nvcc exists
+    from combsengine_b200 import _build
+    if not os.path.exists(_build.LIB):
+        _build.build()
