@@ -1146,8 +1146,8 @@ int32_t cbkv_host_sync(cbkv_arena* arena) {
     if (!a->dev) return CBKV_OK;
     DeviceState* d = dev_of(a);
     CU_TRY(cudaSetDevice(d->device));
-    for (auto& sl : d->io_slots)
-        if (sl.used) CU_TRY(cudaEventSynchronize(sl.out_done));
+    // every output copy runs on the one output stream, in order: waiting for the stream is waiting for all of them
+    if (d->d2h) CU_TRY(cudaStreamSynchronize(d->d2h));
     return CBKV_OK;
     });
 }
